@@ -1,0 +1,174 @@
+// Staged transfer plan for an all-to-all(v) on a (servers x gpus_per_server) cluster.
+//
+// The plan is a flat list of byte-range moves ("ops"). Each op carries its provenance (which
+// origin->final pair of the traffic matrix it belongs to, and where inside that pair's segment),
+// so a plan can be validated, replayed on host buffers, lowered to per-GPU work lists, costed,
+// and serialised without any other state.
+//
+// Capability parity with the reference's GlobalScheduler / LocalScheduler
+// (nvidia/src/fast_alltoall/alltoall_global_scheduler.cc:243-443 flash_scheduler,
+//  :649-886 ablation; alltoall_local_scheduler.cc:129-275 prepare/balance/restore;
+//  buffer planning :888-1107; per-GPU lowering :1181-1821; block split :1109-1150;
+//  chunk pipeline :1152-1178), without the fixed-size 20 MB result struct and its
+//  GPU_NUM_PER_SERVER / MAX_SERVER_NUM / MAX_TRANSFER_STEP_NUM caps.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "decompose.h"
+#include "matrix.h"
+
+namespace fastb {
+
+enum class Buf : uint8_t {
+  kInput = 0,    // caller's send buffer (segments ordered by destination rank)
+  kOutput = 1,   // caller's receive buffer (segments ordered by source rank)
+  kBalance = 2,  // staging on a same-server GPU that relays part of a heavier GPU's load
+  kRail = 3,     // staging on the rail GPU of the destination server, before redistribution
+};
+
+enum class Phase : uint8_t {
+  kBalance = 0,       // intra-server: heavy GPU -> light GPU, before any inter-server stage
+  kIntrinsic = 1,     // intra-server traffic that never leaves the server (or a direct flat op)
+  kRail = 2,          // inter-server stage: GPU i of server s -> GPU i of server perm(s)
+  kRedistribute = 3,  // intra-server: rail GPU -> true destination GPU
+};
+
+struct Op {
+  Phase phase;
+  Buf src_buf, dst_buf;
+  int32_t stage;     // rail / redistribute / staged-direct: stage index; otherwise -1
+  int32_t src_rank, dst_rank;
+  int32_t origin, final_dst;  // the matrix pair this piece belongs to
+  int64_t src_off, dst_off;   // units, relative to the named buffer of the named rank
+  int64_t len;                // units
+  int64_t pair_off;           // units, offset inside the origin->final segment
+};
+
+enum class PlanKind : int {
+  kStaged = 0,     // balance + BvN permutation stages + redistribute (FAST)
+  kSingleBurst = 1,// balance + one burst per destination server + redistribute (the "FLASH-A" ablation)
+  kFanout = 2,     // every pair at once, straight into the output (NCCL-group-like)
+  kSpreadOut = 3,  // n-1 ring-offset rounds
+};
+
+struct Topology {
+  int servers = 1;
+  int gpus = 1;  // per server
+  int ranks() const { return servers * gpus; }
+};
+
+struct PlanOptions {
+  PlanKind kind = PlanKind::kStaged;
+  MatchPolicy match = MatchPolicy::kFirstFit;
+  ScalePolicy scale_policy = ScalePolicy::kNone;
+  int64_t scale = 0;        // explicit coarsening divisor; 0 = derive from scale_policy
+  int64_t split_align = 1;  // units; pieces are only cut at multiples of this inside a segment
+  bool transpose = false;   // plan the reverse collective (combine / backward all-to-all)
+  LinkModel inter{0.7, 22.0};  // used by ScalePolicy::kAlphaBeta only
+  LinkModel intra{0.1, 1.2};
+  double mb_per_unit = 1.0;
+};
+
+struct RankBuffers {
+  int64_t input_units = 0, output_units = 0, balance_units = 0, rail_units = 0;
+};
+
+struct Plan {
+  Topology topo;
+  PlanOptions opt;
+  Matrix matrix;           // as planned (already transposed if opt.transpose)
+  Matrix server_matrix;    // S x S, per-rail load after balancing (ceil(tile_sum / gpus))
+  Decomposition decomp;    // of server_matrix (empty for kFanout / kSpreadOut)
+  int32_t num_stages = 0;  // number of distinct stage indices used by ops
+  std::vector<int64_t> in_disp, out_disp;  // n x n: offset of segment [r][peer] in r's input / output
+  std::vector<RankBuffers> buffers;        // per rank
+  std::vector<Op> ops;                     // global list, grouped by phase then stage
+  uint64_t matrix_hash = 0;
+};
+
+Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt = {});
+
+// ---- validation -----------------------------------------------------------------------------
+// Checks every op against buffer bounds, that each stage's rail ops form a partial permutation at
+// server level (one peer server per server per stage), that every unit of every pair reaches the
+// final output exactly once, and that staged data is forwarded completely. Returns an empty
+// string when the plan is sound, else the first problem found.
+std::string validate_plan(const Plan& p);
+
+// Sum over ops that write final output, per (origin, final) pair: must equal the matrix.
+Matrix delivered_matrix(const Plan& p);
+// Real (non-phantom) units moved by inter-server stage k at GPU-pair granularity.
+Matrix stage_matrix(const Plan& p, int stage);
+
+// Replays the plan on host memory. inputs[r] / outputs[r] are byte buffers of
+// input_units*unit_bytes / output_units*unit_bytes. `drop_op` (>=0) withholds one op, which is
+// how tests model a lost message. Returns the number of output bytes written.
+int64_t execute_on_host(const Plan& p, int unit_bytes, const std::vector<const uint8_t*>& inputs,
+                        const std::vector<uint8_t*>& outputs, int64_t drop_op = -1);
+
+// ---- cost model -----------------------------------------------------------------------------
+struct CostModel {
+  LinkModel inter{0.7, 22.0};  // defaults: 400 GbE class NIC (the reference simulator's ETHER400)
+  LinkModel intra{0.1, 1.2};   // defaults: the reference simulator's B100 entry
+  double mb_per_unit = 1.0;
+};
+struct PlanCost {
+  double total_us = 0, balance_us = 0, inter_us = 0, exposed_intra_us = 0;
+  double lower_bound_us = 0;   // busiest port (or busiest server NIC set) at full rate
+  double spread_out_us = 0;    // ring-offset baseline on the same matrix
+  std::vector<double> stage_inter_us, stage_redistribute_us;
+};
+// Pipeline model: balance, then stage k's inter-server transfer overlaps stage k-1's
+// redistribution (simulation/scheduler/global.cpp:237-402 pipeline2). For one server per GPU
+// (flat NVSwitch domain) every stage is charged to the `inter` link.
+PlanCost model_cost(const Plan& p, const CostModel& cm);
+// Link model for one NVLink-5 port: alpha in us, bandwidth in GB/s.
+LinkModel nvlink_model(double gbytes_per_s = 900.0, double alpha_us = 2.0);
+LinkModel gbps_model(double gbit_per_s, double alpha_us);
+
+// ---- lowering ---------------------------------------------------------------------------------
+// A work item is what one CTA copies in one go.
+struct WorkItem {
+  int64_t src_off, dst_off, bytes;  // bytes, relative to buffer bases
+  int32_t dst_rank;
+  uint8_t src_buf, dst_buf;
+  uint8_t wait_kind;    // 0 none, 1 wait for balance arrivals, 2 wait for rail arrivals of wait_stage
+  uint8_t signal_kind;  // 1 balance counter, 2 rail counter of `stage`, 3 output counter
+  int32_t stage, wait_stage;
+};
+struct RankProgram {
+  int rank = 0;
+  std::vector<WorkItem> items;              // execution order
+  int64_t expect_output_bytes = 0;          // bytes that land in this rank's output
+  int64_t expect_balance_bytes = 0;         // bytes that land in this rank's balance staging
+  std::vector<int64_t> expect_rail_bytes;   // per stage: bytes that land in this rank's rail staging
+  RankBuffers buffers_bytes;
+};
+struct LowerOptions {
+  int unit_bytes = 1;
+  int64_t chunk_bytes = 1 << 20;  // upper size of a work item
+  int64_t min_chunk_bytes = 64 << 10;
+  int max_chunks_per_op = 1 << 16;
+};
+RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo);
+
+// ---- serialisation ------------------------------------------------------------------------------
+std::string plan_to_json(const Plan& p, bool include_ops = true);
+std::vector<uint8_t> plan_to_bytes(const Plan& p);
+Plan plan_from_bytes(const std::vector<uint8_t>& blob);
+
+// ---- workloads ------------------------------------------------------------------------------------
+// Deterministic generators (splitmix64 stream; same output on every platform and from Python).
+Matrix workload_uniform(int n, int64_t max_entry, uint64_t seed, bool zero_diag);
+Matrix workload_balanced(int n, int64_t entry, bool zero_diag);
+// Row i spreads `row_total` over the other ranks with weights 1/k^s assigned along a seeded
+// random permutation of destinations; rounding remainders go to the heaviest destination so each
+// row sums exactly; entries are multiples of `quantum`.
+Matrix workload_zipf_rows(int n, double s, int64_t row_total, uint64_t seed, int64_t quantum = 1);
+// Entries drawn i.i.d. from a Zipf(s) law over {1..max_entry} (the reference testers' generator,
+// simulation/test.cpp:686-722), diagonal kept.
+Matrix workload_zipf_entries(int n, double s, int64_t max_entry, uint64_t seed);
+
+}  // namespace fastb

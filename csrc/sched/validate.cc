@@ -1,0 +1,133 @@
+// Plan validation and host replay (the CPU oracle for every executor).
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <sstream>
+#include <tuple>
+
+#include "plan.h"
+
+namespace fastb {
+
+namespace {
+int64_t buf_units(const RankBuffers& b, Buf k) {
+  switch (k) {
+    case Buf::kInput: return b.input_units;
+    case Buf::kOutput: return b.output_units;
+    case Buf::kBalance: return b.balance_units;
+    default: return b.rail_units;
+  }
+}
+using Interval = std::pair<int64_t, int64_t>;  // [begin, end)
+
+// Empty string if `iv` tiles [0, total) exactly once.
+std::string tiles_exactly(std::vector<Interval>& iv, int64_t total) {
+  std::sort(iv.begin(), iv.end());
+  int64_t pos = 0;
+  for (const Interval& x : iv) {
+    if (x.first != pos) return x.first < pos ? "overlap" : "gap";
+    pos = x.second;
+  }
+  return pos == total ? "" : "short";
+}
+}  // namespace
+
+std::string validate_plan(const Plan& p) {
+  const int n = p.matrix.n, G = p.topo.gpus, S = p.topo.servers;
+  std::ostringstream err;
+  if (static_cast<int>(p.buffers.size()) != n) return "buffers: wrong rank count";
+  std::map<std::pair<int, int>, std::vector<Interval>> delivered;           // (origin, final) -> segment intervals
+  std::map<std::tuple<int, int>, std::vector<Interval>> staged_w, staged_r;  // (rank, buf) -> intervals
+  std::map<int, std::map<int, int>> stage_map, stage_rev;                    // stage -> src server -> dst server
+
+  for (size_t k = 0; k < p.ops.size(); ++k) {
+    const Op& o = p.ops[k];
+    auto bad = [&](const char* what) { err << "op " << k << ": " << what; return err.str(); };
+    if (o.len <= 0) return bad("non-positive length");
+    if (o.src_rank < 0 || o.src_rank >= n || o.dst_rank < 0 || o.dst_rank >= n) return bad("rank out of range");
+    if (o.origin < 0 || o.origin >= n || o.final_dst < 0 || o.final_dst >= n) return bad("pair out of range");
+    if (o.src_off < 0 || o.src_off + o.len > buf_units(p.buffers[o.src_rank], o.src_buf)) return bad("source range outside its buffer");
+    if (o.dst_off < 0 || o.dst_off + o.len > buf_units(p.buffers[o.dst_rank], o.dst_buf)) return bad("destination range outside its buffer");
+    if (o.pair_off < 0 || o.pair_off + o.len > p.matrix.at(o.origin, o.final_dst)) return bad("piece outside its pair segment");
+    if (o.src_buf == Buf::kOutput || o.dst_buf == Buf::kInput) return bad("reads output or writes input");
+    const int ss = o.src_rank / G, ds = o.dst_rank / G;
+    if (o.phase != Phase::kRail && p.opt.kind != PlanKind::kFanout && p.opt.kind != PlanKind::kSpreadOut && ss != ds)
+      return bad("intra-server phase crosses servers");
+    if (o.phase == Phase::kRail) {
+      if (ss == ds) return bad("rail op inside one server");
+      if (o.src_rank % G != o.dst_rank % G) return bad("rail op is not rail-aligned");
+      if (o.stage < 0 || o.stage >= p.num_stages) return bad("stage out of range");
+      if (p.opt.kind == PlanKind::kStaged) {
+        auto& fwd = stage_map[o.stage];
+        auto& rev = stage_rev[o.stage];
+        if (fwd.count(ss) && fwd[ss] != ds) return bad("server sends to two servers in one stage");
+        if (rev.count(ds) && rev[ds] != ss) return bad("server receives from two servers in one stage");
+        fwd[ss] = ds; rev[ds] = ss;
+      }
+    }
+    if (o.src_buf == Buf::kInput) {
+      if (o.src_rank != o.origin) return bad("input read on a rank that is not the origin");
+      if (o.src_off != p.in_disp[static_cast<size_t>(o.origin) * n + o.final_dst] + o.pair_off) return bad("input offset does not match the pair segment");
+    } else {
+      staged_r[{o.src_rank, static_cast<int>(o.src_buf)}].push_back({o.src_off, o.src_off + o.len});
+    }
+    if (o.dst_buf == Buf::kOutput) {
+      if (o.dst_rank != o.final_dst) return bad("output written on a rank that is not the final destination");
+      if (o.dst_off != p.out_disp[static_cast<size_t>(o.final_dst) * n + o.origin] + o.pair_off) return bad("output offset does not match the pair segment");
+      delivered[{o.origin, o.final_dst}].push_back({o.pair_off, o.pair_off + o.len});
+    } else {
+      staged_w[{o.dst_rank, static_cast<int>(o.dst_buf)}].push_back({o.dst_off, o.dst_off + o.len});
+    }
+  }
+  for (int i = 0; i < n; ++i)
+    for (int j = 0; j < n; ++j) {
+      auto it = delivered.find({i, j});
+      std::vector<Interval> none;
+      std::string r = tiles_exactly(it == delivered.end() ? none : it->second, p.matrix.at(i, j));
+      if (!r.empty()) { err << "pair " << i << "->" << j << ": delivery has a " << r; return err.str(); }
+    }
+  for (int r = 0; r < n; ++r)
+    for (Buf b : {Buf::kBalance, Buf::kRail}) {
+      auto key = std::make_tuple(r, static_cast<int>(b));
+      std::vector<Interval> w = staged_w[key], rd = staged_r[key];
+      std::string a = tiles_exactly(w, buf_units(p.buffers[r], b));
+      if (!a.empty()) { err << "rank " << r << " staging " << static_cast<int>(b) << ": writes have a " << a; return err.str(); }
+      // Reads may split a written piece, but together they must cover the same bytes once.
+      a = tiles_exactly(rd, buf_units(p.buffers[r], b));
+      if (!a.empty()) { err << "rank " << r << " staging " << static_cast<int>(b) << ": forwards have a " << a; return err.str(); }
+    }
+  (void)S;
+  return "";
+}
+
+int64_t execute_on_host(const Plan& p, int unit_bytes, const std::vector<const uint8_t*>& inputs,
+                        const std::vector<uint8_t*>& outputs, int64_t drop_op) {
+  const int n = p.matrix.n;
+  if (static_cast<int>(inputs.size()) != n || static_cast<int>(outputs.size()) != n)
+    throw std::invalid_argument("execute_on_host: one input and one output buffer per rank");
+  std::vector<std::vector<uint8_t>> bal(n), rail(n);
+  for (int r = 0; r < n; ++r) {
+    bal[r].resize(static_cast<size_t>(p.buffers[r].balance_units) * unit_bytes);
+    rail[r].resize(static_cast<size_t>(p.buffers[r].rail_units) * unit_bytes);
+  }
+  auto base = [&](int r, Buf b, bool write) -> uint8_t* {
+    switch (b) {
+      case Buf::kInput: return write ? nullptr : const_cast<uint8_t*>(inputs[r]);
+      case Buf::kOutput: return outputs[r];
+      case Buf::kBalance: return bal[r].data();
+      default: return rail[r].data();
+    }
+  };
+  int64_t written = 0;
+  for (size_t k = 0; k < p.ops.size(); ++k) {
+    if (static_cast<int64_t>(k) == drop_op) continue;
+    const Op& o = p.ops[k];
+    const uint8_t* s = base(o.src_rank, o.src_buf, false) + o.src_off * unit_bytes;
+    uint8_t* d = base(o.dst_rank, o.dst_buf, true) + o.dst_off * unit_bytes;
+    std::memcpy(d, s, static_cast<size_t>(o.len) * unit_bytes);
+    if (o.dst_buf == Buf::kOutput) written += o.len * unit_bytes;
+  }
+  return written;
+}
+
+}  // namespace fastb

@@ -1,0 +1,251 @@
+"""Host scheduler: decomposition exactness, plan soundness, replay, cost model, serialisation.
+
+Follows the reference's self-checks (simulation/test.cpp:15-60 DecompositionTester: random
+matrices, re-sum the permutations, compare) and extends them to whole plans.
+"""
+import json
+import subprocess
+
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from fast_b200 import sched
+from fast_b200.sched import MatchPolicy, PlanKind, ScalePolicy, Topology
+
+
+def _resum(stages, n):
+    acc = np.zeros((n, n), dtype=np.int64)
+    for w, to in stages:
+        assert sorted(to) == list(range(n)), "stage is not a permutation"
+        for i, j in enumerate(to):
+            acc[i, j] += w
+    return acc
+
+
+@pytest.mark.parametrize("policy", [MatchPolicy.FIRST_FIT, MatchPolicy.BOTTLENECK])
+@pytest.mark.parametrize("n", [1, 2, 3, 8, 16, 33, 70])
+def test_decomposition_exact(n, policy):
+    for seed in range(3):
+        m = sched.workload_uniform(n, 10000, 100 * n + seed)
+        d = sched.decompose(m, policy)
+        assert d["exact"]
+        assert d["line_sum"] == max(m.sum(0).max(), m.sum(1).max())
+        assert (d["padded"] - d["padding"] == m).all() and (d["padding"] >= 0).all()
+        assert (_resum(d["stages"], n) == d["padded"]).all()
+        assert sum(w for w, _ in d["stages"]) == d["line_sum"]
+        assert len(d["stages"]) <= n * n - 2 * n + 2
+        ws = [w for w, _ in d["stages"]]
+        assert ws == sorted(ws, reverse=True), "stages must run heaviest first"
+
+
+def test_bottleneck_needs_fewer_stages():
+    m = sched.workload_zipf_rows(8, 1.2, 256 << 20, 7)
+    a = len(sched.decompose(m, MatchPolicy.FIRST_FIT)["stages"])
+    b = len(sched.decompose(m, MatchPolicy.BOTTLENECK)["stages"])
+    assert b <= a
+
+
+def test_coarsened_decomposition_covers_input():
+    m = sched.workload_uniform(8, 100000, 5)
+    d = sched.decompose(m, MatchPolicy.FIRST_FIT, 1000)
+    cover = _resum(d["stages"], 8)
+    assert (cover >= m).all()
+    assert len(d["stages"]) <= len(sched.decompose(m)["stages"])
+
+
+def test_sparse_and_zero_matrices():
+    z = np.zeros((4, 4), dtype=np.int64)
+    assert sched.decompose(z)["stages"] == []
+    p = sched.build_plan(z, Topology(2, 2))
+    assert p.validate() == "" and p.num_ops == 0
+    one = z.copy()
+    one[0, 3] = 17
+    p = sched.build_plan(one, Topology(2, 2))
+    assert p.validate() == "" and (p.delivered_matrix() == one).all()
+
+
+def test_rejects_bad_input():
+    with pytest.raises(Exception):
+        sched.build_plan(-np.ones((4, 4), dtype=np.int64), Topology(2, 2))
+    with pytest.raises(Exception):
+        sched.build_plan(np.ones((4, 4), dtype=np.int64), Topology(3, 2))
+    with pytest.raises(Exception):
+        sched.decompose(np.ones((2, 3), dtype=np.int64))
+
+
+TOPOS = [(1, 1), (1, 8), (8, 1), (2, 4), (4, 2), (3, 3), (5, 2)]
+
+
+@pytest.mark.parametrize("servers,gpus", TOPOS)
+@pytest.mark.parametrize("kind", [PlanKind.STAGED, PlanKind.SINGLE_BURST, PlanKind.FANOUT, PlanKind.SPREAD_OUT])
+def test_plan_sound(servers, gpus, kind):
+    n = servers * gpus
+    for seed in range(4):
+        m = sched.workload_uniform(n, 5000, seed + 31 * n, zero_diag=bool(seed % 2))
+        for align in (1, 16):
+            for transpose in (False, True):
+                p = sched.build_plan(m, Topology(servers, gpus), kind=kind, split_align=align, transpose=transpose)
+                assert p.validate() == ""
+                want = m.T if transpose else m
+                assert (p.matrix == want).all() and (p.delivered_matrix() == want).all()
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 4), st.integers(1, 4), st.integers(0, 2**31), st.sampled_from([0.0, 0.5, 1.0, 1.5]))
+def test_plan_property(servers, gpus, seed, skew):
+    n = servers * gpus
+    m = sched.workload_zipf_rows(n, skew, 100000, seed, 4) if n > 1 else np.array([[5]], dtype=np.int64)
+    p = sched.build_plan(m, Topology(servers, gpus), split_align=4)
+    assert p.validate() == ""
+    assert (p.delivered_matrix() == m).all()
+    # every inter-server stage is a partial permutation at server level
+    ops = p.ops
+    for k in range(p.num_stages):
+        rail = ops[(ops[:, 0] == sched.PHASE_RAIL) & (ops[:, 1] == k)]
+        pairs = {(int(a) // gpus, int(b) // gpus) for a, b in rail[:, 2:4]}
+        assert len({a for a, _ in pairs}) == len(pairs) == len({b for _, b in pairs})
+
+
+def test_flat_plan_is_direct_and_bound_tight():
+    m = sched.workload_zipf_rows(8, 1.2, 256 << 20, 3)
+    p = sched.build_plan(m, Topology.flat(8))
+    assert p.validate() == ""
+    ops = p.ops
+    assert (ops[:, 4] == sched.BUF_INPUT).all() and (ops[:, 5] == sched.BUF_OUTPUT).all(), "flat mode never stages"
+    assert p.buffers[:, 2:].sum() == 0
+    d = p.decomposition
+    assert sum(w for w, _ in d["stages"]) == max(m.sum(0).max(), m.sum(1).max())
+    total = sum(p.stage_matrix(k) for k in range(p.num_stages))
+    assert (total == m).all(), "stages must add up to the matrix exactly"
+
+
+def test_balance_equalises_rails():
+    m = np.zeros((8, 8), dtype=np.int64)
+    m[0, 4:] = 1000  # one hot GPU on server 0 sends everything to server 1
+    p = sched.build_plan(m, Topology(2, 4))
+    assert p.validate() == ""
+    ops = p.ops
+    rail = ops[ops[:, 0] == sched.PHASE_RAIL]
+    per_gpu = [rail[rail[:, 2] == g][:, 8].sum() for g in range(4)]
+    assert max(per_gpu) == 1000 and min(per_gpu) == 1000
+    assert (ops[:, 0] == sched.PHASE_BALANCE).any() and (ops[:, 0] == sched.PHASE_REDISTRIBUTE).any()
+    assert p.server_matrix[0, 1] == 1000
+
+
+@pytest.mark.parametrize("servers,gpus", [(2, 3), (1, 4), (4, 1), (3, 2)])
+def test_host_replay_bit_exact(servers, gpus):
+    n = servers * gpus
+    rng = np.random.default_rng(0)
+    m = sched.workload_uniform(n, 60, 9)
+    ub = 6
+    for kind in (PlanKind.STAGED, PlanKind.SINGLE_BURST, PlanKind.FANOUT, PlanKind.SPREAD_OUT):
+        p = sched.build_plan(m, Topology(servers, gpus), kind=kind)
+        ins = [rng.integers(0, 256, int(p.buffers[r, 0]) * ub, dtype=np.uint8) for r in range(n)]
+        outs = [np.full(int(p.buffers[r, 1]) * ub, 0xEE, dtype=np.uint8) for r in range(n)]
+        assert p.execute_on_host(ub, ins, outs) == m.sum() * ub
+        ind, od = p.in_disp, p.out_disp
+        for d in range(n):
+            for s in range(n):
+                a = ins[s][ind[s, d] * ub:(ind[s, d] + m[s, d]) * ub]
+                b = outs[d][od[d, s] * ub:(od[d, s] + m[s, d]) * ub]
+                assert (a == b).all()
+
+
+def test_lost_message_is_visible_in_replay():
+    """Fault injection on the host: withholding one op must leave a hole the checker can see."""
+    m = sched.workload_uniform(6, 60, 2)
+    p = sched.build_plan(m, Topology(2, 3))
+    ins = [np.full(int(p.buffers[r, 0]), 1, dtype=np.uint8) for r in range(6)]
+    outs = [np.zeros(int(p.buffers[r, 1]), dtype=np.uint8) for r in range(6)]
+    full = p.execute_on_host(1, ins, outs)
+    outs2 = [np.zeros_like(o) for o in outs]
+    drop = int(np.nonzero(p.ops[:, 5] == sched.BUF_OUTPUT)[0][0])
+    short = p.execute_on_host(1, ins, outs2, drop_op=drop)
+    assert short == full - p.ops[drop, 8]
+    assert sum(int((o == 0).sum()) for o in outs2) == p.ops[drop, 8]
+
+
+def test_lowering_conserves_bytes_and_orders_waits():
+    m = sched.workload_uniform(8, 70000, 4)
+    p = sched.build_plan(m, Topology(2, 4), split_align=16)
+    ub = 2
+    tot_out = 0
+    for r in range(8):
+        g = p.lower(r, ub, 4096)
+        it = g["items"]
+        assert (it[:, 2] > 0).all() and (it[:, 2] <= 4096).all()
+        mine = p.ops[p.ops[:, 2] == r]
+        assert it[:, 2].sum() == mine[:, 8].sum() * ub
+        assert g["expect_output_bytes"] == m[:, r].sum() * ub
+        tot_out += it[it[:, 7] == 3][:, 2].sum()
+        # an item that forwards staged data always declares what it waits for
+        assert ((it[:, 4] == sched.BUF_BALANCE) == (it[:, 6] == 1)).all()
+        assert ((it[:, 4] == sched.BUF_RAIL) == (it[:, 6] == 2)).all()
+    assert tot_out == m.sum() * ub
+
+
+def test_serialisation_roundtrip_and_cache(tmp_path):
+    m = sched.workload_uniform(8, 999, 1)
+    p = sched.build_plan(m, Topology(2, 4))
+    q = sched.Plan.from_bytes(p.to_bytes())
+    assert q.validate() == "" and (q.ops == p.ops).all() and q.matrix_hash == p.matrix_hash
+    j = json.loads(p.to_json())
+    assert j["servers"] == 2 and len(j["ops"]) == p.num_ops
+    with pytest.raises(Exception):
+        sched.Plan.from_bytes(p.to_bytes()[:40])
+    c = sched.PlanCache()
+    a = c.get(m, Topology(2, 4))
+    b = c.get(m.copy(), Topology(2, 4))
+    assert a is b and c.hits == 1 and c.misses == 1
+    c.save(tmp_path / "plans.bin")
+    c2 = sched.PlanCache()
+    c2.load(tmp_path / "plans.bin")
+    assert c2.get(m, Topology(2, 4)).num_ops == p.num_ops and c2.misses == 0
+
+
+def test_cost_model_against_reference_figures():
+    # 2 servers x 8 GPUs, 400 GbE between, NVLink inside: the reference simulator reports a
+    # 2.4-2.65x modeled speed-up over spread-out for random matrices of this shape.
+    sp = []
+    for seed in range(5):
+        p = sched.build_plan(sched.workload_uniform(16, 10000, seed), Topology(2, 8))
+        c = p.cost(sched.gbps_model(400, 0.7), sched.LinkModel(0.1, 2.3))
+        assert c["total_us"] >= c["lower_bound_us"] > 0
+        sp.append(c["spread_out_us"] / c["total_us"])
+    assert 2.0 < np.mean(sp) < 3.2
+    # flat NVSwitch domain: staged plan within alpha*stages of the port bound
+    m = sched.workload_zipf_rows(8, 1.2, 256 << 20, 3)
+    p = sched.build_plan(m, Topology.flat(8))
+    nv = sched.nvlink_model(900.0, 2.0)
+    c = p.cost(nv, nv, 1e-6)
+    assert c["total_us"] <= c["lower_bound_us"] + 2.0 * p.num_stages + 1e-6
+    f = sched.build_plan(m, Topology.flat(8), kind=PlanKind.SPREAD_OUT).cost(nv, nv, 1e-6)
+    assert f["total_us"] > c["total_us"]
+
+
+def test_coarsening_reduces_stages_for_small_messages():
+    m = sched.workload_uniform(32, 10000, 3)
+    a = sched.build_plan(m, Topology(16, 2))
+    b = sched.build_plan(m, Topology(16, 2), scale_policy=ScalePolicy.ALWAYS)
+    assert b.validate() == "" and (b.delivered_matrix() == m).all()
+    assert b.num_stages < a.num_stages
+
+
+def test_scheduler_latency_budget():
+    m = sched.workload_zipf_rows(8, 1.0, 64 << 20, 1)
+    assert sched.decompose_time_us(m, MatchPolicy.FIRST_FIT, 50) < 90.0  # the reference needs ~90 us for 8x8
+
+
+def test_simulator_cli_config1(tmp_path):
+    from fast_b200 import _build
+
+    exe = _build.build_sim()
+    out = subprocess.run([str(exe), "plan", "--servers", "8", "--gpus", "1", "--skew", "1.2", "--row-bytes", str(256 << 20),
+                          "--seed", "1", "--flat", "1", "--nvlink-gbs", "900"], capture_output=True, text=True, check=True).stdout
+    j = json.loads(out.splitlines()[0])
+    assert j["valid"] and j["stages_sum_to_matrix"] and j["delivered_exact"] and j["decomposition_exact"]
+    assert j["line_sum"] == j["max_line_sum_input"]
+    assert j["modeled_us"] >= j["lower_bound_us"] > 0
+    out = subprocess.run([str(exe), "verify", "--max-dim", "32", "--reps", "2"], capture_output=True, text=True, check=True).stdout
+    assert json.loads(out.splitlines()[-1])["failures"] == 0
