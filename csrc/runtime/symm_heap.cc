@@ -1,0 +1,114 @@
+#include "symm_heap.h"
+
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <stdexcept>
+
+namespace fastb {
+
+namespace {
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string("SymmHeap: ") + what + ": " + cudaGetErrorString(e));
+}
+}  // namespace
+
+SymmHeap::SymmHeap(int rank, int world, size_t bytes) : rank_(rank), world_(world), bytes_(bytes) {
+  if (rank < 0 || rank >= world) throw std::invalid_argument("SymmHeap: rank out of range");
+  peer_base_.assign(world, nullptr);
+  void* p = nullptr;
+  check(cudaMalloc(&p, bytes), "cudaMalloc slab");
+  check(cudaMemset(p, 0, bytes), "cudaMemset slab");
+  peer_base_[rank] = p;
+  free_[0] = bytes;
+  if (world == 1) { opened_ = true; upload_table(); }
+}
+
+std::vector<SymmHeap*> SymmHeap::create_local_group(int world, size_t bytes) {
+  std::vector<SymmHeap*> hs;
+  std::vector<void*> slabs(world, nullptr);
+  for (int r = 0; r < world; ++r) {
+    check(cudaMalloc(&slabs[r], bytes), "cudaMalloc slab");
+    check(cudaMemset(slabs[r], 0, bytes), "cudaMemset slab");
+  }
+  for (int r = 0; r < world; ++r) {
+    SymmHeap* h = new SymmHeap();
+    h->rank_ = r; h->world_ = world; h->bytes_ = bytes;
+    h->peer_base_ = slabs;
+    h->free_[0] = bytes;
+    h->opened_ = true;
+    h->upload_table();
+    hs.push_back(h);
+  }
+  return hs;
+}
+
+SymmHeap::~SymmHeap() {
+  for (int r = 0; r < world_; ++r) {
+    if (!peer_base_[r]) continue;
+    if (r == rank_) cudaFree(peer_base_[r]);
+    else if (r < static_cast<int>(ipc_opened_.size()) && ipc_opened_[r]) cudaIpcCloseMemHandle(peer_base_[r]);
+  }
+  if (d_table_) cudaFree(d_table_);
+}
+
+std::string SymmHeap::ipc_handle() const {
+  cudaIpcMemHandle_t h;
+  check(cudaIpcGetMemHandle(&h, peer_base_[rank_]), "cudaIpcGetMemHandle");
+  static_assert(sizeof(h) == kIpcHandleBytes, "unexpected IPC handle size");
+  return std::string(reinterpret_cast<const char*>(&h), sizeof(h));
+}
+
+void SymmHeap::open_peers(const std::vector<std::string>& handles) {
+  if (static_cast<int>(handles.size()) != world_) throw std::invalid_argument("SymmHeap: need one handle per rank");
+  ipc_opened_.assign(world_, 0);
+  for (int r = 0; r < world_; ++r) {
+    if (r == rank_) continue;
+    if (handles[r].size() != sizeof(cudaIpcMemHandle_t)) throw std::invalid_argument("SymmHeap: bad handle size");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handles[r].data(), sizeof(h));
+    void* p = nullptr;
+    check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    peer_base_[r] = p;
+    ipc_opened_[r] = 1;
+  }
+  opened_ = true;
+  upload_table();
+}
+
+void SymmHeap::upload_table() {
+  if (!d_table_) check(cudaMalloc(reinterpret_cast<void**>(&d_table_), sizeof(void*) * world_), "cudaMalloc table");
+  check(cudaMemcpy(d_table_, peer_base_.data(), sizeof(void*) * world_, cudaMemcpyHostToDevice), "upload table");
+}
+
+size_t SymmHeap::alloc(size_t bytes) {
+  const size_t need = (bytes + 255) / 256 * 256 + (bytes == 0 ? 256 : 0);
+  for (auto it = free_.begin(); it != free_.end(); ++it) {
+    if (it->second < need) continue;
+    const size_t off = it->first, left = it->second - need;
+    free_.erase(it);
+    if (left) free_[off + need] = left;
+    taken_[off] = need;
+    in_use_ += need;
+    return off;
+  }
+  throw std::runtime_error("SymmHeap: out of symmetric memory (asked " + std::to_string(bytes) + " B, in use " +
+                           std::to_string(in_use_) + " of " + std::to_string(bytes_) + ")");
+}
+
+void SymmHeap::free(size_t offset) {
+  auto it = taken_.find(offset);
+  if (it == taken_.end()) throw std::invalid_argument("SymmHeap: free of an unknown offset");
+  size_t off = it->first, sz = it->second;
+  taken_.erase(it);
+  in_use_ -= sz;
+  auto next = free_.lower_bound(off);
+  if (next != free_.end() && off + sz == next->first) { sz += next->second; next = free_.erase(next); }
+  if (next != free_.begin()) {
+    auto prev = std::prev(next);
+    if (prev->first + prev->second == off) { prev->second += sz; return; }
+  }
+  free_[off] = sz;
+}
+
+}  // namespace fastb

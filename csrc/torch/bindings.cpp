@@ -1,0 +1,170 @@
+// Python bindings (torch extension module fast_b200._C): symmetric heap, status blocks, and the
+// launchers of every sm_100a kernel. Takes the place of the reference's TORCH_LIBRARY class
+// flash_comm_t (nvidia/alltoall_nvshmem.cpp:390-662) and pybind module flash_t
+// (amd/flash.cpp:650-666); the user-facing API built on top lives in fast_b200/parallel.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <memory>
+
+#include "kernels/api.h"
+#include "runtime/symm_heap.h"
+
+namespace py = pybind11;
+using namespace fastb;
+
+namespace {
+
+void cuda_check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// ---- symmetric heap -----------------------------------------------------------------------------
+struct HeapPy {
+  std::shared_ptr<SymmHeap> h;
+  int device;
+  torch::Tensor tensor(int64_t offset, std::vector<int64_t> shape, py::object dtype) const {
+    auto dt = torch::python::detail::py_object_to_dtype(dtype);
+    auto opts = torch::TensorOptions().dtype(dt).device(torch::kCUDA, device);
+    return torch::from_blob(static_cast<char*>(h->local_base()) + offset, shape, opts);
+  }
+};
+
+// ---- status block -------------------------------------------------------------------------------
+struct StatusPy {
+  DeviceStatus* d = nullptr;
+  StatusPy() {
+    cuda_check(cudaMalloc(reinterpret_cast<void**>(&d), sizeof(DeviceStatus)), "cudaMalloc status");
+    cuda_check(cudaMemset(d, 0, sizeof(DeviceStatus)), "clear status");
+  }
+  ~StatusPy() { if (d) cudaFree(d); }
+  // Synchronises the current stream, then returns (code, site, detail, seen, want).
+  py::tuple read() const {
+    DeviceStatus s;
+    cuda_check(cudaStreamSynchronize(cur_stream()), "sync before status read");
+    cuda_check(cudaMemcpy(&s, d, sizeof(s), cudaMemcpyDeviceToHost), "read status");
+    return py::make_tuple(s.code, s.site, s.detail, s.seen, s.want);
+  }
+  void clear() { cuda_check(cudaMemsetAsync(d, 0, sizeof(DeviceStatus), cur_stream()), "clear status"); }
+};
+
+// ---- a2a program ----------------------------------------------------------------------------------
+struct A2AProgramPy {
+  torch::Tensor items_dev, expect_rail_dev;
+  int n_items = 0, num_stages = 0;
+  unsigned long long expect_output = 0, expect_balance = 0;
+  int64_t total_bytes = 0;
+
+  // items: int64[k, 10] as produced by Plan.lower(); expect_rail: list of bytes per stage.
+  A2AProgramPy(torch::Tensor items, std::vector<int64_t> expect_rail, int64_t exp_out, int64_t exp_bal, int device) {
+    TORCH_CHECK(items.dim() == 2 && items.size(1) == 10 && items.dtype() == torch::kInt64 && items.is_cpu(), "items must be CPU int64[k, 10]");
+    TORCH_CHECK(static_cast<int>(expect_rail.size()) <= kSigMaxStages, "too many stages for the signal block");
+    n_items = static_cast<int>(items.size(0));
+    num_stages = static_cast<int>(expect_rail.size());
+    expect_output = static_cast<unsigned long long>(exp_out);
+    expect_balance = static_cast<unsigned long long>(exp_bal);
+    auto host = torch::empty({std::max(n_items, 1), static_cast<int64_t>(sizeof(A2AWork))}, torch::kUInt8);
+    A2AWork* w = reinterpret_cast<A2AWork*>(host.data_ptr());
+    auto it = items.contiguous();
+    const int64_t* q = it.data_ptr<int64_t>();
+    for (int i = 0; i < n_items; ++i, q += 10) {
+      w[i].src_off = q[0]; w[i].dst_off = q[1]; w[i].bytes = q[2]; w[i].dst_rank = static_cast<int>(q[3]);
+      w[i].src_buf = static_cast<unsigned char>(q[4]); w[i].dst_buf = static_cast<unsigned char>(q[5]);
+      w[i].wait_kind = static_cast<unsigned char>(q[6]); w[i].signal_kind = static_cast<unsigned char>(q[7]);
+      w[i].stage = static_cast<int>(q[8]); w[i].wait_stage = static_cast<int>(q[9]); w[i].pad_ = 0;
+      total_bytes += q[2];
+    }
+    auto dev = torch::Device(torch::kCUDA, device);
+    items_dev = host.to(dev);
+    auto er = torch::empty({std::max(num_stages, 1)}, torch::kInt64);
+    for (int k = 0; k < num_stages; ++k) er[k] = expect_rail[k];
+    expect_rail_dev = er.to(dev);
+  }
+
+  A2ARankArgs args(const HeapPy& heap, std::array<int64_t, 4> src_ptrs, std::array<int64_t, 4> dst_offs, int64_t sig_off,
+                   uint64_t epoch, const StatusPy& st, uint64_t timeout_ns) const {
+    A2ARankArgs a{};
+    a.items = reinterpret_cast<const A2AWork*>(items_dev.data_ptr());
+    a.n_items = n_items; a.rank = heap.h->rank(); a.world = heap.h->world(); a.num_stages = num_stages;
+    a.peer_table = heap.h->device_peer_table();
+    for (int i = 0; i < 4; ++i) { a.src_base[i] = reinterpret_cast<const unsigned char*>(src_ptrs[i]); a.dst_heap_off[i] = dst_offs[i]; }
+    a.sig_heap_off = sig_off; a.epoch = epoch; a.expect_output = expect_output; a.expect_balance = expect_balance;
+    a.expect_rail = reinterpret_cast<const unsigned long long*>(expect_rail_dev.data_ptr());
+    a.status = st.d; a.timeout_ns = timeout_ns;
+    return a;
+  }
+};
+
+void a2a_launch(const A2AProgramPy& p, const HeapPy& heap, std::array<int64_t, 4> src_ptrs, std::array<int64_t, 4> dst_offs,
+                int64_t sig_off, uint64_t epoch, const StatusPy& st, uint64_t timeout_ns, int ctas, int threads) {
+  TORCH_CHECK(heap.h->world() <= kSigMaxWorld, "world larger than the signal block supports");
+  A2ARankArgs a = p.args(heap, src_ptrs, dst_offs, sig_off, epoch, st, timeout_ns);
+  cuda_check(launch_a2a_push(&a, nullptr, 1, ctas, threads, cur_stream()), "a2a_push launch");
+}
+
+// One cooperative launch that runs every virtual rank of an in-process group.
+void a2a_launch_group(std::vector<const A2AProgramPy*> progs, std::vector<const HeapPy*> heaps,
+                      std::vector<std::array<int64_t, 4>> src_ptrs, std::array<int64_t, 4> dst_offs, int64_t sig_off, uint64_t epoch,
+                      std::vector<const StatusPy*> sts, uint64_t timeout_ns, int ctas, int threads) {
+  const int n = static_cast<int>(progs.size());
+  TORCH_CHECK(n >= 1 && static_cast<int>(heaps.size()) == n && static_cast<int>(src_ptrs.size()) == n && static_cast<int>(sts.size()) == n, "one entry per virtual rank");
+  std::vector<A2ARankArgs> host(n);
+  for (int r = 0; r < n; ++r) host[r] = progs[r]->args(*heaps[r], src_ptrs[r], dst_offs, sig_off, epoch, *sts[r], timeout_ns);
+  auto dev = torch::empty({static_cast<int64_t>(n * sizeof(A2ARankArgs))}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, heaps[0]->device));
+  cuda_check(cudaMemcpyAsync(dev.data_ptr(), host.data(), n * sizeof(A2ARankArgs), cudaMemcpyHostToDevice, cur_stream()), "upload group args");
+  cuda_check(launch_a2a_push(nullptr, reinterpret_cast<const A2ARankArgs*>(dev.data_ptr()), n, ctas, threads, cur_stream()), "a2a_push group launch");
+  cuda_check(cudaStreamSynchronize(cur_stream()), "a2a_push group sync");  // args buffer must outlive the launch
+}
+
+}  // namespace
+
+void bind_moe(py::module_& m);  // defined in moe_bindings.cpp
+
+PYBIND11_MODULE(_C, m) {
+  m.doc() = "fast_b200 native runtime and sm_100a kernels";
+  m.attr("SIG_WORDS") = kSigWords;
+
+  py::class_<HeapPy>(m, "SymmHeap")
+      .def(py::init([](int rank, int world, int64_t bytes, int device) {
+        c10::cuda::CUDAGuard g(device);
+        return HeapPy{std::make_shared<SymmHeap>(rank, world, static_cast<size_t>(bytes)), device};
+      }))
+      .def_static("create_local_group", [](int world, int64_t bytes, int device) {
+        c10::cuda::CUDAGuard g(device);
+        std::vector<HeapPy> out;
+        for (SymmHeap* h : SymmHeap::create_local_group(world, static_cast<size_t>(bytes))) out.push_back(HeapPy{std::shared_ptr<SymmHeap>(h), device});
+        return out;
+      })
+      .def("ipc_handle", [](const HeapPy& h) { return py::bytes(h.h->ipc_handle()); })
+      .def("open_peers", [](HeapPy& h, std::vector<std::string> handles) { c10::cuda::CUDAGuard g(h.device); h.h->open_peers(handles); })
+      .def("alloc", [](HeapPy& h, int64_t bytes) { return static_cast<int64_t>(h.h->alloc(static_cast<size_t>(bytes))); })
+      .def("free", [](HeapPy& h, int64_t off) { h.h->free(static_cast<size_t>(off)); })
+      .def("tensor", &HeapPy::tensor)
+      .def("base_ptr", [](const HeapPy& h, int r) { return reinterpret_cast<int64_t>(h.h->peer_base(r)); })
+      .def("table_ptr", [](const HeapPy& h) { return reinterpret_cast<int64_t>(h.h->device_peer_table()); })
+      .def_property_readonly("rank", [](const HeapPy& h) { return h.h->rank(); })
+      .def_property_readonly("world", [](const HeapPy& h) { return h.h->world(); })
+      .def_property_readonly("bytes", [](const HeapPy& h) { return static_cast<int64_t>(h.h->bytes()); })
+      .def_property_readonly("in_use", [](const HeapPy& h) { return static_cast<int64_t>(h.h->in_use()); });
+
+  py::class_<StatusPy>(m, "StatusBlock")
+      .def(py::init<>())
+      .def("read", &StatusPy::read)
+      .def("clear", &StatusPy::clear)
+      .def("ptr", [](const StatusPy& s) { return reinterpret_cast<int64_t>(s.d); });
+
+  py::class_<A2AProgramPy>(m, "A2AProgram")
+      .def(py::init<torch::Tensor, std::vector<int64_t>, int64_t, int64_t, int>())
+      .def_readonly("n_items", &A2AProgramPy::n_items)
+      .def_readonly("num_stages", &A2AProgramPy::num_stages)
+      .def_readonly("total_bytes", &A2AProgramPy::total_bytes);
+
+  m.def("a2a_launch", &a2a_launch);
+  m.def("a2a_launch_group", &a2a_launch_group);
+  m.def("wait_probe", [](int64_t flag_ptr, uint64_t want, const StatusPy& st, uint64_t timeout_ns) {
+    cuda_check(launch_wait_probe(reinterpret_cast<const unsigned long long*>(flag_ptr), want, st.d, timeout_ns, cur_stream()), "wait_probe");
+  });
+  bind_moe(m);
+}

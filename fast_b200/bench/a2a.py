@@ -1,0 +1,135 @@
+"""All-to-all(v) bandwidth bench: this runtime's staged and fan-out plans against NCCL.
+
+    torchrun --nproc-per-node N -m fast_b200.bench.a2a --mode uniform|skewed [--sizes ...]
+
+Device-timed with CUDA events on the launching stream, max over ranks, seeded matrices. The
+reference's counterpart is its perf loop (nvidia/alltoall_nvshmem.cpp:172-381) and the AMD
+tester's sweeps (amd/test_alltoall.cpp:1994-2596); algbw = bytes sent per rank / time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from .. import sched
+from ..parallel import Communicator
+from ..sched import PlanKind, Topology
+
+
+def _time_ms(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(iters):
+        fn()
+    ev[1].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev[0].elapsed_time(ev[1]) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def nccl_alltoallv(out, inp, in_splits, out_splits):
+    dist.all_to_all_single(out, inp, out_splits, in_splits)
+
+
+def nccl_sendrecv_group(out, inp, in_splits, out_splits, rank, world):
+    ops = []
+    io = np.concatenate([[0], np.cumsum(in_splits)])
+    oo = np.concatenate([[0], np.cumsum(out_splits)])
+    for step in range(world):
+        d = (rank + step) % world
+        s = (rank - step) % world
+        if in_splits[d]:
+            ops.append(dist.P2POp(dist.isend, inp[io[d]:io[d + 1]], d))
+        if out_splits[s]:
+            ops.append(dist.P2POp(dist.irecv, out[oo[s]:oo[s + 1]], s))
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+
+
+def run(args):
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group("nccl")
+    max_row = max(args.sizes)
+    comm = Communicator(heap_bytes=int(max_row * 2.5) + (64 << 20), topo=Topology.flat(world), ctas=args.ctas, threads=args.threads)
+    out = comm.alloc(int(max_row * 2.2), torch.uint8)
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    inp = torch.randn(max_row // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
+    nccl_out = torch.empty(int(max_row * 2.2), dtype=torch.uint8, device="cuda")
+    results = []
+    for size in args.sizes:
+        skews = args.skews if args.mode == "skewed" else [None]
+        for skew in skews:
+            acc = {}
+            nmat = args.matrices if args.mode == "skewed" else 1
+            for mi in range(nmat):
+                if args.mode == "uniform":
+                    per = max(size // world // 16 * 16, 16)
+                    m = np.full((world, world), per, dtype=np.int64)
+                else:
+                    m = sched.workload_zipf_rows(world, skew, size, 1000 * mi + 7, 16)
+                in_splits = [int(x) for x in m[rank]]
+                out_splits = [int(x) for x in m[:, rank]]
+                sent = int(m[rank].sum())
+                bound_bytes = int(max((m.sum(0) - np.diag(m)).max(), (m.sum(1) - np.diag(m)).max()))
+                iters = max(3, min(args.iters, int(2e9 // max(sent, 1))))
+                variants = {"nccl_alltoallv": lambda: nccl_alltoallv(nccl_out[: sum(out_splits)], inp[:sent], in_splits, out_splits)}
+                if args.sendrecv:
+                    variants["nccl_sendrecv"] = lambda: nccl_sendrecv_group(nccl_out, inp, in_splits, out_splits, rank, world)
+                for name, kind, opts in [("ours_fanout", PlanKind.FANOUT, {}), ("ours_staged", PlanKind.STAGED, {}),
+                                         ("ours_staged_bottleneck", PlanKind.STAGED, {"match": sched.MatchPolicy.BOTTLENECK}),
+                                         ("ours_spreadout", PlanKind.SPREAD_OUT, {})]:
+                    s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk, **opts)
+                    variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
+                for name, fn in variants.items():
+                    ms = _time_ms(fn, iters, args.warmup)
+                    acc.setdefault(name, []).append((ms, sent, bound_bytes))
+                comm.check()
+                if mi == 0 and args.verify:
+                    s = comm.schedule(m, unit_bytes=1, kind=PlanKind.STAGED, chunk_bytes=args.chunk)
+                    comm.all_to_all_v(out, inp, s)
+                    nccl_alltoallv(nccl_out[: sum(out_splits)], inp[:sent], in_splits, out_splits)
+                    torch.cuda.synchronize()
+                    assert torch.equal(out[: sum(out_splits)], nccl_out[: sum(out_splits)]), "mismatch vs NCCL"
+            row = {"mode": args.mode, "world": world, "row_bytes": size, "skew": skew, "matrices": nmat}
+            for name, xs in acc.items():
+                ms = float(np.mean([x[0] for x in xs]))
+                row[name] = {"ms": round(ms, 4), "algbw_GBps": round(float(np.mean([x[1] / x[0] / 1e6 for x in xs])), 2),
+                             "bound_frac_770": round(float(np.mean([x[2] / 770e9 / (x[0] * 1e-3) for x in xs])), 4)}
+            results.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    return results
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="skewed", choices=["uniform", "skewed"])
+    ap.add_argument("--sizes", type=int, nargs="+", default=[64 << 20])
+    ap.add_argument("--skews", type=float, nargs="+", default=[0.0, 0.5, 1.0, 1.5])
+    ap.add_argument("--matrices", type=int, default=4)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--ctas", type=int, default=64)
+    ap.add_argument("--threads", type=int, default=512)
+    ap.add_argument("--chunk", type=int, default=1 << 20)
+    ap.add_argument("--sendrecv", action="store_true")
+    ap.add_argument("--verify", action="store_true")
+    run(ap.parse_args())
+
+
+if __name__ == "__main__":
+    main()

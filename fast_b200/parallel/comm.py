@@ -1,0 +1,272 @@
+"""Communicator: symmetric memory, traffic-matrix scheduling and the all-to-all(v) entry points.
+
+API parity with the reference's framework-facing class (amd/flash.cpp:337-648): construct from
+(rank, world, topology); ``schedule(matrix, transpose)``; ``buffer_sizes()``; caller-owned or
+library-owned staging; ``all_to_all_v`` / ``all_to_all_single``; element-unit matrices with an
+element size; bf16 / fp8 payloads are just bytes here. The NVIDIA class of the reference only
+exposes self-tests (nvidia/alltoall_nvshmem.cpp:508-601); this one is a general collective.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import runtime, sched
+from ..sched import PlanKind, Topology
+
+
+@dataclass
+class Schedule:
+    """A plan lowered for one rank, with its device-resident work list."""
+
+    plan: "sched.Plan"
+    unit_bytes: int
+    program: object  # _C.A2AProgram
+    lowered: dict
+    rank: int
+
+    @property
+    def input_bytes(self) -> int:
+        return int(self.lowered["input_bytes"])
+
+    @property
+    def output_bytes(self) -> int:
+        return int(self.lowered["output_bytes"])
+
+    @property
+    def balance_bytes(self) -> int:
+        return int(self.lowered["balance_bytes"])
+
+    @property
+    def rail_bytes(self) -> int:
+        return int(self.lowered["rail_bytes"])
+
+    @property
+    def max_bytes(self) -> dict:
+        """Largest need of any rank per buffer: symmetric staging is sized by these so that every
+        rank allocates the same amounts in the same order."""
+        b = self.plan.buffers.max(axis=0) * self.unit_bytes
+        return {"input": int(b[0]), "output": int(b[1]), "balance": int(b[2]), "rail": int(b[3])}
+
+    def buffer_sizes(self) -> dict:
+        """Bytes of each buffer this rank needs (the reference's get_buffer_szs, amd/flash.cpp:385-397)."""
+        return {"input": self.input_bytes, "output": self.output_bytes, "balance": self.balance_bytes, "rail": self.rail_bytes}
+
+
+class Communicator:
+    """One rank of an all-to-all domain. Use ``Communicator(group)`` with one process per GPU, or
+    ``LocalGroup`` for several virtual ranks on a single GPU (tests, single-GPU runs)."""
+
+    def __init__(self, group=None, heap_bytes: int = 1 << 30, topo: Optional[Topology] = None, device=None,
+                 timeout_s: float = 5.0, ctas: int = 64, threads: int = 512, _heap=None, _rank=None, _world=None):
+        import torch.distributed as dist
+
+        self._C = runtime.ext()
+        if _heap is not None:
+            self.rank, self.world, self.heap = _rank, _world, _heap
+            self.device = torch.device("cuda", device if device is not None else torch.cuda.current_device())
+            self.group = None
+        else:
+            self.group = group
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+            self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.device = torch.device("cuda", device if device is not None else torch.cuda.current_device())
+            self.heap = self._C.SymmHeap(self.rank, self.world, int(heap_bytes), self.device.index)
+            if self.world > 1:
+                handles: List[Optional[bytes]] = [None] * self.world
+                dist.all_gather_object(handles, self.heap.ipc_handle(), group=group)
+                self.heap.open_peers(handles)
+                dist.barrier(group=group)
+        self.topo = topo or Topology.flat(self.world)
+        if self.topo.ranks != self.world:
+            raise ValueError("topology does not match the world size")
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.ctas, self.threads = ctas, threads
+        self.status = self._C.StatusBlock()
+        self.sig_off = self.heap.alloc(self._C.SIG_WORDS * 8)
+        self.epoch = 0
+        self.broken = False
+        self.plan_cache = sched.PlanCache()
+        self._staging = {}  # name -> (offset, bytes)
+        self._sched_cache = {}
+
+    # ---- symmetric memory ---------------------------------------------------------------------
+    def alloc(self, shape, dtype=torch.uint8) -> torch.Tensor:
+        """A tensor inside the symmetric heap; all ranks must allocate in the same order."""
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        nbytes = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        off = self.heap.alloc(max(nbytes, 1))
+        t = self.heap.tensor(off, list(shape), dtype)
+        t._symm_off = off
+        return t
+
+    def free(self, t: torch.Tensor) -> None:
+        self.heap.free(t._symm_off)
+
+    def offset_of(self, t: torch.Tensor) -> Optional[int]:
+        base = self.heap.base_ptr(self.rank)
+        p = t.data_ptr()
+        return p - base if base <= p and p + t.numel() * t.element_size() <= base + self.heap.bytes else None
+
+    def _stage(self, name: str, nbytes: int) -> int:
+        cur = self._staging.get(name)
+        if cur is None or cur[1] < nbytes:
+            if cur is not None:
+                self.heap.free(cur[0])
+            grown = max(nbytes, 256)
+            self._staging[name] = (self.heap.alloc(grown), grown)
+        return self._staging[name][0]
+
+    # ---- scheduling -----------------------------------------------------------------------------
+    def schedule(self, matrix, unit_bytes: int = 1, transpose: bool = False, kind=PlanKind.STAGED, chunk_bytes: int = 1 << 20,
+                 **plan_opts) -> Schedule:
+        """Plan the collective for ``matrix`` (units; ``matrix[i, j]`` = rank i -> rank j).
+
+        Every rank must pass the same matrix. Staged plans are built with pieces cut on 16-byte
+        boundaries whenever the unit size allows it.
+        """
+        m = np.ascontiguousarray(matrix, dtype=np.int64)
+        if "split_align" not in plan_opts:
+            plan_opts["split_align"] = max(1, 16 // np.gcd(16, unit_bytes))
+        key = (sched.matrix_hash(m), unit_bytes, transpose, str(kind), chunk_bytes, tuple(sorted((k, str(v)) for k, v in plan_opts.items())))
+        s = self._sched_cache.get(key)
+        if s is None:
+            plan = self.plan_cache.get(m, self.topo, kind=kind, transpose=transpose, **plan_opts)
+            err = plan.validate()
+            if err:
+                raise RuntimeError(f"scheduler produced an invalid plan: {err}")
+            low = plan.lower(self.rank, unit_bytes, chunk_bytes)
+            prog = self._C.A2AProgram(torch.from_numpy(low["items"]), [int(x) for x in low["expect_rail_bytes"]],
+                                      int(low["expect_output_bytes"]), int(low["expect_balance_bytes"]), self.device.index)
+            s = Schedule(plan, unit_bytes, prog, low, self.rank)
+            if len(self._sched_cache) > 512:
+                self._sched_cache.pop(next(iter(self._sched_cache)))
+            self._sched_cache[key] = s
+        return s
+
+    # ---- execution --------------------------------------------------------------------------------
+    def _launch_args(self, s: Schedule, output: torch.Tensor, input: torch.Tensor):
+        if self.broken:
+            raise RuntimeError("communicator saw a failed collective; call reset() on every rank first")
+        if input.numel() * input.element_size() < s.input_bytes:
+            raise ValueError("input smaller than the schedule needs")
+        if output.numel() * output.element_size() < s.output_bytes:
+            raise ValueError("output smaller than the schedule needs")
+        out_off = self.offset_of(output)
+        copy_back = None
+        if out_off is None:  # library-owned receive staging, copied out afterwards
+            out_off = self._stage("recv", s.max_bytes["output"])
+            copy_back = self.heap.tensor(out_off, [s.output_bytes], torch.uint8)
+        bal_off = self._stage("balance", s.max_bytes["balance"])
+        rail_off = self._stage("rail", s.max_bytes["rail"])
+        base = self.heap.base_ptr(self.rank)
+        src = [input.data_ptr(), 0, base + bal_off, base + rail_off]
+        dst = [0, out_off, bal_off, rail_off]
+        return src, dst, copy_back
+
+    def all_to_all_v(self, output: torch.Tensor, input: torch.Tensor, s: Schedule) -> torch.Tensor:
+        """Run a scheduled all-to-all(v) on the current stream. ``input`` holds the segments for
+        rank 0..n-1 back to back; ``output`` receives the segments from rank 0..n-1 back to back.
+        ``output`` in the symmetric heap (``alloc``) is written in place by the peers; any other
+        tensor goes through a library-owned receive buffer and one extra local copy."""
+        src, dst, copy_back = self._launch_args(s, output, input)
+        self.epoch += 1
+        self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, self.ctas, self.threads)
+        if copy_back is not None:
+            output.view(torch.uint8).reshape(-1)[: s.output_bytes].copy_(copy_back[: s.output_bytes])
+        return output
+
+    def all_to_all_single(self, output: torch.Tensor, input: torch.Tensor, output_split_sizes: Optional[Sequence[int]] = None,
+                          input_split_sizes: Optional[Sequence[int]] = None, matrix=None, kind=PlanKind.FANOUT) -> torch.Tensor:
+        """``torch.distributed.all_to_all_single`` semantics (splits count rows of dim 0)."""
+        import torch.distributed as dist
+
+        row_bytes = input.element_size() * int(np.prod(input.shape[1:])) if input.dim() > 1 else input.element_size()
+        if matrix is None:
+            if input_split_sizes is None:
+                per = input.shape[0] // self.world
+                matrix = np.full((self.world, self.world), per, dtype=np.int64)
+            else:
+                mine = torch.tensor(list(input_split_sizes), dtype=torch.int64)
+                rows = [torch.empty_like(mine) for _ in range(self.world)]
+                if self.world > 1:
+                    backend_dev = self.device if dist.get_backend(self.group) == "nccl" else torch.device("cpu")
+                    g = [r.to(backend_dev) for r in rows]
+                    dist.all_gather(g, mine.to(backend_dev), group=self.group)
+                    rows = [r.cpu() for r in g]
+                else:
+                    rows = [mine]
+                matrix = torch.stack(rows).numpy()
+        s = self.schedule(matrix, unit_bytes=row_bytes, kind=kind)
+        return self.all_to_all_v(output, input, s)
+
+    # ---- health -------------------------------------------------------------------------------------
+    def check(self) -> None:
+        """Synchronise the stream and raise ``CollectiveTimeout`` if a device wait gave up."""
+        code, site, detail, seen, want = self.status.read()
+        if code != 0:
+            self.broken = True
+            raise runtime.CollectiveTimeout(code, site, detail, seen, want)
+
+    def reset(self) -> None:
+        """After a failed collective: clear status and signal words (collective over the group)."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.device)
+        if self.group is not None or (dist.is_initialized() and self.world > 1):
+            dist.barrier(group=self.group)
+        self.heap.tensor(self.sig_off, [self._C.SIG_WORDS], torch.int64).zero_()
+        self.status.clear()
+        self.epoch = 0
+        torch.cuda.synchronize(self.device)
+        if self.group is not None or (dist.is_initialized() and self.world > 1):
+            dist.barrier(group=self.group)
+        self.broken = False
+
+
+class LocalGroup:
+    """``world`` virtual ranks on one GPU, executed by ONE cooperative launch per collective.
+
+    Kernels of different ranks wait on one another, so they may never run as separate launches on
+    one device; the group launch puts every rank's CTAs in the same grid. Used by the single-GPU
+    tests and by single-GPU runs of multi-rank plans.
+    """
+
+    def __init__(self, world: int, heap_bytes: int = 256 << 20, topo: Optional[Topology] = None, device: int = 0,
+                 timeout_s: float = 5.0, ctas: int = 8, threads: int = 256):
+        C = runtime.ext()
+        self._C = C
+        heaps = C.SymmHeap.create_local_group(world, int(heap_bytes), device)
+        self.comms = [Communicator(heap_bytes=heap_bytes, topo=topo, device=device, timeout_s=timeout_s, ctas=ctas, threads=threads,
+                                   _heap=h, _rank=r, _world=world) for r, h in enumerate(heaps)]
+        self.world, self.ctas, self.threads = world, ctas, threads
+
+    def schedule(self, matrix, **kw) -> List[Schedule]:
+        return [c.schedule(matrix, **kw) for c in self.comms]
+
+    def all_to_all_v(self, outputs, inputs, scheds) -> None:
+        srcs, cbs = [], []
+        dst0 = None
+        for c, o, i, s in zip(self.comms, outputs, inputs, scheds):
+            src, dst, cb = c._launch_args(s, o, i)
+            if dst0 is None:
+                dst0 = dst
+            elif dst != dst0:
+                raise RuntimeError("virtual ranks disagree on symmetric offsets; allocate in the same order on every rank")
+            srcs.append(src)
+            cbs.append(cb)
+        c0 = self.comms[0]
+        for c in self.comms:
+            c.epoch += 1
+        self._C.a2a_launch_group([s.program for s in scheds], [c.heap for c in self.comms], srcs, dst0, c0.sig_off, c0.epoch,
+                                 [c.status for c in self.comms], c0.timeout_ns, self.ctas, self.threads)
+        for o, cb, s in zip(outputs, cbs, scheds):
+            if cb is not None:
+                o.view(torch.uint8).reshape(-1)[: s.output_bytes].copy_(cb[: s.output_bytes])
+
+    def check(self) -> None:
+        for c in self.comms:
+            c.check()

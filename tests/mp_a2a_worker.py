@@ -1,0 +1,56 @@
+"""Child of test_multi_process_bit_exact: one process per GPU, real peer memory."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from fast_b200 import sched  # noqa: E402
+from fast_b200.parallel import Communicator  # noqa: E402
+from fast_b200.sched import PlanKind, Topology  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl")
+    topos = [Topology.flat(world)] + ([Topology(2, world // 2)] if world % 2 == 0 and world >= 4 else [])
+    for topo in topos:
+        comm = Communicator(heap_bytes=256 << 20, topo=topo, ctas=16, threads=512)
+        out = comm.alloc(32 << 20, torch.uint8)
+        for kind in (PlanKind.STAGED, PlanKind.FANOUT, PlanKind.SPREAD_OUT, PlanKind.SINGLE_BURST):
+            for seed in range(3):
+                m = sched.workload_zipf_rows(world, 1.0, 4 << 20, seed, 16)
+                s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=256 << 10)
+                ind = np.concatenate([[0], np.cumsum(m[rank])])
+                inp = np.concatenate([((rank << 24) | (d << 16) | (np.arange(int(m[rank, d]) // 4) & 0xFFFF)).astype(np.int32) for d in range(world)])
+                d_in = torch.from_numpy(inp).cuda()
+                out.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                for _ in range(2):
+                    comm.all_to_all_v(out, d_in, s)
+                comm.check()
+                want = np.concatenate([((src << 24) | (rank << 16) | (np.arange(int(m[src, rank]) // 4) & 0xFFFF)).astype(np.int32) for src in range(world)])
+                got = out[: want.size * 4].view(torch.int32).cpu().numpy()
+                assert np.array_equal(got, want), f"rank {rank} kind {kind} seed {seed} topo {topo}"
+        # torch.distributed-style entry point with uneven row splits
+        rows = [(rank + d) % 3 + 1 for d in range(world)]
+        x = torch.full((sum(rows), 8), float(rank), device="cuda", dtype=torch.bfloat16)
+        recv_rows = [(s + rank) % 3 + 1 for s in range(world)]
+        y = torch.empty((sum(recv_rows), 8), device="cuda", dtype=torch.bfloat16)
+        comm.all_to_all_single(y, x, recv_rows, rows)
+        comm.check()
+        ref = torch.cat([torch.full((recv_rows[s], 8), float(s), dtype=torch.bfloat16) for s in range(world)])
+        assert torch.equal(y.cpu(), ref)
+        comm.free(out)
+        dist.barrier()
+    if rank == 0:
+        print("A2A_MP_OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

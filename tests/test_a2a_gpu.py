@@ -1,0 +1,131 @@
+"""GPU tests of the all-to-all(v) executor: bit-exact against the host replay of the same plan.
+
+Pattern words follow the reference's verification scheme (src << 24 | dst << 16 | index,
+nvidia/src/fast_alltoall/flash_alltoall_nvshmem.cu:1445-1473).
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from fast_b200 import sched
+from fast_b200.sched import PlanKind, Topology
+
+pytestmark = pytest.mark.gpu
+
+
+def _pattern_inputs(m, unit_words):
+    n = m.shape[0]
+    ins = []
+    for r in range(n):
+        segs = []
+        for d in range(n):
+            k = int(m[r, d]) * unit_words
+            segs.append(((r << 24) | (d << 16) | (np.arange(k) & 0xFFFF)).astype(np.int32))
+        ins.append(np.concatenate(segs) if segs else np.zeros(0, np.int32))
+    return ins
+
+
+def _expected_outputs(m, ins, unit_words):
+    n = m.shape[0]
+    ind = np.concatenate([np.zeros((n, 1), np.int64), np.cumsum(m, 1)], 1) * unit_words
+    outs = []
+    for d in range(n):
+        outs.append(np.concatenate([ins[s][ind[s, d]:ind[s, d + 1]] for s in range(n)]))
+    return outs
+
+
+@pytest.mark.parametrize("servers,gpus", [(1, 1), (2, 1), (4, 1), (8, 1), (2, 2), (2, 4), (1, 4)])
+@pytest.mark.parametrize("kind", [PlanKind.STAGED, PlanKind.FANOUT, PlanKind.SPREAD_OUT, PlanKind.SINGLE_BURST])
+def test_local_group_bit_exact(servers, gpus, kind):
+    from fast_b200.parallel import LocalGroup
+
+    n = servers * gpus
+    grp = LocalGroup(n, heap_bytes=64 << 20, topo=Topology(servers, gpus), ctas=4, threads=256)
+    for seed, unit_words in [(1, 4), (2, 1), (3, 64)]:
+        m = sched.workload_uniform(n, 300, seed + n, zero_diag=False)
+        ss = grp.schedule(m, unit_bytes=4 * unit_words, kind=kind, chunk_bytes=8192)
+        ins = _pattern_inputs(m, unit_words)
+        want = _expected_outputs(m, ins, unit_words)
+        d_in = [torch.from_numpy(x).cuda() for x in ins]
+        mx = max(s.max_bytes["output"] for s in ss) // 4
+        d_out = [c.alloc(mx, torch.int32) for c in grp.comms]
+        for o in d_out:
+            o.fill_(-1)
+        for _ in range(2):  # twice: counters must be clean for the next epoch
+            grp.all_to_all_v(d_out, d_in, ss)
+            grp.check()
+            for r in range(n):
+                got = d_out[r][: want[r].size].cpu().numpy()
+                assert np.array_equal(got, want[r]), f"rank {r} differs"
+        for c, o in zip(grp.comms, d_out):
+            c.free(o)
+
+
+def test_unaligned_byte_units():
+    from fast_b200.parallel import LocalGroup
+
+    n = 4
+    grp = LocalGroup(n, heap_bytes=16 << 20, ctas=2, threads=128)
+    rng = np.random.default_rng(0)
+    m = np.array([[0, 1, 15, 17], [33, 0, 16, 5], [7, 1000, 3, 0], [129, 2, 0, 31]], dtype=np.int64)
+    ss = grp.schedule(m, unit_bytes=1, kind=PlanKind.STAGED, chunk_bytes=64)
+    ins = [rng.integers(0, 256, int(m[r].sum()), dtype=np.uint8) for r in range(n)]
+    d_in = [torch.from_numpy(x).cuda() for x in ins]
+    d_out = [torch.zeros(int(m[:, r].sum()) + 16, dtype=torch.uint8, device="cuda") for r in range(n)]  # library-owned staging path
+    grp.all_to_all_v(d_out, d_in, ss)
+    grp.check()
+    host_out = [np.zeros(int(m[:, r].sum()), np.uint8) for r in range(n)]
+    ss[0].plan.execute_on_host(1, ins, host_out)
+    for r in range(n):
+        assert np.array_equal(d_out[r][: host_out[r].size].cpu().numpy(), host_out[r])
+
+
+def test_bounded_wait_reports_timeout():
+    """A wait on a flag nobody sets must end by itself and leave a readable status."""
+    from fast_b200 import runtime
+
+    C = runtime.ext()
+    st = C.StatusBlock()
+    flag = torch.zeros(1, dtype=torch.int64, device="cuda")
+    C.wait_probe(flag.data_ptr(), 1, st, 50_000_000)  # 50 ms
+    code, site, detail, seen, want = st.read()
+    assert (code, site, seen, want) == (1, 9, 0, 1)
+    # the context stays usable
+    assert int((torch.ones(4, device="cuda") * 2).sum().item()) == 8
+    st.clear()
+    flag.fill_(1)
+    C.wait_probe(flag.data_ptr(), 1, st, 50_000_000)
+    assert st.read()[0] == 0
+
+
+def test_missing_peer_times_out_cleanly():
+    """Rank 1 of a 2-rank group never publishes its epoch: rank 0's push must give up, not hang."""
+    from fast_b200 import runtime
+    from fast_b200.parallel import LocalGroup
+
+    grp = LocalGroup(2, heap_bytes=8 << 20, timeout_s=0.05, ctas=1, threads=64)
+    m = np.array([[0, 64], [64, 0]], dtype=np.int64)
+    c0 = grp.comms[0]
+    s0 = c0.schedule(m, unit_bytes=16, kind=PlanKind.FANOUT)
+    out = c0.alloc(64 * 16, torch.uint8)
+    grp.comms[1].alloc(64 * 16, torch.uint8)
+    inp = torch.zeros(64 * 16, dtype=torch.uint8, device="cuda")
+    c0.all_to_all_v(out, inp, s0)  # alone: the peer never enters
+    with pytest.raises(runtime.CollectiveTimeout) as e:
+        c0.check()
+    assert e.value.site == 1 and e.value.detail == 1
+    assert c0.broken
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_multi_process_bit_exact():
+    n = min(torch.cuda.device_count(), 8)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29533", os.path.join(os.path.dirname(__file__), "mp_a2a_worker.py")], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "A2A_MP_OK" in r.stdout
