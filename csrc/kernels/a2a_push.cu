@@ -115,7 +115,8 @@ __global__ void wait_probe_kernel(const unsigned long long* flag, unsigned long 
 cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* device_args, int virtual_ranks, int ctas, int threads,
                             cudaStream_t stream) {
   if (ctas < 1 || threads < 32 || threads > 1024 || virtual_ranks < 1) return cudaErrorInvalidValue;
-  if (virtual_ranks == 1) {
+  if (device_args == nullptr) {
+    if (host_args == nullptr || virtual_ranks != 1) return cudaErrorInvalidValue;
     a2a_push_kernel<<<ctas, threads, 0, stream>>>(*host_args);
     return cudaGetLastError();
   }

@@ -1,0 +1,96 @@
+"""Grouped bf16 GEMMs of the expert MLP on the tcgen05 kernel (forward, dgrad, wgrad).
+
+Rows of all groups live in one matrix; ``group_off`` (int32[G+1], device) gives each group's row
+range and every offset is a multiple of 128, so tiles never straddle two groups and the rows
+between a group's real end and its padded end are zero.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import runtime
+
+FORWARD, DGRAD, WGRAD = 0, 1, 2
+STORE, SWIGLU = 0, 1
+_BM, _BN, _BK = 128, 256, 64
+
+_status = None
+_maps: dict = {}
+
+
+def _st():
+    global _status
+    if _status is None:
+        _status = runtime.ext().StatusBlock()
+    return _status
+
+
+def check() -> None:
+    """Raise if a GEMM launched through this module gave up on an mbarrier wait."""
+    code, site, detail, seen, want = _st().read()
+    if code:
+        raise runtime.CollectiveTimeout(code, site, detail, seen, want)
+
+
+def _tmap(t: torch.Tensor, box_rows: int):
+    assert t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+    m = _maps.get(key)
+    if m is None:
+        if len(_maps) > 4096:
+            _maps.clear()
+        m = runtime.ext().TensorMap2D(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), 64, box_rows)
+        _maps[key] = m
+    return m
+
+
+def _ctas() -> int:
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+
+
+def pad_group_offsets(counts: torch.Tensor) -> torch.Tensor:
+    """int32[G+1] offsets with every group rounded up to 128 rows (host/torch helper for tests)."""
+    padded = (counts.to(torch.int64) + 127) // 128 * 128
+    off = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=counts.device)
+    off[1:] = torch.cumsum(padded, 0)
+    return off.to(torch.int32)
+
+
+def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
+                     gate_up_out: Optional[torch.Tensor] = None, timeout_s: float = 5.0) -> torch.Tensor:
+    """out[rows of g] = a[rows of g] @ w[g].T  (a [R, K], w [G, N, K], out [R, N]).
+
+    With ``swiglu`` the N columns of every 256-wide tile are [128 gate | 128 up] of the same 128
+    features and ``out`` is [R, N/2] = silu(gate) * up; ``gate_up_out`` ([R, N]) optionally keeps
+    the raw tile for the backward pass.
+    """
+    G, N, K = w.shape
+    assert a.shape[1] == K and K % _BK == 0 and N % _BN == 0 and a.shape[0] % _BM == 0
+    assert out.shape[0] == a.shape[0] and out.shape[1] == (N // 2 if swiglu else N)
+    C = runtime.ext()
+    C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), _BN), group_off, N // _BN, 0, K, N, 0, out,
+                   gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas())
+    return out
+
+
+def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, timeout_s: float = 5.0) -> torch.Tensor:
+    """out[rows of g] = dy[rows of g] @ w[g]  (dy [R, N], w [G, N, K], out [R, K])."""
+    G, N, K = w.shape
+    assert dy.shape[1] == N and N % _BK == 0 and K % _BN == 0 and dy.shape[0] % _BM == 0
+    C = runtime.ext()
+    C.grouped_gemm(DGRAD, STORE, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, None, _st().ptr(),
+                   int(timeout_s * 1e9), _ctas())
+    return out
+
+
+def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, timeout_s: float = 5.0) -> torch.Tensor:
+    """out[g] = dy[rows of g].T @ x[rows of g]  (dy [R, N], x [R, K], out [G, N, K]). Rows between a
+    group's real end and its padded end must be zero in at least one operand and finite in both."""
+    G, N, K = out.shape
+    assert dy.shape[1] == N and x.shape[1] == K and N % _BM == 0 and K % _BN == 0
+    C = runtime.ext()
+    C.grouped_gemm(WGRAD, STORE, _tmap(dy, _BK), _tmap(x, _BK), group_off, K // _BN, N // _BM, 0, 0, N, out.view(G * N, K), None, _st().ptr(),
+                   int(timeout_s * 1e9), _ctas())
+    return out

@@ -1,0 +1,101 @@
+"""tcgen05 grouped GEMM against a plain PyTorch fp32 reference of the same contraction."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(G, N, K, counts, seed=0):
+    from fast_b200.ops import pad_group_offsets
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    counts = torch.tensor(counts, device="cuda")
+    off = pad_group_offsets(counts)
+    R = int(off[-1].item())
+    a = torch.zeros(R, K, device="cuda", dtype=torch.bfloat16)
+    for i in range(G):
+        s, c = int(off[i]), int(counts[i])
+        a[s:s + c] = torch.randn(c, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(G, N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    return counts, off, R, a, w
+
+
+def _close(got, want, tol=2e-2):
+    err = (got.float() - want).abs().max().item()
+    scale = want.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("G,N,K,counts", [(1, 256, 64, [128]), (1, 256, 256, [128]), (2, 512, 320, [200, 77]), (4, 768, 512, [0, 300, 128, 1])])
+def test_forward(G, N, K, counts):
+    from fast_b200.ops import gemm
+
+    counts, off, R, a, w = _setup(G, N, K, counts)
+    out = torch.full((R, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_fwd(a, w, off, out)
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        _close(out[s:e], a[s:e].float() @ w[i].float().T)
+
+
+def test_forward_swiglu():
+    from fast_b200.ops import gemm
+
+    G, N, K = 2, 512, 256
+    counts, off, R, a, w = _setup(G, N, K, [130, 256], seed=3)
+    act = torch.empty(R, N // 2, device="cuda", dtype=torch.bfloat16)
+    gu = torch.empty(R, N, device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_fwd(a, w, off, act, swiglu=True, gate_up_out=gu)
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        full = a[s:e].float() @ w[i].float().T
+        _close(gu[s:e], full)
+        t = full.view(e - s, N // 256, 2, 128)
+        _close(act[s:e], (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(e - s, N // 2))
+
+
+@pytest.mark.parametrize("G,N,K,counts", [(1, 64, 256, [128]), (2, 320, 512, [200, 77]), (3, 512, 768, [1, 0, 257])])
+def test_dgrad(G, N, K, counts):
+    from fast_b200.ops import gemm
+
+    counts, off, R, dy, w = _setup(G, K, N, counts, seed=5)  # dy [R, N]; w [G, N, K]
+    w = w.transpose(1, 2).contiguous()  # [G, N, K]
+    out = torch.full((R, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_dgrad(dy, w, off, out)
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        _close(out[s:e], dy[s:e].float() @ w[i].float())
+
+
+@pytest.mark.parametrize("G,N,K,counts", [(1, 128, 256, [128]), (2, 256, 512, [200, 77]), (3, 384, 256, [1, 0, 257])])
+def test_wgrad(G, N, K, counts):
+    from fast_b200.ops import gemm
+
+    counts, off, R, x, _ = _setup(G, 256, K, counts, seed=7)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    dy = torch.zeros(R, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(G):
+        s, c = int(off[i]), int(counts[i])
+        dy[s:s + c] = torch.randn(c, N, generator=g, device="cuda").to(torch.bfloat16)
+    out = torch.full((G, N, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_wgrad(dy, x, off, out)
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        _close(out[i], dy[s:e].float().T @ x[s:e].float())
+
+
+def test_large_shape_matches():
+    from fast_b200.ops import gemm
+
+    G, N, K = 2, 2048, 1024
+    counts, off, R, a, w = _setup(G, N, K, [1500, 900], seed=9)
+    out = torch.empty(R, N, device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_fwd(a, w, off, out)
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        _close(out[s:e], a[s:e].float() @ w[i].float().T)
