@@ -112,22 +112,29 @@ __global__ void wait_probe_kernel(const unsigned long long* flag, unsigned long 
 
 }  // namespace
 
+namespace { unsigned long long g_launches = 0; }
+unsigned long long launch_count() { return g_launches; }
+void note_launch(int n) { g_launches += static_cast<unsigned long long>(n); }
+
 cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* device_args, int virtual_ranks, int ctas, int threads,
                             cudaStream_t stream) {
   if (ctas < 1 || threads < 32 || threads > 1024 || virtual_ranks < 1) return cudaErrorInvalidValue;
   if (device_args == nullptr) {
     if (host_args == nullptr || virtual_ranks != 1) return cudaErrorInvalidValue;
     a2a_push_kernel<<<ctas, threads, 0, stream>>>(*host_args);
-    return cudaGetLastError();
+    note_launch();
+  return cudaGetLastError();
   }
   // All virtual ranks wait on one another, so they must be co-resident: cooperative launch.
   void* params[] = {const_cast<A2ARankArgs**>(&device_args)};
+  note_launch();
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(a2a_push_group_kernel), dim3(ctas, virtual_ranks), dim3(threads), params, 0, stream);
 }
 
 cudaError_t launch_wait_probe(const unsigned long long* flag, unsigned long long want, DeviceStatus* status,
                               unsigned long long timeout_ns, cudaStream_t stream) {
   wait_probe_kernel<<<1, 32, 0, stream>>>(flag, want, status, timeout_ns);
+  note_launch();
   return cudaGetLastError();
 }
 

@@ -10,6 +10,10 @@
 
 namespace fastb {
 
+// Number of kernels this library has launched in this process (for bench accounting).
+unsigned long long launch_count();
+void note_launch(int n = 1);
+
 // ---------------------------------------------------------------------------------------------
 // a2a_push: executes one rank's work list of a staged / fan-out all-to-all(v) plan.
 // ---------------------------------------------------------------------------------------------
@@ -73,6 +77,10 @@ struct GemmArgs {
   long long ldc2;
   DeviceStatus* status;
   unsigned long long timeout_ns;
+  // Optional arrival gate: before the first load of group g the TMA producer waits until
+  // gate_counter[g] >= gate_target[g] (rows pushed by peers have landed). Null = no gate.
+  const unsigned long long* gate_counter;
+  const unsigned long long* gate_target;
 };
 
 int grouped_gemm_smem_bytes();
@@ -80,5 +88,91 @@ int grouped_gemm_smem_bytes();
 // dgrad A {64,128} B {64,64}; wgrad A {64,64} B {64,64}  ({inner, outer} elements).
 cudaError_t launch_grouped_gemm(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
                                 int ctas, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// MoE routing / dispatch / combine
+// ---------------------------------------------------------------------------------------------
+cudaError_t launch_route_topk(const float* logits, const float* bias, int T, int E, int K, int* topk_idx, float* topk_w, int* slot_in_block,
+                              int* block_cnt, cudaStream_t stream);
+constexpr int kRouteTokensPerBlock = 128;  // tokens per routing block (block_cnt / block_base granularity)
+
+struct SplitsArgs {
+  void* const* peer_table;
+  int rank, world, num_experts, num_blocks, num_channels;
+  long long counts_heap_off;   // int [world][E] on every rank
+  long long flags_heap_off;    // u64 [world] on every rank: epoch of the last counts row received from each rank
+  unsigned long long epoch;
+  const int* block_cnt;        // [num_blocks][E]
+  int* block_base;             // [num_blocks][E] out
+  int* send_base;              // [E] out: destination row of my first token for expert e
+  int* send_cnt;               // [E] out: tokens I send to expert e
+  int* group_off;              // [E/world + 1] out: padded row offsets of my experts
+  int* group_rows;             // [E/world] out: real rows of my experts
+  unsigned long long* arrive_target;  // [num_channels][E/world] in/out: cumulative rows expected
+  int* traffic_matrix;         // [world][world] out (tokens), may be null
+  DeviceStatus* status;
+  unsigned long long timeout_ns;
+};
+cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream);
+cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* group_off, const int* group_rows, int groups, cudaStream_t stream);
+
+struct DispatchArgs {
+  void* const* peer_table;
+  int rank, world, num_experts, T, K, H;
+  const __nv_bfloat16* x;      // [T, H]
+  const int* topk_idx;         // [T, K]
+  const float* row_scale;      // [T, K] or null: scale applied to the row sent for slot j
+  const int* slot_in_block;    // [T, K]
+  const int* block_base;       // [blocks][E]
+  const int* send_base;        // [E]
+  int* dest_row;               // [T, K]: written when compute_rows != 0, else read
+  int compute_rows;
+  int fp8;                     // 1: send e4m3 bytes + one fp32 scale per 128 elements
+  long long recv_heap_off;     // destination rows: bf16 [cap, H] (or u8 [cap, H] when fp8)
+  long long scale_heap_off;    // fp8 only: float [cap, H/128]
+  long long arrive_heap_off;   // u64 [E/world] arrival counters of this channel
+  long long entry_flags_heap_off;  // u64 [world]; used when entry_epoch != 0
+  unsigned long long entry_epoch;
+  DeviceStatus* status;
+  unsigned long long timeout_ns;
+};
+cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t stream);
+
+struct CombineArgs {
+  void* const* peer_table;
+  int rank, world, num_experts, T, K, H;
+  const int* topk_idx;         // [T, K]
+  const int* dest_row;         // [T, K]
+  const float* weights;        // [T, K] or null (= 1)
+  long long src_heap_off;      // bf16 [cap, H] on every rank
+  long long ready_flags_heap_off;  // u64 [world] in my slab: peer d's rows are final once flags[d] >= ready_epoch
+  unsigned long long ready_epoch;
+  __nv_bfloat16* out;          // [T, H] sum_j w * row_j (null in dot mode)
+  const __nv_bfloat16* dot_with;  // dot mode: [T, H]
+  float* dot_out;              // dot mode: [T, K] = <dot_with[t], row_j>
+  DeviceStatus* status;
+  unsigned long long timeout_ns;
+};
+cudaError_t launch_combine_pull(const CombineArgs& a, int ctas, cudaStream_t stream);
+
+// Writes `epoch` (release, system scope) into slot `rank` of the flag array of every rank.
+cudaError_t launch_peer_signal(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch, cudaStream_t stream);
+// Bounded wait until counter[i] >= target[i] for all i < n (one thread each).
+cudaError_t launch_wait_counters(const unsigned long long* counter, const unsigned long long* target, int n, DeviceStatus* status,
+                                 unsigned long long timeout_ns, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// element-wise
+// ---------------------------------------------------------------------------------------------
+// gate_up: [rows, 2I] in tiles of [128 gate | 128 up]; act: [rows, I].
+cudaError_t launch_swiglu_fwd(const __nv_bfloat16* gate_up, __nv_bfloat16* act, long long rows, int inter, cudaStream_t stream);
+// d_gate_up = d(silu(g) * u) given d_act. rows_dev (optional, device) caps the rows processed.
+cudaError_t launch_swiglu_bwd(const __nv_bfloat16* gate_up, const __nv_bfloat16* d_act, __nv_bfloat16* d_gate_up, long long rows, int inter,
+                              const int* rows_dev, cudaStream_t stream);
+// Dequantises e4m3 rows with one fp32 scale per 128 elements to bf16.
+cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, cudaStream_t stream);
+// AdamW on bf16 parameters with fp32 master weights and moments.
+cudaError_t launch_adamw(__nv_bfloat16* param, float* master, float* m, float* v, const __nv_bfloat16* grad, long long n, float lr, float beta1,
+                         float beta2, float eps, float weight_decay, float bias_c1, float bias_c2, float grad_scale, cudaStream_t stream);
 
 }  // namespace fastb

@@ -1,0 +1,151 @@
+// Element-wise kernels of the expert MLP and the optimizer (memory-bound; 16-byte accesses).
+#include <cuda_fp8.h>
+
+#include "api.h"
+
+namespace fastb {
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+// gate_up rows are tiles of [128 gate | 128 up]; chunk c (8 features) of tile n sits at
+// 256 n + 8 (c % 16) for the gate and 128 further for the up projection.
+__global__ void swiglu_fwd_kernel(const uint4* __restrict__ gu, uint4* __restrict__ act, long long rows, int inter) {
+  const int cpr = inter / 8;  // output chunks per row
+  const long long total = rows * cpr;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cpr;
+    const int c = static_cast<int>(i % cpr);
+    const long long base = r * (2 * cpr) + (c / 16) * 32 + (c % 16);
+    float g[8], u[8], o[8];
+    unpack8(gu[base], g);
+    unpack8(gu[base + 16], u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.0f + __expf(-g[k])) * u[k];
+    act[i] = pack8(o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const uint4* __restrict__ gu, const uint4* __restrict__ dact, uint4* __restrict__ dgu, long long rows, int inter,
+                                  const int* __restrict__ rows_dev) {
+  if (rows_dev) rows = min(rows, static_cast<long long>(*rows_dev));  // rows in use this step (device-side count)
+  const int cpr = inter / 8;
+  const long long total = rows * cpr;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cpr;
+    const int c = static_cast<int>(i % cpr);
+    const long long base = r * (2 * cpr) + (c / 16) * 32 + (c % 16);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(gu[base], g);
+    unpack8(gu[base + 16], u);
+    unpack8(dact[i], d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float s = 1.0f / (1.0f + __expf(-g[k]));
+      const float silu = g[k] * s;
+      du[k] = d[k] * silu;
+      dg[k] = d[k] * u[k] * (s + silu * (1.0f - s));
+    }
+    dgu[base] = pack8(dg);
+    dgu[base + 16] = pack8(du);
+  }
+}
+
+__global__ void dequant_fp8_kernel(const uint2* __restrict__ q, const float* __restrict__ scales, uint4* __restrict__ out, long long rows, int H) {
+  const int cpr = H / 8;
+  const long long total = rows * cpr;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cpr;
+    const int c = static_cast<int>(i % cpr);
+    const float sc = scales[r * (H / 128) + c / 16];
+    const uint2 v = q[i];
+    const unsigned char* b = reinterpret_cast<const unsigned char*>(&v);
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const __half_raw h = __nv_cvt_fp8_to_halfraw(b[k], __NV_E4M3);
+      f[k] = __half2float(*reinterpret_cast<const __half*>(&h)) * sc;
+    }
+    out[i] = pack8(f);
+  }
+}
+
+__global__ void adamw_kernel(uint4* __restrict__ param, float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ v,
+                             const uint4* __restrict__ grad, long long n8, float lr, float b1, float b2, float eps, float wd, float c1, float c2,
+                             float gscale) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float g[8], w[8], mm[8], vv[8];
+    unpack8(grad[i], g);
+    float4 t;
+    t = master[2 * i]; w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+    t = master[2 * i + 1]; w[4] = t.x; w[5] = t.y; w[6] = t.z; w[7] = t.w;
+    t = m[2 * i]; mm[0] = t.x; mm[1] = t.y; mm[2] = t.z; mm[3] = t.w;
+    t = m[2 * i + 1]; mm[4] = t.x; mm[5] = t.y; mm[6] = t.z; mm[7] = t.w;
+    t = v[2 * i]; vv[0] = t.x; vv[1] = t.y; vv[2] = t.z; vv[3] = t.w;
+    t = v[2 * i + 1]; vv[4] = t.x; vv[5] = t.y; vv[6] = t.z; vv[7] = t.w;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = g[k] * gscale;
+      mm[k] = b1 * mm[k] + (1.0f - b1) * gk;
+      vv[k] = b2 * vv[k] + (1.0f - b2) * gk * gk;
+      const float upd = (mm[k] * c1) / (sqrtf(vv[k] * c2) + eps);
+      w[k] = w[k] - lr * (upd + wd * w[k]);
+    }
+    master[2 * i] = make_float4(w[0], w[1], w[2], w[3]); master[2 * i + 1] = make_float4(w[4], w[5], w[6], w[7]);
+    m[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]); m[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+    v[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]); v[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    param[i] = pack8(w);
+  }
+}
+
+int grid_for(long long items) { return static_cast<int>(std::min<long long>((items + 255) / 256, 148 * 8)); }
+
+}  // namespace
+
+cudaError_t launch_swiglu_fwd(const __nv_bfloat16* gate_up, __nv_bfloat16* act, long long rows, int inter, cudaStream_t stream) {
+  if (inter % 128) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  swiglu_fwd_kernel<<<grid_for(rows * inter / 8), 256, 0, stream>>>(reinterpret_cast<const uint4*>(gate_up), reinterpret_cast<uint4*>(act), rows, inter);
+  note_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_swiglu_bwd(const __nv_bfloat16* gate_up, const __nv_bfloat16* d_act, __nv_bfloat16* d_gate_up, long long rows, int inter,
+                              const int* rows_dev, cudaStream_t stream) {
+  if (inter % 128) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  swiglu_bwd_kernel<<<grid_for(rows * inter / 8), 256, 0, stream>>>(reinterpret_cast<const uint4*>(gate_up), reinterpret_cast<const uint4*>(d_act),
+                                                                  reinterpret_cast<uint4*>(d_gate_up), rows, inter, rows_dev);
+  note_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, cudaStream_t stream) {
+  if (H % 128) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  dequant_fp8_kernel<<<grid_for(rows * H / 8), 256, 0, stream>>>(reinterpret_cast<const uint2*>(q), scales, reinterpret_cast<uint4*>(out), rows, H);
+  note_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_adamw(__nv_bfloat16* param, float* master, float* m, float* v, const __nv_bfloat16* grad, long long n, float lr, float beta1,
+                         float beta2, float eps, float weight_decay, float bias_c1, float bias_c2, float grad_scale, cudaStream_t stream) {
+  if (n % 8) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  adamw_kernel<<<grid_for(n / 8), 256, 0, stream>>>(reinterpret_cast<uint4*>(param), reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
+                                                    reinterpret_cast<float4*>(v), reinterpret_cast<const uint4*>(grad), n / 8, lr, beta1, beta2, eps,
+                                                    weight_decay, bias_c1, bias_c2, grad_scale);
+  note_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace fastb

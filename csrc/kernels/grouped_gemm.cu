@@ -107,7 +107,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
+      int gated_group = -1;
       for (int tile = blockIdx.x; ok && walk.locate(tile, tc); tile += gridDim.x) {
+        if (p.gate_counter != nullptr && tc.g != gated_group) {
+          // Arrival gate: rows of this group are pushed by peers; start as soon as they are all in.
+          if (!(ok = wait_ge_bounded(p.gate_counter + tc.g, p.gate_target[tc.g], p.status, kSiteRailArrive, tc.g, p.timeout_ns))) { *abort_flag = 1; break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");  // peer (generic-proxy) writes before TMA (async-proxy) reads
+          gated_group = tc.g;
+        }
         for (int kb = 0; kb < tc.red_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -260,6 +267,7 @@ static cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
   kern<<<ctas, kThreads, kSmemBytes, stream>>>(a, b, args);
+  note_launch();
   return cudaGetLastError();
 }
 

@@ -1,0 +1,259 @@
+// Fused MoE transport kernels over peer memory (NVLink P2P loads/stores issued inside the kernel):
+//   dispatch_push : gather token rows by routing index, optional per-row scale, optional e4m3
+//                   quantisation with 1x128 block scales, and store them straight into the final
+//                   row of the owning expert's receive buffer on the peer; per-expert arrival
+//                   counters are bumped with release semantics once a CTA's rows are out.
+//   combine_pull  : un-permute + top-k weighted reduction: every token pulls its k expert rows
+//                   from the peers and accumulates them in fp32 (fixed slot order => reproducible),
+//                   or, in dot mode, produces <grad_out[t], row_j> for the router gradient.
+// In FAST's terms these are the all-to-all of the forward pass and its transpose
+// (amd/flash.cpp:400-408 `backward` flag) with the permute / reduce fused in; the reference moves
+// opaque bytes with ncclSend/ncclRecv groups or NVSHMEM puts and leaves the packing to the caller.
+#include <cuda_fp8.h>
+
+#include "api.h"
+
+namespace fastb {
+
+namespace {
+
+constexpr int kCommThreads = 256;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+constexpr int kMaxK = 8;
+
+__global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const DispatchArgs a) {
+  extern __shared__ int s_cnt[];  // [E] rows this CTA sent per expert
+  __shared__ int s_ok;
+  const int E = a.num_experts, El = E / a.world;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (a.entry_epoch != 0) {
+    // Entry handshake: publish that my receive buffers may be written, then wait for the peers.
+    unsigned long long* my_flags = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[a.rank]) + a.entry_flags_heap_off);
+    if (blockIdx.x == 0 && threadIdx.x < a.world) {
+      unsigned long long* dst = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[threadIdx.x]) + a.entry_flags_heap_off);
+      st_release_sys(dst + a.rank, a.entry_epoch);
+    }
+    if (threadIdx.x < a.world && !wait_ge_bounded(my_flags + threadIdx.x, a.entry_epoch, a.status, kSiteEntryReady, threadIdx.x, a.timeout_ns)) s_ok = 0;
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  constexpr int tpb = kRouteTokensPerBlock;
+  const int chunks = a.H / 8;  // 16-byte chunks per row
+  for (int t = blockIdx.x * wpb + warp; t < a.T; t += gridDim.x * wpb) {
+    unsigned char* dst[kMaxK];
+    float scale[kMaxK];
+    int row_of[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) {
+      dst[j] = nullptr; scale[j] = 1.0f; row_of[j] = 0;
+      if (j < a.K) {
+        const long long tj = static_cast<long long>(t) * a.K + j;
+        const int e = a.topk_idx[tj];
+        int row;
+        if (a.compute_rows) {
+          row = a.send_base[e] + a.block_base[static_cast<long long>(t / tpb) * E + e] + a.slot_in_block[tj];
+          if (lane == 0) a.dest_row[tj] = row;
+        } else {
+          row = a.dest_row[tj];
+        }
+        row_of[j] = row;
+        dst[j] = static_cast<unsigned char*>(a.peer_table[e / El]);
+        if (a.row_scale) scale[j] = a.row_scale[tj];
+        if (lane == 0) atomicAdd(&s_cnt[e], 1);
+      }
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.H);
+    if (!a.fp8) {
+      for (int c = lane; c < chunks; c += 32) {
+        const uint4 v = __ldg(src + c);
+        float f[8];
+        if (a.row_scale) unpack8(v, f);
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+          if (j >= a.K) break;
+          uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + (static_cast<long long>(row_of[j]) * a.H) * 2) + c;
+          if (a.row_scale) {
+            float g[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] = f[i] * scale[j];
+            *out = pack8(g);
+          } else {
+            *out = v;
+          }
+        }
+      }
+    } else {
+      // 128 elements = 16 lanes x 8 elements share one scale (amax / 448).
+      const int sgroups = a.H / 128;
+      for (int c = lane; c < chunks; c += 32) {
+        float f[8];
+        unpack8(__ldg(src + c), f);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+        for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float sc = fmaxf(amax, 1e-12f) * (1.0f / 448.0f);
+        const float inv = 1.0f / sc;
+        uint2 q;
+        unsigned char* qb = reinterpret_cast<unsigned char*>(&q);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+          if (j >= a.K) break;
+          uint2* out = reinterpret_cast<uint2*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
+          *out = q;
+          if ((lane & 15) == 0)
+            reinterpret_cast<float*>(dst[j] + a.scale_heap_off)[static_cast<long long>(row_of[j]) * sgroups + c / 16] = sc;
+        }
+      }
+    }
+  }
+  __syncthreads();  // every row of this CTA is stored before the counters move
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int n = s_cnt[e];
+    if (n == 0) continue;
+    unsigned long long* cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[e / El]) + a.arrive_heap_off);
+    fence_sys();
+    red_add_release_sys(cnt + (e % El), static_cast<unsigned long long>(n));
+  }
+}
+
+__global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const CombineArgs a) {
+  __shared__ int s_ok;
+  const int El = a.num_experts / a.world;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (a.ready_epoch != 0) {
+    const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(static_cast<unsigned char*>(a.peer_table[a.rank]) + a.ready_flags_heap_off);
+    if (threadIdx.x < a.world && !wait_ge_bounded(flags + threadIdx.x, a.ready_epoch, a.status, kSiteCombineReady, threadIdx.x, a.timeout_ns)) s_ok = 0;
+    __syncthreads();
+    if (!s_ok) return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int chunks = a.H / 8;
+  for (int t = blockIdx.x * wpb + warp; t < a.T; t += gridDim.x * wpb) {
+    const uint4* rows[kMaxK];
+    float w[kMaxK];
+#pragma unroll
+    for (int j = 0; j < kMaxK; ++j) {
+      rows[j] = nullptr; w[j] = 0.0f;
+      if (j < a.K) {
+        const long long tj = static_cast<long long>(t) * a.K + j;
+        const int e = a.topk_idx[tj];
+        rows[j] = reinterpret_cast<const uint4*>(static_cast<unsigned char*>(a.peer_table[e / El]) + a.src_heap_off +
+                                                 static_cast<long long>(a.dest_row[tj]) * a.H * 2);
+        w[j] = a.weights ? a.weights[tj] : 1.0f;
+      }
+    }
+    if (a.dot_out == nullptr) {
+      uint4* out = reinterpret_cast<uint4*>(a.out + static_cast<long long>(t) * a.H);
+      for (int c = lane; c < chunks; c += 32) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        uint4 v[kMaxK];
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j)
+          if (j < a.K) v[j] = __ldcg(rows[j] + c);
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+          if (j >= a.K) break;
+          float f[8];
+          unpack8(v[j], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[j], f[i], acc[i]);
+        }
+        out[c] = pack8(acc);
+      }
+    } else {
+      const uint4* g = reinterpret_cast<const uint4*>(a.dot_with + static_cast<long long>(t) * a.H);
+      float dots[kMaxK];
+#pragma unroll
+      for (int j = 0; j < kMaxK; ++j) dots[j] = 0.0f;
+      for (int c = lane; c < chunks; c += 32) {
+        float gf[8];
+        unpack8(__ldg(g + c), gf);
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) {
+          if (j >= a.K) break;
+          float f[8];
+          unpack8(__ldcg(rows[j] + c), f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dots[j] = fmaf(gf[i], f[i], dots[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxK; ++j) {
+        if (j >= a.K) break;
+        float d = dots[j];
+#pragma unroll
+        for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (lane == 0) a.dot_out[static_cast<long long>(t) * a.K + j] = d;
+      }
+    }
+  }
+}
+
+__global__ void peer_signal_kernel(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    unsigned long long* dst = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(peer_table[threadIdx.x]) + flags_heap_off);
+    st_release_sys(dst + rank, epoch);
+  }
+}
+
+__global__ void wait_counters_kernel(const unsigned long long* counter, const unsigned long long* target, int n, DeviceStatus* st,
+                                     unsigned long long timeout_ns) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) wait_ge_bounded(counter + i, target[i], st, kSiteRailArrive, i, timeout_ns);
+}
+
+}  // namespace
+
+cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t stream) {
+  if (a.K < 1 || a.K > kMaxK || a.H % 256 || a.world < 1 || a.num_experts % a.world || ctas < 1) return cudaErrorInvalidValue;
+  if (a.T == 0) return cudaSuccess;
+  dispatch_push_kernel<<<ctas, kCommThreads, sizeof(int) * a.num_experts, stream>>>(a);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_pull(const CombineArgs& a, int ctas, cudaStream_t stream) {
+  if (a.K < 1 || a.K > kMaxK || a.H % 256 || a.world < 1 || a.num_experts % a.world || ctas < 1) return cudaErrorInvalidValue;
+  if (a.T == 0) return cudaSuccess;
+  combine_pull_kernel<<<ctas, kCommThreads, 0, stream>>>(a);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_signal(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch, cudaStream_t stream) {
+  peer_signal_kernel<<<1, 64, 0, stream>>>(peer_table, rank, world, flags_heap_off, epoch);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_counters(const unsigned long long* counter, const unsigned long long* target, int n, DeviceStatus* status,
+                                 unsigned long long timeout_ns, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  wait_counters_kernel<<<(n + 63) / 64, 64, 0, stream>>>(counter, target, n, status, timeout_ns);
+  note_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace fastb

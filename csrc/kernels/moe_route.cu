@@ -1,0 +1,204 @@
+// MoE routing on the device, with no host round trip between the gate and the expert GEMMs:
+//   route_topk   : softmax(+bias) top-k per token, per-block expert histogram and the stable rank
+//                  of every (token, slot) inside its block;
+//   splits_scan  : prefix sums over blocks -> per-expert send counts, all-gather of the counts by
+//                  direct stores into every peer's symmetric pad, then receive offsets, padded
+//                  group offsets for the grouped GEMM and cumulative arrival targets.
+// The reference has no router; its counterpart of the count exchange is the host-side workload
+// broadcast (nvidia/alltoall_nvshmem.cpp:452-472), which this replaces with ~1 KB of NVLink stores.
+#include "api.h"
+
+namespace fastb {
+
+namespace {
+
+constexpr int kTokensPerBlock = kRouteTokensPerBlock;
+constexpr int kRouteThreads = 256;
+
+// One warp per token at a time. E <= 256 (8 values per lane).
+template <int MAX_PER_LANE>
+__global__ void __launch_bounds__(kRouteThreads) route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E,
+                                                                   int K, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                                   int* __restrict__ slot_in_block, int* __restrict__ block_cnt) {
+  extern __shared__ int s_eid[];  // [kTokensPerBlock * K]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kRouteThreads / 32;
+  const int t0 = blockIdx.x * kTokensPerBlock;
+  const int nt = min(kTokensPerBlock, T - t0);
+  for (int lt = warp; lt < kTokensPerBlock; lt += nwarps) {
+    const int t = t0 + lt;
+    if (lt >= nt) {
+      for (int j = lane; j < K; j += 32) s_eid[lt * K + j] = -1;
+      continue;
+    }
+    float sel[MAX_PER_LANE], raw[MAX_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      raw[i] = e < E ? logits[static_cast<long long>(t) * E + e] : -INFINITY;
+      sel[i] = e < E ? raw[i] + (bias ? bias[e] : 0.0f) : -INFINITY;
+      mx = fmaxf(mx, raw[i]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // Selection uses logits + bias; the weights are the softmax of the raw logits over the
+    // chosen experts (renormalised), which for bias == 0 is Mixtral's softmax-over-top-k.
+    float wsum = 0.0f;
+    float my_w = 0.0f;
+    int my_e = -1;
+    for (int j = 0; j < K; ++j) {
+      float best = -INFINITY;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < MAX_PER_LANE; ++i)
+        if (sel[i] > best) { best = sel[i]; best_e = lane + 32 * i; }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      float r = 0.0f;
+#pragma unroll
+      for (int i = 0; i < MAX_PER_LANE; ++i)
+        if (lane + 32 * i == best_e) { r = raw[i]; sel[i] = -INFINITY; }
+      r = __shfl_sync(0xffffffffu, r, best_e & 31);
+      const float p = __expf(r - mx);
+      wsum += p;
+      if (lane == j) { my_w = p; my_e = best_e; }
+    }
+    if (lane < K) {
+      topk_idx[static_cast<long long>(t) * K + lane] = my_e;
+      topk_w[static_cast<long long>(t) * K + lane] = my_w / wsum;
+      s_eid[lt * K + lane] = my_e;
+    }
+  }
+  __syncthreads();
+  // Stable rank of every entry among the entries of the same expert in this block: thread e walks
+  // the block's entries in (token, slot) order.
+  const int n = kTokensPerBlock * K;
+  for (int e = threadIdx.x; e < E; e += kRouteThreads) {
+    int c = 0;
+    for (int i = 0; i < n; ++i)
+      if (s_eid[i] == e) {
+        slot_in_block[static_cast<long long>(t0) * K + i] = c;
+        ++c;
+      }
+    block_cnt[static_cast<long long>(blockIdx.x) * E + e] = c;
+  }
+}
+
+// Single CTA. Thread e owns expert e (E <= 1024).
+__global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
+  extern __shared__ int s_tot[];  // [E] padded totals per expert, then [world] scratch
+  const int e = threadIdx.x;
+  const int E = a.num_experts, W = a.world, El = E / W;
+  unsigned char* my_slab = static_cast<unsigned char*>(a.peer_table[a.rank]);
+  int* my_counts = reinterpret_cast<int*>(my_slab + a.counts_heap_off);                       // [W][E]
+  unsigned long long* my_flags = reinterpret_cast<unsigned long long*>(my_slab + a.flags_heap_off);  // [W]
+  int mine = 0;
+  if (e < E) {
+    for (int b = 0; b < a.num_blocks; ++b) {
+      a.block_base[static_cast<long long>(b) * E + e] = mine;
+      mine += a.block_cnt[static_cast<long long>(b) * E + e];
+    }
+    // All-gather by stores: my row of the count matrix goes to every rank (myself included).
+    for (int r = 0; r < W; ++r) {
+      int* dst = reinterpret_cast<int*>(static_cast<unsigned char*>(a.peer_table[r]) + a.counts_heap_off);
+      dst[a.rank * E + e] = mine;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (e < W) {
+    unsigned long long* dst = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[e]) + a.flags_heap_off);
+    st_release_sys(dst + a.rank, a.epoch);
+  }
+  __shared__ int s_ok;
+  if (e == 0) s_ok = 1;
+  __syncthreads();
+  if (e < W) {
+    if (!wait_ge_bounded(my_flags + e, a.epoch, a.status, kSiteCountsArrive, e, a.timeout_ns)) s_ok = 0;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  int tot = 0, before_me = 0;
+  if (e < E) {
+    for (int s = 0; s < W; ++s) {
+      const int c = *reinterpret_cast<volatile int*>(my_counts + s * E + e);
+      tot += c;
+      if (s < a.rank) before_me += c;
+    }
+    s_tot[e] = (tot + 127) / 128 * 128;
+  }
+  __syncthreads();
+  if (e < E) {
+    // Row where my first token for expert e lands on its owner: padded sizes of the owner's
+    // earlier experts plus the rows of lower-ranked sources for e.
+    const int d = e / El, le = e % El;
+    int base = 0;
+    for (int q = 0; q < le; ++q) base += s_tot[d * El + q];
+    a.send_base[e] = base + before_me;
+    a.send_cnt[e] = mine;
+    if (d == a.rank) {
+      a.group_off[le] = base;
+      a.group_rows[le] = tot;
+      if (le == El - 1) a.group_off[El] = base + s_tot[e];
+      // Monotone arrival targets, one per channel (forward dispatch, backward dispatch).
+      for (int ch = 0; ch < a.num_channels; ++ch) a.arrive_target[ch * El + le] += static_cast<unsigned long long>(tot);
+    }
+  }
+  // Token traffic matrix of this step, [src][dst], for the scheduler / observability.
+  if (a.traffic_matrix)
+    for (int i = threadIdx.x; i < W * W; i += blockDim.x) {
+      const int s = i / W, d = i % W;
+      int sent = 0;
+      for (int q = 0; q < El; ++q) sent += *reinterpret_cast<volatile int*>(my_counts + s * E + d * El + q);
+      a.traffic_matrix[i] = sent;
+    }
+}
+
+// Zeroes the rows between each group's real end and its padded end.
+__global__ void zero_pad_rows_kernel(unsigned char* buf, long long row_bytes, const int* __restrict__ group_off, const int* __restrict__ group_rows, int groups) {
+  const int g = blockIdx.y;
+  if (g >= groups) return;
+  const long long begin = (static_cast<long long>(group_off[g]) + group_rows[g]) * row_bytes;
+  const long long end = static_cast<long long>(group_off[g + 1]) * row_bytes;
+  uint4* p = reinterpret_cast<uint4*>(buf + begin);
+  const long long n = (end - begin) / 16;
+  for (long long i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) p[i] = make_uint4(0, 0, 0, 0);
+}
+
+}  // namespace
+
+cudaError_t launch_route_topk(const float* logits, const float* bias, int T, int E, int K, int* topk_idx, float* topk_w, int* slot_in_block,
+                              int* block_cnt, cudaStream_t stream) {
+  if (E < 1 || E > 256 || K < 1 || K > 32 || K > E) return cudaErrorInvalidValue;
+  const int blocks = (T + kTokensPerBlock - 1) / kTokensPerBlock;
+  if (blocks == 0) return cudaSuccess;
+  const size_t smem = sizeof(int) * kTokensPerBlock * K;
+  if (E <= 32) route_topk_kernel<1><<<blocks, kRouteThreads, smem, stream>>>(logits, bias, T, E, K, topk_idx, topk_w, slot_in_block, block_cnt);
+  else if (E <= 64) route_topk_kernel<2><<<blocks, kRouteThreads, smem, stream>>>(logits, bias, T, E, K, topk_idx, topk_w, slot_in_block, block_cnt);
+  else if (E <= 128) route_topk_kernel<4><<<blocks, kRouteThreads, smem, stream>>>(logits, bias, T, E, K, topk_idx, topk_w, slot_in_block, block_cnt);
+  else route_topk_kernel<8><<<blocks, kRouteThreads, smem, stream>>>(logits, bias, T, E, K, topk_idx, topk_w, slot_in_block, block_cnt);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream) {
+  if (a.num_experts < 1 || a.num_experts > 1024 || a.world < 1 || a.world > a.num_experts || a.num_experts % a.world) return cudaErrorInvalidValue;
+  int threads = (std::max(a.num_experts, a.world) + 31) / 32 * 32;
+  splits_scan_kernel<<<1, threads, sizeof(int) * (a.num_experts + a.world), stream>>>(a);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* group_off, const int* group_rows, int groups, cudaStream_t stream) {
+  if (row_bytes % 16) return cudaErrorInvalidValue;
+  if (groups == 0) return cudaSuccess;
+  zero_pad_rows_kernel<<<dim3(8, groups), 256, 0, stream>>>(static_cast<unsigned char*>(buf), row_bytes, group_off, group_rows, groups);
+  note_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace fastb

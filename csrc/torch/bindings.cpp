@@ -8,47 +8,14 @@
 
 #include <memory>
 
-#include "kernels/api.h"
-#include "runtime/symm_heap.h"
+#include "py_types.h"
 
 namespace py = pybind11;
 using namespace fastb;
+using namespace fastb_py;
 
 namespace {
 
-void cuda_check(cudaError_t e, const char* what) {
-  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
-}
-cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
-
-// ---- symmetric heap -----------------------------------------------------------------------------
-struct HeapPy {
-  std::shared_ptr<SymmHeap> h;
-  int device;
-  torch::Tensor tensor(int64_t offset, std::vector<int64_t> shape, py::object dtype) const {
-    auto dt = torch::python::detail::py_object_to_dtype(dtype);
-    auto opts = torch::TensorOptions().dtype(dt).device(torch::kCUDA, device);
-    return torch::from_blob(static_cast<char*>(h->local_base()) + offset, shape, opts);
-  }
-};
-
-// ---- status block -------------------------------------------------------------------------------
-struct StatusPy {
-  DeviceStatus* d = nullptr;
-  StatusPy() {
-    cuda_check(cudaMalloc(reinterpret_cast<void**>(&d), sizeof(DeviceStatus)), "cudaMalloc status");
-    cuda_check(cudaMemset(d, 0, sizeof(DeviceStatus)), "clear status");
-  }
-  ~StatusPy() { if (d) cudaFree(d); }
-  // Synchronises the current stream, then returns (code, site, detail, seen, want).
-  py::tuple read() const {
-    DeviceStatus s;
-    cuda_check(cudaStreamSynchronize(cur_stream()), "sync before status read");
-    cuda_check(cudaMemcpy(&s, d, sizeof(s), cudaMemcpyDeviceToHost), "read status");
-    return py::make_tuple(s.code, s.site, s.detail, s.seen, s.want);
-  }
-  void clear() { cuda_check(cudaMemsetAsync(d, 0, sizeof(DeviceStatus), cur_stream()), "clear status"); }
-};
 
 // ---- a2a program ----------------------------------------------------------------------------------
 struct A2AProgramPy {
@@ -166,5 +133,6 @@ PYBIND11_MODULE(_C, m) {
   m.def("wait_probe", [](int64_t flag_ptr, uint64_t want, const StatusPy& st, uint64_t timeout_ns) {
     cuda_check(launch_wait_probe(reinterpret_cast<const unsigned long long*>(flag_ptr), want, st.d, timeout_ns, cur_stream()), "wait_probe");
   });
+  m.def("launch_count", &launch_count);
   bind_moe(m);
 }

@@ -1,18 +1,22 @@
 // Bindings of the MoE kernels (routing, split scan, dispatch, grouped GEMM, combine).
-#include <ATen/cuda/CUDAContext.h>
 #include <cuda.h>
 #include <cuda_runtime.h>
-#include <torch/extension.h>
 
-#include "kernels/api.h"
+#include "py_types.h"
 
 namespace py = pybind11;
 using namespace fastb;
+using namespace fastb_py;
 
 namespace {
 
-void cu_check(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e)); }
-cudaStream_t stream_now() { return at::cuda::getCurrentCUDAStream().stream(); }
+void cu_check(cudaError_t e, const char* what) { cuda_check(e, what); }
+cudaStream_t stream_now() { return cur_stream(); }
+
+template <class T> T* ptr_or_null(const c10::optional<torch::Tensor>& t) { return t.has_value() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr; }
+void want(const torch::Tensor& t, c10::ScalarType dt, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == dt, name, ": expected a contiguous CUDA tensor of the right dtype");
+}
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -50,7 +54,7 @@ struct TensorMap2D {
 
 void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2D& b, torch::Tensor group_off, int tiles_n, int fixed_m_tiles,
                   int red_len, int b_rows_per_group, int c_rows_per_group, torch::Tensor c, c10::optional<torch::Tensor> c2, int64_t status_ptr,
-                  uint64_t timeout_ns, int ctas) {
+                  uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target) {
   TORCH_CHECK(group_off.is_cuda() && group_off.dtype() == torch::kInt32 && group_off.is_contiguous() && group_off.numel() >= 2, "group_off: cuda int32[G+1]");
   TORCH_CHECK(c.is_cuda() && c.dtype() == torch::kBFloat16 && c.dim() == 2 && c.stride(1) == 1, "c: cuda bf16 [rows, cols]");
   TORCH_CHECK(red_len % 64 == 0 && tiles_n >= 1, "reduction length must be a multiple of 64");
@@ -66,7 +70,81 @@ void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2
   }
   g.status = reinterpret_cast<DeviceStatus*>(status_ptr);
   g.timeout_ns = timeout_ns;
+  if (gate_counter_ptr != 0) {
+    TORCH_CHECK(gate_target.has_value() && gate_target->is_cuda() && gate_target->scalar_type() == torch::kInt64 && gate_target->numel() >= g.num_groups,
+                "gate_target: cuda int64[G]");
+    g.gate_counter = reinterpret_cast<const unsigned long long*>(gate_counter_ptr);
+    g.gate_target = reinterpret_cast<const unsigned long long*>(gate_target->data_ptr());
+  }
   cu_check(launch_grouped_gemm(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, g, ctas, stream_now()), "grouped_gemm launch");
+}
+
+void route_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int K, torch::Tensor topk_idx, torch::Tensor topk_w,
+                torch::Tensor slot_in_block, torch::Tensor block_cnt) {
+  want(logits, torch::kFloat32, "logits"); want(topk_idx, torch::kInt32, "topk_idx"); want(topk_w, torch::kFloat32, "topk_w");
+  want(slot_in_block, torch::kInt32, "slot_in_block"); want(block_cnt, torch::kInt32, "block_cnt");
+  const int T = static_cast<int>(logits.size(0)), E = static_cast<int>(logits.size(1));
+  const int blocks = (T + kRouteTokensPerBlock - 1) / kRouteTokensPerBlock;
+  TORCH_CHECK(topk_idx.numel() == static_cast<int64_t>(T) * K && slot_in_block.numel() >= static_cast<int64_t>(blocks) * kRouteTokensPerBlock * K &&
+              block_cnt.numel() == static_cast<int64_t>(blocks) * E, "route_topk: output shapes");
+  cu_check(launch_route_topk(logits.data_ptr<float>(), ptr_or_null<const float>(bias), T, E, K, topk_idx.data_ptr<int>(), topk_w.data_ptr<float>(),
+                             slot_in_block.data_ptr<int>(), block_cnt.data_ptr<int>(), stream_now()), "route_topk");
+}
+
+void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint64_t epoch, torch::Tensor block_cnt, torch::Tensor block_base,
+                 torch::Tensor send_base, torch::Tensor send_cnt, torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor arrive_target,
+                 c10::optional<torch::Tensor> traffic, int num_channels, const StatusPy& st, uint64_t timeout_ns) {
+  SplitsArgs a{};
+  a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
+  a.num_experts = static_cast<int>(send_base.numel()); a.num_blocks = static_cast<int>(block_cnt.numel() / a.num_experts); a.num_channels = num_channels;
+  a.counts_heap_off = counts_off; a.flags_heap_off = flags_off; a.epoch = epoch;
+  want(block_cnt, torch::kInt32, "block_cnt"); want(block_base, torch::kInt32, "block_base"); want(send_base, torch::kInt32, "send_base");
+  want(send_cnt, torch::kInt32, "send_cnt"); want(group_off, torch::kInt32, "group_off"); want(group_rows, torch::kInt32, "group_rows");
+  want(arrive_target, torch::kInt64, "arrive_target");
+  const int El = a.num_experts / a.world;
+  TORCH_CHECK(group_off.numel() == El + 1 && group_rows.numel() == El && arrive_target.numel() == static_cast<int64_t>(num_channels) * El, "splits_scan: shapes");
+  a.block_cnt = block_cnt.data_ptr<int>(); a.block_base = block_base.data_ptr<int>(); a.send_base = send_base.data_ptr<int>();
+  a.send_cnt = send_cnt.data_ptr<int>(); a.group_off = group_off.data_ptr<int>(); a.group_rows = group_rows.data_ptr<int>();
+  a.arrive_target = reinterpret_cast<unsigned long long*>(arrive_target.data_ptr());
+  a.traffic_matrix = ptr_or_null<int>(traffic);
+  a.status = st.d; a.timeout_ns = timeout_ns;
+  cu_check(launch_splits_scan(a, stream_now()), "splits_scan");
+}
+
+void zero_pad_rows(torch::Tensor buf, torch::Tensor group_off, torch::Tensor group_rows) {
+  TORCH_CHECK(buf.is_cuda() && buf.dim() == 2 && buf.is_contiguous(), "buf: contiguous CUDA matrix");
+  cu_check(launch_zero_pad_rows(buf.data_ptr(), buf.size(1) * buf.element_size(), group_off.data_ptr<int>(), group_rows.data_ptr<int>(),
+                                static_cast<int>(group_rows.numel()), stream_now()), "zero_pad_rows");
+}
+
+void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, c10::optional<torch::Tensor> row_scale, torch::Tensor slot_in_block,
+                   torch::Tensor block_base, torch::Tensor send_base, torch::Tensor dest_row, bool compute_rows, bool fp8, int64_t recv_off,
+                   int64_t scale_off, int64_t arrive_off, int64_t entry_flags_off, uint64_t entry_epoch, const StatusPy& st, uint64_t timeout_ns, int ctas) {
+  want(x, torch::kBFloat16, "x"); want(topk_idx, torch::kInt32, "topk_idx"); want(dest_row, torch::kInt32, "dest_row");
+  DispatchArgs a{};
+  a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
+  a.num_experts = static_cast<int>(send_base.numel()); a.T = static_cast<int>(x.size(0)); a.H = static_cast<int>(x.size(1));
+  a.K = static_cast<int>(topk_idx.size(1));
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()); a.topk_idx = topk_idx.data_ptr<int>(); a.row_scale = ptr_or_null<const float>(row_scale);
+  a.slot_in_block = slot_in_block.data_ptr<int>(); a.block_base = block_base.data_ptr<int>(); a.send_base = send_base.data_ptr<int>();
+  a.dest_row = dest_row.data_ptr<int>(); a.compute_rows = compute_rows; a.fp8 = fp8;
+  a.recv_heap_off = recv_off; a.scale_heap_off = scale_off; a.arrive_heap_off = arrive_off;
+  a.entry_flags_heap_off = entry_flags_off; a.entry_epoch = entry_epoch; a.status = st.d; a.timeout_ns = timeout_ns;
+  cu_check(launch_dispatch_push(a, ctas, stream_now()), "dispatch_push");
+}
+
+void combine_pull(const HeapPy& heap, int num_experts, torch::Tensor topk_idx, torch::Tensor dest_row, c10::optional<torch::Tensor> weights, int64_t src_off,
+                  int64_t ready_off, uint64_t ready_epoch, c10::optional<torch::Tensor> out, c10::optional<torch::Tensor> dot_with,
+                  c10::optional<torch::Tensor> dot_out, int H, const StatusPy& st, uint64_t timeout_ns, int ctas) {
+  CombineArgs a{};
+  a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world(); a.num_experts = num_experts;
+  a.T = static_cast<int>(topk_idx.size(0)); a.K = static_cast<int>(topk_idx.size(1)); a.H = H;
+  a.topk_idx = topk_idx.data_ptr<int>(); a.dest_row = dest_row.data_ptr<int>(); a.weights = ptr_or_null<const float>(weights);
+  a.src_heap_off = src_off; a.ready_flags_heap_off = ready_off; a.ready_epoch = ready_epoch;
+  a.out = ptr_or_null<__nv_bfloat16>(out); a.dot_with = ptr_or_null<const __nv_bfloat16>(dot_with); a.dot_out = ptr_or_null<float>(dot_out);
+  TORCH_CHECK((a.out != nullptr) != (a.dot_out != nullptr), "combine_pull: give either out or dot_out");
+  a.status = st.d; a.timeout_ns = timeout_ns;
+  cu_check(launch_combine_pull(a, ctas, stream_now()), "combine_pull");
 }
 
 }  // namespace
@@ -75,4 +153,43 @@ void bind_moe(py::module_& m) {
   py::class_<TensorMap2D>(m, "TensorMap2D").def(py::init<int64_t, int64_t, int64_t, int64_t, int, int>());
   m.def("grouped_gemm", &grouped_gemm);
   m.def("grouped_gemm_smem_bytes", &grouped_gemm_smem_bytes);
+  m.attr("ROUTE_TOKENS_PER_BLOCK") = kRouteTokensPerBlock;
+  m.def("route_topk", &route_topk);
+  m.def("splits_scan", &splits_scan);
+  m.def("zero_pad_rows", &zero_pad_rows);
+  m.def("dispatch_push", &dispatch_push);
+  m.def("combine_pull", &combine_pull);
+  m.def("peer_signal", [](const HeapPy& heap, int64_t flags_off, uint64_t epoch) {
+    cu_check(launch_peer_signal(heap.h->device_peer_table(), heap.h->rank(), heap.h->world(), flags_off, epoch, stream_now()), "peer_signal");
+  });
+  m.def("wait_counters", [](int64_t counter_ptr, torch::Tensor target, const StatusPy& st, uint64_t timeout_ns) {
+    cu_check(launch_wait_counters(reinterpret_cast<const unsigned long long*>(counter_ptr), reinterpret_cast<const unsigned long long*>(target.data_ptr()),
+                                  static_cast<int>(target.numel()), st.d, timeout_ns, stream_now()), "wait_counters");
+  });
+  m.def("swiglu_fwd", [](torch::Tensor gu, torch::Tensor act) {
+    want(gu, torch::kBFloat16, "gate_up"); want(act, torch::kBFloat16, "act");
+    cu_check(launch_swiglu_fwd(reinterpret_cast<const __nv_bfloat16*>(gu.data_ptr()), reinterpret_cast<__nv_bfloat16*>(act.data_ptr()), gu.size(0),
+                               static_cast<int>(act.size(1)), stream_now()), "swiglu_fwd");
+  });
+  m.def("swiglu_bwd", [](torch::Tensor gu, torch::Tensor dact, torch::Tensor dgu, int64_t rows_dev_ptr) {
+    want(gu, torch::kBFloat16, "gate_up"); want(dact, torch::kBFloat16, "d_act"); want(dgu, torch::kBFloat16, "d_gate_up");
+    cu_check(launch_swiglu_bwd(reinterpret_cast<const __nv_bfloat16*>(gu.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(dact.data_ptr()),
+                               reinterpret_cast<__nv_bfloat16*>(dgu.data_ptr()), gu.size(0), static_cast<int>(dact.size(1)), reinterpret_cast<const int*>(rows_dev_ptr),
+                               stream_now()), "swiglu_bwd");
+  });
+  m.def("dequant_fp8", [](torch::Tensor q, torch::Tensor scales, torch::Tensor out) {
+    want(q, torch::kUInt8, "q"); want(scales, torch::kFloat32, "scales"); want(out, torch::kBFloat16, "out");
+    cu_check(launch_dequant_fp8(q.data_ptr<uint8_t>(), scales.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), q.size(0),
+                                static_cast<int>(q.size(1)), stream_now()), "dequant_fp8");
+  });
+  m.def("adamw", [](torch::Tensor param, torch::Tensor master, torch::Tensor m1, torch::Tensor v, torch::Tensor grad, double lr, double b1, double b2,
+                    double eps, double wd, int64_t step, double grad_scale) {
+    want(param, torch::kBFloat16, "param"); want(master, torch::kFloat32, "master"); want(m1, torch::kFloat32, "m"); want(v, torch::kFloat32, "v");
+    want(grad, torch::kBFloat16, "grad");
+    const double c1 = 1.0 / (1.0 - std::pow(b1, static_cast<double>(step))), c2 = 1.0 / (1.0 - std::pow(b2, static_cast<double>(step)));
+    cu_check(launch_adamw(reinterpret_cast<__nv_bfloat16*>(param.data_ptr()), master.data_ptr<float>(), m1.data_ptr<float>(), v.data_ptr<float>(),
+                          reinterpret_cast<const __nv_bfloat16*>(grad.data_ptr()), param.numel(), static_cast<float>(lr), static_cast<float>(b1),
+                          static_cast<float>(b2), static_cast<float>(eps), static_cast<float>(wd), static_cast<float>(c1), static_cast<float>(c2),
+                          static_cast<float>(grad_scale), stream_now()), "adamw");
+  });
 }

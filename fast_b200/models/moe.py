@@ -1,0 +1,123 @@
+"""MoE layer and the Mixtral-shaped block model built on the expert-parallel engine.
+
+Weight layout (framework-owned): ``w13`` is [experts_local, 2*inter, hidden] where every group of
+256 rows holds 128 gate rows followed by the 128 up rows of the same features (so that one GEMM
+tile carries both halves of SwiGLU); ``w2`` is [experts_local, hidden, inter].
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..parallel.comm import Communicator
+from ..parallel.ep import ExpertParallel
+
+
+def interleave_gate_up(w1: torch.Tensor, w3: torch.Tensor) -> torch.Tensor:
+    """[E, I, H] gate and up projections -> [E, 2I, H] in tiles of [128 gate | 128 up]."""
+    E, I, H = w1.shape
+    return torch.stack([w1.view(E, I // 128, 128, H), w3.view(E, I // 128, 128, H)], dim=2).reshape(E, 2 * I, H).contiguous()
+
+
+def split_gate_up(w13: torch.Tensor):
+    E, I2, H = w13.shape
+    t = w13.view(E, I2 // 256, 2, 128, H)
+    return t[:, :, 0].reshape(E, I2 // 2, H), t[:, :, 1].reshape(E, I2 // 2, H)
+
+
+class _MoEFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weights, w13, w2, engine, rs):
+        engine.dispatch(x, rs)
+        engine.experts_forward(w13, w2, rs)
+        out = engine.combine(rs, weights.detach().float().contiguous())
+        ctx.engine, ctx.rs = engine, rs
+        ctx.save_for_backward(weights, w13, w2)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        weights, w13, w2 = ctx.saved_tensors
+        eng = ctx.engine
+        if not hasattr(eng, "_dw13") or eng._dw13.shape != w13.shape:
+            eng._dw13, eng._dw2 = torch.empty_like(w13), torch.empty_like(w2)
+        gx, gw = eng.backward(grad_out.contiguous(), ctx.rs, weights.detach().float().contiguous(), w13, w2, eng._dw13, eng._dw2)
+        return gx, gw.to(weights.dtype), eng._dw13, eng._dw2, None, None
+
+
+class MoELayer(nn.Module):
+    """Top-k softmax-routed SwiGLU experts, expert-parallel over the communicator's ranks."""
+
+    def __init__(self, comm: Communicator, hidden: int, inter: int, num_experts: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
+                 router_bias: bool = False, training: bool = True, capacity_rows: Optional[int] = None, init_std: float = 0.02, seed: int = 0):
+        super().__init__()
+        self.comm, self.hidden, self.inter, self.num_experts, self.top_k = comm, hidden, inter, num_experts, top_k
+        El = num_experts // comm.world
+        dev = comm.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.gate = nn.Parameter((torch.randn(num_experts, hidden, generator=g, device=dev) * init_std).to(torch.bfloat16))
+        ge = torch.Generator(device=dev).manual_seed(seed + 1 + comm.rank)
+        self.w13 = nn.Parameter((torch.randn(El, 2 * inter, hidden, generator=ge, device=dev) * init_std).to(torch.bfloat16))
+        self.w2 = nn.Parameter((torch.randn(El, hidden, inter, generator=ge, device=dev) * init_std).to(torch.bfloat16))
+        self.router_bias = nn.Parameter(torch.zeros(num_experts, device=dev), requires_grad=False) if router_bias else None
+        self.engine = ExpertParallel(comm, num_experts, hidden, inter, top_k, max_tokens, fp8_dispatch=fp8_dispatch, training=training,
+                                     capacity_rows=capacity_rows)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: [tokens, hidden] bf16 -> [tokens, hidden] bf16."""
+        logits = (x @ self.gate.t()).float()
+        rs = self.engine.route(logits.detach(), self.router_bias)
+        if torch.is_grad_enabled() and self.training:
+            w = torch.softmax(logits.gather(1, rs.topk_idx.long()), dim=-1)
+            return _MoEFunction.apply(x, w, self.w13, self.w2, self.engine, rs)
+        self.engine.dispatch(x, rs)
+        self.engine.experts_forward(self.w13, self.w2, rs)
+        return self.engine.combine(rs, rs.topk_w)
+
+
+class MixtralBlockModel(nn.Module):
+    """Embedding -> RMSNorm -> MoE block (+ residual) -> mean-square loss; Mixtral-8x7B shapes by default."""
+
+    def __init__(self, comm: Communicator, vocab: int = 32000, hidden: int = 4096, inter: int = 14336, num_experts: int = 8, top_k: int = 2,
+                 max_tokens: int = 8 * 4096, capacity_rows: Optional[int] = None, seed: int = 0):
+        super().__init__()
+        dev = comm.device
+        g = torch.Generator(device=dev).manual_seed(seed + 100)
+        self.embed = nn.Parameter((torch.randn(vocab, hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16))
+        self.norm_w = nn.Parameter(torch.ones(hidden, device=dev, dtype=torch.bfloat16))
+        self.moe = MoELayer(comm, hidden, inter, num_experts, top_k, max_tokens, capacity_rows=capacity_rows, seed=seed)
+        self.eps = 1e-5
+
+    def replicated_parameters(self):
+        return [self.embed, self.norm_w, self.moe.gate]
+
+    def expert_parameters(self):
+        return [self.moe.w13, self.moe.w2]
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        h = torch.nn.functional.embedding(token_ids.reshape(-1), self.embed)
+        hn = torch.nn.functional.rms_norm(h, (h.shape[-1],), self.norm_w, self.eps)
+        out = h + self.moe(hn)
+        return out.float().pow(2).mean()
+
+
+@torch.no_grad()
+def reference_moe(x, gate, w13_all, w2_all, top_k, bias=None):
+    """Plain fp32 PyTorch MoE on one device with ALL experts ([E, 2I, H] interleaved, [E, H, I])."""
+    xf = x.float()
+    logits = xf @ gate.float().t()
+    sel = logits + (bias.float() if bias is not None else 0.0)
+    idx = sel.topk(top_k, dim=-1).indices
+    w = torch.softmax(logits.gather(1, idx), dim=-1)
+    w1, w3 = split_gate_up(w13_all.float())
+    out = torch.zeros_like(xf)
+    for e in range(w13_all.shape[0]):
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = xf[tok]
+        a = torch.nn.functional.silu(h @ w1[e].t()) * (h @ w3[e].t())
+        out.index_add_(0, tok, (a @ w2_all[e].float().t()) * w[tok, slot].unsqueeze(1))
+    return out, idx, w

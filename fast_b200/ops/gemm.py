@@ -59,29 +59,30 @@ def pad_group_offsets(counts: torch.Tensor) -> torch.Tensor:
 
 
 def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
-                     gate_up_out: Optional[torch.Tensor] = None, timeout_s: float = 5.0) -> torch.Tensor:
+                     gate_up_out: Optional[torch.Tensor] = None, timeout_s: float = 5.0, gate=None) -> torch.Tensor:
     """out[rows of g] = a[rows of g] @ w[g].T  (a [R, K], w [G, N, K], out [R, N]).
 
     With ``swiglu`` the N columns of every 256-wide tile are [128 gate | 128 up] of the same 128
     features and ``out`` is [R, N/2] = silu(gate) * up; ``gate_up_out`` ([R, N]) optionally keeps
-    the raw tile for the backward pass.
+    the raw tile for the backward pass. ``gate=(counter_ptr, target)`` makes the TMA producer
+    wait, group by group, until ``counter[g] >= target[g]`` (rows pushed by peers have landed).
     """
     G, N, K = w.shape
     assert a.shape[1] == K and K % _BK == 0 and N % _BN == 0 and a.shape[0] % _BM == 0
     assert out.shape[0] == a.shape[0] and out.shape[1] == (N // 2 if swiglu else N)
     C = runtime.ext()
     C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), _BN), group_off, N // _BN, 0, K, N, 0, out,
-                   gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas())
+                   gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)))
     return out
 
 
-def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, timeout_s: float = 5.0) -> torch.Tensor:
+def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, timeout_s: float = 5.0, gate=None) -> torch.Tensor:
     """out[rows of g] = dy[rows of g] @ w[g]  (dy [R, N], w [G, N, K], out [R, K])."""
     G, N, K = w.shape
     assert dy.shape[1] == N and N % _BK == 0 and K % _BN == 0 and dy.shape[0] % _BM == 0
     C = runtime.ext()
     C.grouped_gemm(DGRAD, STORE, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas())
+                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)))
     return out
 
 
@@ -92,5 +93,5 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, group_off: torch.Tenso
     assert dy.shape[1] == N and x.shape[1] == K and N % _BM == 0 and K % _BN == 0
     C = runtime.ext()
     C.grouped_gemm(WGRAD, STORE, _tmap(dy, _BK), _tmap(x, _BK), group_off, K // _BN, N // _BM, 0, 0, N, out.view(G * N, K), None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas())
+                   int(timeout_s * 1e9), _ctas(), 0, None)
     return out

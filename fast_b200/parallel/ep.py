@@ -1,0 +1,195 @@
+"""Expert-parallel MoE engine: routing -> count exchange -> fused dispatch -> grouped expert GEMMs
+-> fused combine, and the mirrored backward pass, all stream-ordered on the device.
+
+Nothing in the step returns to the host between the gate and the combined output: routing
+indices, split counts, receive offsets and GEMM group boundaries are produced and consumed in
+device memory, and peers are synchronised by flags and counters in the symmetric heap.
+
+In the reference, the host computes a schedule from a token matrix (amd/flash.cpp:400-420) and
+runs the forward all-to-all, and again with ``backward=1`` for the reverse direction; the MoE
+layer around it is left to the caller. Here the same two collectives are fused with the permute,
+the quantisation, the expert GEMMs and the weighted reduction.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import runtime
+from ..ops import gemm
+from .comm import Communicator
+
+
+@dataclass
+class RouteState:
+    """Per-step routing products kept for combine and for the backward pass."""
+
+    topk_idx: torch.Tensor
+    topk_w: torch.Tensor
+    dest_row: torch.Tensor
+    slot_in_block: torch.Tensor
+    block_base: torch.Tensor
+    send_base: torch.Tensor
+    group_off: torch.Tensor
+    group_rows: torch.Tensor
+    epoch: int
+
+
+class ExpertParallel:
+    def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
+                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: int = 64):
+        C = runtime.ext()
+        self._C, self.comm = C, comm
+        W = comm.world
+        assert num_experts % W == 0 and hidden % 256 == 0 and (2 * inter) % 256 == 0 and inter % 64 == 0
+        self.E, self.El, self.H, self.I, self.K, self.T = num_experts, num_experts // W, hidden, inter, top_k, max_tokens
+        self.fp8, self.training, self.comm_ctas = fp8_dispatch, training, comm_ctas
+        worst = W * max_tokens * min(top_k, self.El) + 128 * self.El
+        self.cap = int(capacity_rows) if capacity_rows else worst
+        self.cap = (min(self.cap, worst) + 127) // 128 * 128
+        dev = comm.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        # symmetric: control words
+        self.counts = comm.alloc((W, self.E), torch.int32)
+        self.flags = comm.alloc((8, 64), torch.int64)  # rows: 0 counts, 1 fwd-ready, 2 bwd-entry, 3 bwd-ready
+        self.arrive = comm.alloc((2, self.El), torch.int64)
+        for t in (self.counts, self.flags, self.arrive):
+            t.zero_()
+        # symmetric: payload
+        if fp8_dispatch:
+            self.xq_recv = comm.alloc((self.cap, hidden), torch.uint8)
+            self.xs_recv = comm.alloc((self.cap, hidden // 128), torch.float32)
+            self.x_recv = torch.zeros(self.cap, hidden, dtype=torch.bfloat16, device=dev)
+        else:
+            self.x_recv = comm.alloc((self.cap, hidden), torch.bfloat16)
+        self.y = comm.alloc((self.cap, hidden), torch.bfloat16)
+        self.x_recv.zero_()
+        self.y.zero_()
+        # local work buffers
+        self.act = torch.zeros(self.cap, inter, dtype=torch.bfloat16, device=dev)
+        if training:
+            self.dy_recv = comm.alloc((self.cap, hidden), torch.bfloat16)
+            self.dx_recv = comm.alloc((self.cap, hidden), torch.bfloat16)
+            self.dy_recv.zero_()
+            self.dx_recv.zero_()
+            self.gu = torch.zeros(self.cap, 2 * inter, dtype=torch.bfloat16, device=dev)
+            self.dact = torch.zeros(self.cap, inter, dtype=torch.bfloat16, device=dev)
+            self.dgu = torch.zeros(self.cap, 2 * inter, dtype=torch.bfloat16, device=dev)
+        blocks = (max_tokens + C.ROUTE_TOKENS_PER_BLOCK - 1) // C.ROUTE_TOKENS_PER_BLOCK
+        self.blocks = blocks
+        self.block_cnt = torch.zeros(blocks, self.E, **i32)
+        self.block_base = torch.zeros(blocks, self.E, **i32)
+        self.slot_in_block = torch.zeros(blocks * C.ROUTE_TOKENS_PER_BLOCK, top_k, **i32)
+        self.send_base = torch.zeros(self.E, **i32)
+        self.send_cnt = torch.zeros(self.E, **i32)
+        self.group_off = torch.zeros(self.El + 1, **i32)
+        self.group_rows = torch.zeros(self.El, **i32)
+        self.arrive_target = torch.zeros(2, self.El, dtype=torch.int64, device=dev)
+        self.traffic = torch.zeros(W, W, **i32)
+        self.epoch = 0
+        self.status = comm.status
+        self.timeout_ns = comm.timeout_ns
+        torch.cuda.synchronize(dev)
+        if W > 1:
+            import torch.distributed as dist
+
+            dist.barrier(group=comm.group)
+
+    # ---- helpers -----------------------------------------------------------------------------
+    def _off(self, t: torch.Tensor) -> int:
+        return t._symm_off
+
+    def _flag_off(self, row: int) -> int:
+        return self.flags._symm_off + row * 64 * 8
+
+    def _arrive_ptr(self, ch: int) -> int:
+        return self.arrive.data_ptr() + ch * self.El * 8
+
+    def traffic_matrix(self) -> torch.Tensor:
+        """Token traffic matrix [src, dst] of the last routed step (device tensor)."""
+        return self.traffic
+
+    # ---- forward ---------------------------------------------------------------------------------
+    def route(self, logits: torch.Tensor, bias: Optional[torch.Tensor] = None) -> RouteState:
+        C = self._C
+        T = logits.shape[0]
+        assert T <= self.T and logits.shape[1] == self.E and logits.dtype == torch.float32
+        topk_idx = torch.empty(T, self.K, dtype=torch.int32, device=logits.device)
+        topk_w = torch.empty(T, self.K, dtype=torch.float32, device=logits.device)
+        dest_row = torch.empty(T, self.K, dtype=torch.int32, device=logits.device)
+        nb = (T + C.ROUTE_TOKENS_PER_BLOCK - 1) // C.ROUTE_TOKENS_PER_BLOCK
+        C.route_topk(logits.contiguous(), bias, self.K, topk_idx, topk_w, self.slot_in_block, self.block_cnt[:nb])
+        self.epoch += 1
+        C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
+                      self.send_cnt, self.group_off, self.group_rows, self.arrive_target, self.traffic, 2 if self.training else 1, self.status,
+                      self.timeout_ns)
+        return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows, self.epoch)
+
+    def dispatch(self, x: torch.Tensor, rs: RouteState) -> None:
+        C = self._C
+        if self.fp8:
+            C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, True,
+                            self._off(self.xq_recv), self._off(self.xs_recv), self.arrive._symm_off, 0, 0, self.status, self.timeout_ns, self.comm_ctas)
+        else:
+            C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
+            C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, False,
+                            self._off(self.x_recv), 0, self.arrive._symm_off, 0, 0, self.status, self.timeout_ns, self.comm_ctas)
+
+    def experts_forward(self, w13: torch.Tensor, w2: torch.Tensor, rs: RouteState) -> None:
+        C = self._C
+        gate = (self._arrive_ptr(0), self.arrive_target[0])
+        if self.fp8:
+            C.wait_counters(self._arrive_ptr(0), self.arrive_target[0], self.status, self.timeout_ns)
+            C.dequant_fp8(self.xq_recv, self.xs_recv, self.x_recv)
+            C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
+            gate = None
+        gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate)
+        gemm.grouped_gemm_fwd(self.act, w2, rs.group_off, self.y)
+        C.peer_signal(self.comm.heap, self._flag_off(1), rs.epoch)
+
+    def combine(self, rs: RouteState, weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T = rs.topk_idx.shape[0]
+        if out is None:
+            out = torch.empty(T, self.H, dtype=torch.bfloat16, device=rs.topk_idx.device)
+        self._C.combine_pull(self.comm.heap, self.E, rs.topk_idx, rs.dest_row, weights, self._off(self.y), self._flag_off(1), rs.epoch, out, None, None,
+                             self.H, self.status, self.timeout_ns, self.comm_ctas)
+        return out
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                weights: Optional[torch.Tensor] = None):
+        rs = self.route(logits, bias)
+        self.dispatch(x, rs)
+        self.experts_forward(w13, w2, rs)
+        out = self.combine(rs, rs.topk_w if weights is None else weights)
+        return out, rs
+
+    # ---- backward --------------------------------------------------------------------------------
+    def backward(self, grad_out: torch.Tensor, rs: RouteState, weights: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, dw13: torch.Tensor,
+                 dw2: torch.Tensor):
+        """Returns (grad_x [T, H], grad_weights [T, K]); fills dw13 / dw2."""
+        C = self._C
+        T = rs.topk_idx.shape[0]
+        dev = grad_out.device
+        grad_w = torch.empty(T, self.K, dtype=torch.float32, device=dev)
+        # d(weights): <grad_out[t], y_row(t, j)> - the expert outputs are still in place on the peers.
+        C.combine_pull(self.comm.heap, self.E, rs.topk_idx, rs.dest_row, None, self._off(self.y), self._flag_off(1), rs.epoch, None, grad_out, grad_w,
+                       self.H, self.status, self.timeout_ns, self.comm_ctas)
+        # Transposed combine: push w * grad_out to the expert rows (channel 1).
+        C.zero_pad_rows(self.dy_recv, rs.group_off, rs.group_rows)
+        C.dispatch_push(self.comm.heap, grad_out, rs.topk_idx, weights, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, False, False,
+                        self._off(self.dy_recv), 0, self.arrive._symm_off + self.El * 8, self._flag_off(2), rs.epoch, self.status, self.timeout_ns,
+                        self.comm_ctas)
+        gate = (self._arrive_ptr(1), self.arrive_target[1])
+        gemm.grouped_gemm_dgrad(self.dy_recv, w2, rs.group_off, self.dact, gate=gate)
+        gemm.grouped_gemm_wgrad(self.dy_recv, self.act, rs.group_off, dw2)
+        C.swiglu_bwd(self.gu, self.dact, self.dgu, rs.group_off.data_ptr() + 4 * self.El)
+        gemm.grouped_gemm_dgrad(self.dgu, w13, rs.group_off, self.dx_recv)
+        gemm.grouped_gemm_wgrad(self.dgu, self.x_recv, rs.group_off, dw13)
+        C.peer_signal(self.comm.heap, self._flag_off(3), rs.epoch)
+        grad_x = torch.empty(T, self.H, dtype=torch.bfloat16, device=dev)
+        # Transposed dispatch: every token pulls and sums the gradients of its k rows.
+        C.combine_pull(self.comm.heap, self.E, rs.topk_idx, rs.dest_row, None, self._off(self.dx_recv), self._flag_off(3), rs.epoch, grad_x, None, None,
+                       self.H, self.status, self.timeout_ns, self.comm_ctas)
+        return grad_x, grad_w

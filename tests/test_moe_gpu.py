@@ -1,0 +1,181 @@
+"""MoE kernels and the expert-parallel layer against plain fp32 PyTorch references (single rank;
+the multi-rank path runs in tests/mp_moe_worker.py when at least 2 GPUs are present)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref_forward(x, gate, w13, w2, top_k, bias=None):
+    from fast_b200.models.moe import split_gate_up
+
+    xf = x.float()
+    logits = xf @ gate.float().t()
+    sel = logits + (bias.float() if bias is not None else 0.0)
+    idx = sel.topk(top_k, dim=-1).indices
+    w = torch.softmax(logits.gather(1, idx), dim=-1)
+    w1, w3 = split_gate_up(w13.float())
+    out = torch.zeros_like(xf)
+    for e in range(w13.shape[0]):
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = xf[tok]
+        a = torch.nn.functional.silu(h @ w1[e].t()) * (h @ w3[e].t())
+        out = out.index_add(0, tok, (a @ w2[e].float().t()) * w[tok, slot].unsqueeze(1))
+    return out, idx, w
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9)).item()
+
+
+@pytest.mark.parametrize("E,K", [(8, 2), (256, 8), (64, 6)])
+def test_route_topk_matches_torch(E, K):
+    from fast_b200 import runtime
+
+    C = runtime.ext()
+    T = 1000
+    g = torch.Generator(device="cuda").manual_seed(E)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    bias = torch.randn(E, generator=g, device="cuda") * 1.5
+    nb = (T + C.ROUTE_TOKENS_PER_BLOCK - 1) // C.ROUTE_TOKENS_PER_BLOCK
+    idx = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, K, dtype=torch.float32, device="cuda")
+    slot = torch.zeros(nb * C.ROUTE_TOKENS_PER_BLOCK, K, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(nb, E, dtype=torch.int32, device="cuda")
+    C.route_topk(logits, bias, K, idx, w, slot, cnt)
+    ref_idx = (logits + bias).topk(K, dim=-1).indices
+    assert torch.equal(idx.long(), ref_idx)
+    ref_w = torch.softmax(logits.gather(1, ref_idx), dim=-1)
+    assert torch.allclose(w, ref_w, atol=1e-5)
+    # histogram and stable in-block ranks
+    for b in range(nb):
+        blk = idx[b * 128:(b + 1) * 128].reshape(-1).long()
+        assert torch.equal(cnt[b].long(), torch.bincount(blk, minlength=E))
+    flat = idx.reshape(-1).cpu()
+    s = slot[:T].reshape(-1).cpu()
+    seen = {}
+    for i in range(min(flat.numel(), 128 * K)):
+        e = int(flat[i])
+        assert int(s[i]) == seen.get(e, 0)
+        seen[e] = seen.get(e, 0) + 1
+
+
+def test_elementwise_kernels():
+    from fast_b200 import runtime
+    from fast_b200.models.moe import split_gate_up
+
+    C = runtime.ext()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rows, inter = 300, 384
+    gu = torch.randn(rows, 2 * inter, generator=g, device="cuda").to(torch.bfloat16)
+    act = torch.empty(rows, inter, device="cuda", dtype=torch.bfloat16)
+    C.swiglu_fwd(gu, act)
+    gt, ut = split_gate_up(gu.float().t().reshape(1, 2 * inter, rows))
+    gt, ut = gt[0].t().requires_grad_(), ut[0].t().requires_grad_()
+    ref = torch.nn.functional.silu(gt) * ut
+    assert _rel(act, ref) < 1e-2
+    dact = torch.randn(rows, inter, generator=g, device="cuda").to(torch.bfloat16)
+    dgu = torch.empty_like(gu)
+    C.swiglu_bwd(gu, dact, dgu, 0)
+    ref.backward(dact.float())
+    dg, du = split_gate_up(dgu.float().t().reshape(1, 2 * inter, rows))
+    assert _rel(dg[0].t(), gt.grad) < 1e-2 and _rel(du[0].t(), ut.grad) < 1e-2
+    # AdamW against torch.optim.AdamW on fp32
+    p = torch.randn(4096, generator=g, device="cuda")
+    grad = torch.randn(4096, generator=g, device="cuda").to(torch.bfloat16)
+    pb = p.to(torch.bfloat16)
+    master, m, v = pb.float().clone(), torch.zeros(4096, device="cuda"), torch.zeros(4096, device="cuda")
+    ref_p = pb.float().clone().requires_grad_()
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in (1, 2, 3):
+        C.adamw(pb, master, m, v, grad, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
+        ref_p.grad = grad.float()
+        opt.step()
+    assert torch.allclose(master, ref_p.detach(), atol=1e-5, rtol=1e-5)
+    assert torch.equal(pb, master.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("E,K,H,I,T,fp8", [(4, 2, 256, 256, 300, False), (8, 2, 512, 384, 1000, False), (32, 8, 256, 128, 513, False), (8, 2, 256, 256, 300, True)])
+def test_moe_forward_single_rank(E, K, H, I, T, fp8):
+    from fast_b200.models import MoELayer
+    from fast_b200.parallel import Communicator
+
+    comm = Communicator(heap_bytes=256 << 20, device=0)
+    layer = MoELayer(comm, H, I, E, K, max_tokens=1024, fp8_dispatch=fp8, training=False, router_bias=True)
+    layer.eval()
+    g = torch.Generator(device="cuda").manual_seed(7)
+    layer.router_bias.data = torch.randn(E, generator=g, device="cuda") * 0.5
+    x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        out = layer(x)
+        out2 = layer(x)  # second call: epochs, counters and pads must be reusable
+    comm.check()
+    ref, _, _ = _ref_forward(x, layer.gate, layer.w13, layer.w2, K, layer.router_bias)
+    tol = 6e-2 if fp8 else 2e-2
+    assert _rel(out, ref) < tol
+    assert torch.equal(out, out2)
+    tm = layer.engine.traffic_matrix()
+    assert int(tm.sum().item()) == T * K
+
+
+def test_moe_backward_single_rank():
+    from fast_b200.models import MoELayer
+    from fast_b200.parallel import Communicator
+
+    E, K, H, I, T = 8, 2, 256, 256, 600
+    comm = Communicator(heap_bytes=256 << 20, device=0)
+    layer = MoELayer(comm, H, I, E, K, max_tokens=1024)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16).requires_grad_()
+    gout = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    out = layer(x)
+    out.backward(gout)
+    comm.check()
+    # fp32 reference with autograd
+    xr = x.detach().float().requires_grad_()
+    gate = layer.gate.detach().float().requires_grad_()
+    w13 = layer.w13.detach().float().requires_grad_()
+    w2 = layer.w2.detach().float().requires_grad_()
+    ref, _, _ = _ref_forward(xr, gate, w13, w2, K)
+    ref.backward(gout.float())
+    assert _rel(out, ref) < 2e-2
+    assert _rel(x.grad, xr.grad) < 3e-2
+    assert _rel(layer.w13.grad, w13.grad) < 3e-2
+    assert _rel(layer.w2.grad, w2.grad) < 3e-2
+    assert _rel(layer.gate.grad, gate.grad) < 5e-2
+
+
+def test_block_model_trains():
+    from fast_b200.models import MixtralBlockModel
+    from fast_b200.parallel import Communicator
+    from fast_b200.utils import FusedAdamW
+
+    comm = Communicator(heap_bytes=256 << 20, device=0)
+    model = MixtralBlockModel(comm, vocab=512, hidden=256, inter=256, num_experts=4, top_k=2, max_tokens=512)
+    opt = FusedAdamW(model.expert_parameters(), lr=5e-3)
+    ids = torch.randint(0, 512, (2, 256), device="cuda", generator=torch.Generator(device="cuda").manual_seed(0))
+    losses = []
+    for _ in range(5):
+        opt.zero_grad()
+        loss = model(ids)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.item()))
+    comm.check()
+    assert all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_moe_multi_process():
+    n = min(torch.cuda.device_count(), 8)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+                        "--master-port", "29543", os.path.join(os.path.dirname(__file__), "mp_moe_worker.py")], capture_output=True, text=True, env=env, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "MOE_MP_OK" in r.stdout
