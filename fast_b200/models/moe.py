@@ -69,6 +69,7 @@ class MoELayer(nn.Module):
         """x: [tokens, hidden] bf16 -> [tokens, hidden] bf16."""
         logits = (x @ self.gate.t()).float()
         rs = self.engine.route(logits.detach(), self.router_bias)
+        self.last_route = rs
         if torch.is_grad_enabled() and self.training:
             w = torch.softmax(logits.gather(1, rs.topk_idx.long()), dim=-1)
             return _MoEFunction.apply(x, w, self.w13, self.w2, self.engine, rs)

@@ -123,7 +123,7 @@ class ExpertParallel:
         C.route_topk(logits.contiguous(), bias, self.K, topk_idx, topk_w, self.slot_in_block, self.block_cnt[:nb])
         self.epoch += 1
         C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
-                      self.send_cnt, self.group_off, self.group_rows, self.arrive_target, self.traffic, 2 if self.training else 1, self.status,
+                      self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1, self.status,
                       self.timeout_ns)
         return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows, self.epoch)
 

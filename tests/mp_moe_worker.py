@@ -33,7 +33,7 @@ def main():
             with torch.no_grad():
                 out = layer(x)
             comm.check()
-            ref, _, _ = _ref_forward(x, layer.gate, w13_all, w2_all, K)
+            ref, _, _ = _ref_forward(x, layer.gate, w13_all, w2_all, K, idx=layer.last_route.topk_idx.long())
             assert _rel(out, ref) < 6e-2, f"fp8 forward rank {rank}: {_rel(out, ref)}"
             continue
         for it in range(2):
@@ -45,7 +45,7 @@ def main():
         xr = x.detach().float().requires_grad_()
         gate = layer.gate.detach().float().requires_grad_()
         w13r, w2r = w13_all.float().requires_grad_(), w2_all.float().requires_grad_()
-        ref, _, _ = _ref_forward(xr, gate, w13r, w2r, K)
+        ref, _, _ = _ref_forward(xr, gate, w13r, w2r, K, idx=layer.last_route.topk_idx.long())
         ref.backward(gout.float())
         assert _rel(out, ref) < 2e-2, f"forward rank {rank}: {_rel(out, ref)}"
         assert _rel(x.grad, xr.grad) < 3e-2, f"dx rank {rank}"

@@ -10,13 +10,15 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _ref_forward(x, gate, w13, w2, top_k, bias=None):
+def _ref_forward(x, gate, w13, w2, top_k, bias=None, idx=None):
+    """fp32 reference. `idx` pins the expert choice (near-ties may flip between bf16 and fp32 logits)."""
     from fast_b200.models.moe import split_gate_up
 
     xf = x.float()
     logits = xf @ gate.float().t()
-    sel = logits + (bias.float() if bias is not None else 0.0)
-    idx = sel.topk(top_k, dim=-1).indices
+    if idx is None:
+        sel = logits + (bias.float() if bias is not None else 0.0)
+        idx = sel.topk(top_k, dim=-1).indices
     w = torch.softmax(logits.gather(1, idx), dim=-1)
     w1, w3 = split_gate_up(w13.float())
     out = torch.zeros_like(xf)
@@ -116,7 +118,7 @@ def test_moe_forward_single_rank(E, K, H, I, T, fp8):
         out = layer(x)
         out2 = layer(x)  # second call: epochs, counters and pads must be reusable
     comm.check()
-    ref, _, _ = _ref_forward(x, layer.gate, layer.w13, layer.w2, K, layer.router_bias)
+    ref, _, _ = _ref_forward(x, layer.gate, layer.w13, layer.w2, K, layer.router_bias, idx=layer.last_route.topk_idx.long())
     tol = 6e-2 if fp8 else 2e-2
     assert _rel(out, ref) < tol
     assert torch.equal(out, out2)
@@ -142,7 +144,7 @@ def test_moe_backward_single_rank():
     gate = layer.gate.detach().float().requires_grad_()
     w13 = layer.w13.detach().float().requires_grad_()
     w2 = layer.w2.detach().float().requires_grad_()
-    ref, _, _ = _ref_forward(xr, gate, w13, w2, K)
+    ref, _, _ = _ref_forward(xr, gate, w13, w2, K, idx=layer.last_route.topk_idx.long())
     ref.backward(gout.float())
     assert _rel(out, ref) < 2e-2
     assert _rel(x.grad, xr.grad) < 3e-2
