@@ -43,7 +43,8 @@ class ExpertParallel:
         C = runtime.ext()
         self._C, self.comm = C, comm
         W = comm.world
-        assert num_experts % W == 0 and hidden % 256 == 0 and (2 * inter) % 256 == 0 and inter % 64 == 0
+        assert num_experts % W == 0 and hidden % 256 == 0 and inter % 128 == 0 and top_k <= 8
+        assert not training or inter % 256 == 0, "training needs inter % 256 == 0 (dgrad output tiles are 256 wide)"
         self.E, self.El, self.H, self.I, self.K, self.T = num_experts, num_experts // W, hidden, inter, top_k, max_tokens
         self.fp8, self.training, self.comm_ctas = fp8_dispatch, training, comm_ctas
         worst = W * max_tokens * min(top_k, self.El) + 128 * self.El
