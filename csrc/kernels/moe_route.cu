@@ -202,3 +202,85 @@ cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* grou
 }
 
 }  // namespace fastb
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in route_noalloc.h).
+// ---------------------------------------------------------------------------------------------
+#include <cstdio>
+
+#include "route_noalloc.h"
+
+namespace fastb {
+namespace {
+
+constexpr int kNoAllocMaxTokens = 16384, kNoAllocMaxExperts = 256, kNoAllocMaxTopK = 8;
+constexpr int kNoAllocMaxBlocks = kNoAllocMaxTokens / kRouteTokensPerBlock;
+constexpr size_t kNoAllocCntBytes = sizeof(int) * kNoAllocMaxBlocks * kNoAllocMaxExperts;    // per-block histograms
+constexpr size_t kNoAllocSlotBytes = sizeof(int) * kNoAllocMaxTokens * kNoAllocMaxTopK;       // in-block ranks
+constexpr size_t kNoAllocBytes = kNoAllocCntBytes + kNoAllocSlotBytes;                        // 640 KiB
+
+// Scratch of the allocation-free entry point. In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels receive the device address obtained from it.
+static __device__ __align__(256) unsigned char g_route_scratch[kNoAllocBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_scratch_addr[kMaxDevices] = {};
+thread_local char g_noalloc_error[256] = "";
+
+__global__ void sum_block_counts_kernel(const int* __restrict__ block_cnt, int blocks, int E, int* __restrict__ expert_counts) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int s = 0;
+  for (int b = 0; b < blocks; ++b) s += block_cnt[static_cast<long long>(b) * E + e];
+  expert_counts[e] = s;
+}
+
+int refuse(cudaError_t code, const char* fmt, int a = 0, int b = 0) {
+  snprintf(g_noalloc_error, sizeof(g_noalloc_error), fmt, a, b);
+  return static_cast<int>(code);
+}
+
+}  // namespace
+}  // namespace fastb
+
+extern "C" void fastb_route_topk_noalloc_limits(int* max_tokens, int* max_experts, int* max_top_k) {
+  if (max_tokens) *max_tokens = fastb::kNoAllocMaxTokens;
+  if (max_experts) *max_experts = fastb::kNoAllocMaxExperts;
+  if (max_top_k) *max_top_k = fastb::kNoAllocMaxTopK;
+}
+
+extern "C" const char* fastb_noalloc_last_error(void) { return fastb::g_noalloc_error; }
+
+extern "C" int fastb_route_topk_noalloc(const float* logits, const float* bias, int T, int E, int K, int* topk_idx, float* topk_w,
+                                        int* expert_counts, void* stream_v) {
+  using namespace fastb;
+  g_noalloc_error[0] = '\0';
+  if (!logits || !topk_idx || !topk_w || !expert_counts) return refuse(cudaErrorInvalidValue, "fastb_route_topk_noalloc: null buffer");
+  if (T < 0 || T > kNoAllocMaxTokens) return refuse(cudaErrorInvalidValue, "fastb_route_topk_noalloc: %d tokens exceed the fixed scratch (max %d)", T, kNoAllocMaxTokens);
+  if (E < 1 || E > kNoAllocMaxExperts) return refuse(cudaErrorInvalidValue, "fastb_route_topk_noalloc: %d experts exceed the fixed scratch (max %d)", E, kNoAllocMaxExperts);
+  if (K < 1 || K > kNoAllocMaxTopK || K > E) return refuse(cudaErrorInvalidValue, "fastb_route_topk_noalloc: top-%d is outside 1..min(%d, experts)", K, kNoAllocMaxTopK);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return refuse(e, "fastb_route_topk_noalloc: cudaGetDevice failed");
+  if (dev < 0 || dev >= kMaxDevices) return refuse(cudaErrorInvalidDevice, "fastb_route_topk_noalloc: device index %d not supported (max %d)", dev, kMaxDevices - 1);
+  if (g_scratch_addr[dev] == nullptr) {
+    // Once per device, with that device current: translate the symbol into its device address.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_route_scratch);
+    if (e != cudaSuccess || p == nullptr) return refuse(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "fastb_route_topk_noalloc: cudaGetSymbolAddress failed");
+    g_scratch_addr[dev] = p;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  const int blocks = (T + kRouteTokensPerBlock - 1) / kRouteTokensPerBlock;
+  int* block_cnt = reinterpret_cast<int*>(static_cast<unsigned char*>(g_scratch_addr[dev]));
+  int* slot_in_block = reinterpret_cast<int*>(static_cast<unsigned char*>(g_scratch_addr[dev]) + kNoAllocCntBytes);
+  if (blocks > 0) {
+    e = launch_route_topk(logits, bias, T, E, K, topk_idx, topk_w, slot_in_block, block_cnt, stream);
+    if (e != cudaSuccess) return refuse(e, "fastb_route_topk_noalloc: routing kernel launch failed");
+  }
+  sum_block_counts_kernel<<<(E + 127) / 128, 128, 0, stream>>>(block_cnt, blocks, E, expert_counts);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return refuse(e, "fastb_route_topk_noalloc: count kernel launch failed");
+  note_launch();
+  return 0;
+}
