@@ -116,8 +116,8 @@ def main():
     C = runtime.ext()
     tokens = args.seqs * args.seq_len
     El = EXPERTS // world
-    worst = world * tokens * min(TOP_K, El) + 128 * El
-    cap = worst if args.capacity_factor <= 0 else min(worst, int(args.capacity_factor * tokens * TOP_K) + 128 * El)
+    worst = world * tokens * min(TOP_K, El) + 256 * El  # every expert's rows are padded to 256
+    cap = worst if args.capacity_factor <= 0 else min(worst, int(args.capacity_factor * tokens * TOP_K) + 256 * El)
     heap = 4 * cap * HIDDEN * 2 + (256 << 20)
     comm = Communicator(heap_bytes=heap, device=local, timeout_s=20.0)
     model = MixtralBlockModel(comm, vocab=VOCAB, hidden=HIDDEN, inter=FFN, num_experts=EXPERTS, top_k=TOP_K, max_tokens=tokens, capacity_rows=cap)

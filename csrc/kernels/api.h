@@ -81,6 +81,7 @@ struct GemmArgs {
   // gate_counter[g] >= gate_target[g] (rows pushed by peers have landed). Null = no gate.
   const unsigned long long* gate_counter;
   const unsigned long long* gate_target;
+  int band_rows;           // rows of a raster band (0 = default 4096): tiles are visited band by band, all columns per band
 };
 
 int grouped_gemm_smem_bytes();
@@ -88,6 +89,11 @@ int grouped_gemm_smem_bytes();
 // dgrad A {64,128} B {64,64}; wgrad A {64,64} B {64,64}  ({inner, outer} elements).
 cudaError_t launch_grouped_gemm(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
                                 int ctas, cudaStream_t stream);
+// CTA-pair variant (256 x 256 tiles, cta_group::2). Group offsets must be multiples of 256,
+// fixed_m_tiles counts 256-row tiles, and operand B's boxes are forward {64,128}; dgrad / wgrad
+// boxes are as above.
+cudaError_t launch_grouped_gemm_pair(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
+                                     int ctas, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // MoE routing / dispatch / combine
@@ -99,6 +105,8 @@ constexpr int kRouteTokensPerBlock = 128;  // tokens per routing block (block_cn
 struct SplitsArgs {
   void* const* peer_table;
   int rank, world, num_experts, num_blocks, num_channels;
+  int row_align;               // group row ranges are padded to this many rows (128 or 256)
+  int cap_rows;                // rows of the receive buffers; a step that needs more is refused on every rank
   long long counts_heap_off;   // int [world][E] on every rank
   long long flags_heap_off;    // u64 [world] on every rank: epoch of the last counts row received from each rank
   unsigned long long epoch;
@@ -171,6 +179,15 @@ cudaError_t launch_swiglu_bwd(const __nv_bfloat16* gate_up, const __nv_bfloat16*
                               const int* rows_dev, cudaStream_t stream);
 // Dequantises e4m3 rows with one fp32 scale per 128 elements to bf16.
 cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, cudaStream_t stream);
+// out = scale * sum((a + b)^2) with (a + b) rounded to bf16 first (loss of a residual sum); partial is scratch of partial_len floats.
+cudaError_t launch_sumsq_add(const __nv_bfloat16* a, const __nv_bfloat16* b, long long n, float scale, float* partial, int partial_len, float* out,
+                             cudaStream_t stream);
+// out = bf16(a + b) * (*gscale) * factor (gradient of the above).
+cudaError_t launch_scaled_sum(const __nv_bfloat16* a, const __nv_bfloat16* b, long long n, const float* gscale, float factor, __nv_bfloat16* out,
+                              cudaStream_t stream);
+// Table gradient of an embedding lookup from ids sorted ascending (with their positions); rows of grad_table not named by any id are left as they are.
+cudaError_t launch_embedding_bwd(const long long* sorted_ids, const long long* perm, const __nv_bfloat16* grad_out, __nv_bfloat16* grad_table, long long T,
+                                 int H, cudaStream_t stream);
 // AdamW on bf16 parameters with fp32 master weights and moments.
 cudaError_t launch_adamw(__nv_bfloat16* param, float* master, float* m, float* v, const __nv_bfloat16* grad, long long n, float lr, float beta1,
                          float beta2, float eps, float weight_decay, float bias_c1, float bias_c2, float grad_scale, cudaStream_t stream);

@@ -110,6 +110,83 @@ __global__ void adamw_kernel(uint4* __restrict__ param, float4* __restrict__ mas
   }
 }
 
+// sum((a + b)^2) over n8 chunks of 8 bf16: per-block partial sums, then one block folds them in a
+// fixed order (deterministic).
+__global__ void sumsq_add_partial_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, long long n8, float* __restrict__ partial) {
+  float acc = 0.0f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x[8], y[8];
+    unpack8(a[i], x);
+    unpack8(b[i], y);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const float o = __bfloat162float(__float2bfloat16_rn(x[k] + y[k])); acc = fmaf(o, o, acc); }
+  }
+  __shared__ float s[32];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? s[threadIdx.x] : 0.0f;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) partial[blockIdx.x] = v;
+  }
+}
+__global__ void fold_partials_kernel(const float* __restrict__ partial, int n, float scale, float* __restrict__ out) {
+  __shared__ float s[32];
+  float acc = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) acc += partial[i];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? s[threadIdx.x] : 0.0f;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) *out = v * scale;
+  }
+}
+// grad = (a + b) * (*gscale) * factor, as bf16.
+__global__ void scaled_sum_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, long long n8, const float* __restrict__ gscale, float factor,
+                                  uint4* __restrict__ out) {
+  const float g = (*gscale) * factor;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x[8], y[8], o[8];
+    unpack8(a[i], x);
+    unpack8(b[i], y);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = __bfloat162float(__float2bfloat16_rn(x[k] + y[k])) * g;
+    out[i] = pack8(o);
+  }
+}
+
+// Embedding gradient: ids sorted ascending with their original positions; the warp that sits on the
+// first entry of a run of equal ids sums the run's rows in fp32 (in position order) and writes one
+// bf16 row of the table gradient.
+__global__ void embedding_bwd_kernel(const long long* __restrict__ sorted_ids, const long long* __restrict__ perm, const uint4* __restrict__ grad_out,
+                                     uint4* __restrict__ grad_table, long long T, int H) {
+  const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (i >= T) return;
+  const long long id = sorted_ids[i];
+  if (i > 0 && sorted_ids[i - 1] == id) return;
+  long long end = i + 1;
+  while (end < T && sorted_ids[end] == id) ++end;
+  const int chunks = H / 8;
+  for (int c = lane; c < chunks; c += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (long long j = i; j < end; ++j) {
+      float f[8];
+      unpack8(grad_out[perm[j] * chunks + c], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    }
+    grad_table[id * chunks + c] = pack8(acc);
+  }
+}
+
 int grid_for(long long items) { return static_cast<int>(std::min<long long>((items + 255) / 256, 148 * 8)); }
 
 }  // namespace
@@ -127,6 +204,34 @@ cudaError_t launch_swiglu_bwd(const __nv_bfloat16* gate_up, const __nv_bfloat16*
   if (rows == 0) return cudaSuccess;
   swiglu_bwd_kernel<<<grid_for(rows * inter / 8), 256, 0, stream>>>(reinterpret_cast<const uint4*>(gate_up), reinterpret_cast<const uint4*>(d_act),
                                                                   reinterpret_cast<uint4*>(d_gate_up), rows, inter, rows_dev);
+  note_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_sumsq_add(const __nv_bfloat16* a, const __nv_bfloat16* b, long long n, float scale, float* partial, int partial_len, float* out,
+                             cudaStream_t stream) {
+  if (n % 8 || partial_len < 1) return cudaErrorInvalidValue;
+  const int blocks = std::min(partial_len, grid_for(n / 8));
+  sumsq_add_partial_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b), n / 8, partial);
+  fold_partials_kernel<<<1, 1024, 0, stream>>>(partial, blocks, scale, out);
+  note_launch(2);
+  return cudaGetLastError();
+}
+cudaError_t launch_scaled_sum(const __nv_bfloat16* a, const __nv_bfloat16* b, long long n, const float* gscale, float factor, __nv_bfloat16* out,
+                              cudaStream_t stream) {
+  if (n % 8) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  scaled_sum_kernel<<<grid_for(n / 8), 256, 0, stream>>>(reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b), n / 8, gscale, factor,
+                                                       reinterpret_cast<uint4*>(out));
+  note_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_embedding_bwd(const long long* sorted_ids, const long long* perm, const __nv_bfloat16* grad_out, __nv_bfloat16* grad_table, long long T,
+                                 int H, cudaStream_t stream) {
+  if (H % 8) return cudaErrorInvalidValue;
+  if (T == 0) return cudaSuccess;
+  const long long threads = T * 32;
+  embedding_bwd_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(sorted_ids, perm, reinterpret_cast<const uint4*>(grad_out),
+                                                                                      reinterpret_cast<uint4*>(grad_table), T, H);
   note_launch();
   return cudaGetLastError();
 }

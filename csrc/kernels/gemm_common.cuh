@@ -1,0 +1,100 @@
+// Pieces shared by the one-CTA and the CTA-pair grouped GEMM kernels: tile walk and epilogues.
+#pragma once
+#include "api.h"
+#include "sm100_ptx.cuh"
+
+namespace fastb {
+namespace gemm {
+
+constexpr int BN = 256, BK = 64, UMMA_K = 16;
+
+struct TileCoord {
+  int g, m_idx, n_idx;   // group, tile row inside the group (of the fixed dim for wgrad), tile column
+  int row0;              // first row of the group in the grouped matrix
+  int red_blocks;        // BK steps of the reduction
+};
+
+// Walks the tile space group by group; inside a group, in bands of kBandRows rows: all column tiles
+// of a band are visited (m fastest inside the band) before the next band starts. The tiles that
+// run at the same time then form a roughly square patch of the output, which minimises the
+// operand bytes a wave pulls from DRAM (a wave of p x q tiles reads p A-panels and q B-panels).
+// TILE_M is 128 (one CTA) or 256 (CTA pair).
+constexpr int kDefaultBandRows = 4096;
+template <int TILE_M>
+struct TileWalker {
+  const int* off; int G, tiles_n, fixed_m, red_len; GemmMode mode; int band_rows;
+  int g = 0, base = 0;
+  __device__ bool locate(int tile, TileCoord& c) {
+    while (g < G) {
+      const int r0 = off[g], r1 = off[g + 1];
+      const int mt = mode == GemmMode::kWgrad ? fixed_m : (r1 - r0) / TILE_M;
+      const int cnt = mt * tiles_n;
+      if (tile < base + cnt) {
+        const int local = tile - base;
+        const int kBand = max(1, (band_rows > 0 ? band_rows : kDefaultBandRows) / TILE_M);
+        const int band = local / (kBand * tiles_n), rem = local % (kBand * tiles_n);
+        const int m0 = band * kBand, cur = min(kBand, mt - m0);
+        c.g = g; c.n_idx = rem / cur; c.m_idx = m0 + rem % cur; c.row0 = r0;
+        c.red_blocks = mode == GemmMode::kWgrad ? (r1 - r0) / BK : red_len / BK;
+        return true;
+      }
+      base += cnt; ++g;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ uint4 pack8(const uint32_t* r) {
+  return make_uint4(pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1])), pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                    pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5])), pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7])));
+}
+
+// One thread = one output row: reads its 256 fp32 accumulators from TMEM (t_row = TMEM address of
+// the row's first column) and writes bf16 to global. `zero` writes zeros without touching TMEM.
+__device__ __forceinline__ void epilogue_store_row(__nv_bfloat16* crow, uint32_t t_row, bool zero) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    if (!zero) { ptx::tmem_ld_32x32(t_row + c * 32, r); ptx::tmem_wait_ld(); }
+    else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = 0;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) dst[q] = pack8(r + 8 * q);
+  }
+}
+
+// SwiGLU: the 256 columns of a tile are [128 gate | 128 up] of the same 128 features.
+__device__ __forceinline__ void epilogue_swiglu_row(__nv_bfloat16* arow, __nv_bfloat16* gurow, uint32_t t_row) {
+#pragma unroll 1
+  for (int c = 0; c < BN / 64; ++c) {
+    uint32_t g[32], u[32];
+    ptx::tmem_ld_32x32(t_row + c * 32, g);
+    ptx::tmem_ld_32x32(t_row + BN / 2 + c * 32, u);
+    ptx::tmem_wait_ld();
+    uint4* dst = reinterpret_cast<uint4*>(arow + c * 32);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = silu(__uint_as_float(g[8 * q + i])) * __uint_as_float(u[8 * q + i]);
+      dst[q] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+    }
+    if (gurow) {
+      uint4* dg = reinterpret_cast<uint4*>(gurow + c * 32);
+      uint4* du = reinterpret_cast<uint4*>(gurow + BN / 2 + c * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { dg[q] = pack8(g + 8 * q); du[q] = pack8(u + 8 * q); }
+    }
+  }
+}
+
+}  // namespace gemm
+}  // namespace fastb

@@ -13,16 +13,16 @@
 //
 // The reference has no GEMM of any kind; this is part of the fused MoE path layered on its
 // all-to-all (see SwiGLU epilogue below).
-#include "api.h"
-#include "sm100_ptx.cuh"
+#include "gemm_common.cuh"
 
 namespace fastb {
 
 namespace {
 
 using namespace ptx;
+using namespace gemm;
 
-constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int BM = 128;
 constexpr int kStages = 4;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
@@ -38,40 +38,6 @@ struct __align__(8) SmemCtl {
   int abort_flag;
 };
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + sizeof(SmemCtl);
-
-struct TileCoord {
-  int g, m_idx, n_idx;   // group, tile row inside group (or of the fixed dim for wgrad), tile column
-  int row0;              // first row of the group in the grouped matrix
-  int red_blocks;        // number of BK steps of the reduction
-};
-
-// Walks the tile space in the order [group][n tile][m tile] (m fastest, so that CTAs running
-// side by side share one B tile and stream A through L2).
-struct TileWalker {
-  const int* off; int G, tiles_n, fixed_m, red_len; GemmMode mode;
-  int g = 0, base = 0;
-  __device__ bool locate(int tile, TileCoord& c) {
-    while (g < G) {
-      const int r0 = off[g], r1 = off[g + 1];
-      const int mt = mode == GemmMode::kWgrad ? fixed_m : (r1 - r0) / BM;
-      const int cnt = mt * tiles_n;
-      if (tile < base + cnt) {
-        const int local = tile - base;
-        c.g = g; c.n_idx = local / mt; c.m_idx = local % mt; c.row0 = r0;
-        c.red_blocks = mode == GemmMode::kWgrad ? (r1 - r0) / BK : red_len / BK;
-        return true;
-      }
-      base += cnt; ++g;
-    }
-    return false;
-  }
-};
-
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 template <GemmMode MODE, GemmEpilogue EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -99,7 +65,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
 
-  TileWalker walk{p.group_off, p.num_groups, p.tiles_n, p.fixed_m_tiles, p.red_len, MODE};
+  TileWalker<BM> walk{p.group_off, p.num_groups, p.tiles_n, p.fixed_m_tiles, p.red_len, MODE, p.band_rows};
   TileCoord tc;
 
   if (warp == 0) {
@@ -193,56 +159,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                                         : static_cast<long long>(tc.row0) + tc.m_idx * BM + row_in_tile;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
       if (EPI == GemmEpilogue::kStore) {
-        __nv_bfloat16* crow = p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * BN;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          if (!empty_reduction) { tmem_ld_32x32(t_row + c * 32, r); tmem_wait_ld(); }
-          else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0;
-          }
-          uint4* dst = reinterpret_cast<uint4*>(crow + c * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
-            v.y = pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
-            v.z = pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
-            v.w = pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
-            dst[q] = v;
-          }
-        }
+        epilogue_store_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * BN, t_row, empty_reduction);
       } else {
-        // SwiGLU: the 256 columns of a tile are [128 gate | 128 up] of the same 128 features.
-        __nv_bfloat16* arow = p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (BN / 2);
-        __nv_bfloat16* gurow = p.c2 ? p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * BN : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(t_row + c * 32, g);
-          tmem_ld_32x32(t_row + BN / 2 + c * 32, u);
-          tmem_wait_ld();
-          uint4* dst = reinterpret_cast<uint4*>(arow + c * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float o[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = silu(__uint_as_float(g[8 * q + i])) * __uint_as_float(u[8 * q + i]);
-            dst[q] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
-          }
-          if (gurow) {
-            uint4* dg = reinterpret_cast<uint4*>(gurow + c * 32);
-            uint4* du = reinterpret_cast<uint4*>(gurow + BN / 2 + c * 32);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              dg[q] = make_uint4(pack_bf16(__uint_as_float(g[8 * q + 0]), __uint_as_float(g[8 * q + 1])), pack_bf16(__uint_as_float(g[8 * q + 2]), __uint_as_float(g[8 * q + 3])),
-                                 pack_bf16(__uint_as_float(g[8 * q + 4]), __uint_as_float(g[8 * q + 5])), pack_bf16(__uint_as_float(g[8 * q + 6]), __uint_as_float(g[8 * q + 7])));
-              du[q] = make_uint4(pack_bf16(__uint_as_float(u[8 * q + 0]), __uint_as_float(u[8 * q + 1])), pack_bf16(__uint_as_float(u[8 * q + 2]), __uint_as_float(u[8 * q + 3])),
-                                 pack_bf16(__uint_as_float(u[8 * q + 4]), __uint_as_float(u[8 * q + 5])), pack_bf16(__uint_as_float(u[8 * q + 6]), __uint_as_float(u[8 * q + 7])));
-            }
-          }
-        }
+        epilogue_swiglu_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (BN / 2),
+                            p.c2 ? p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * BN : nullptr, t_row);
       }
       if (!empty_reduction) {
         tc_fence_before_sync();

@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
   const int E = a.num_experts, El = E / a.world;
   for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
   if (threadIdx.x == 0) s_ok = 1;
+  if (*reinterpret_cast<volatile unsigned long long*>(&a.status->abort) != 0ull) return;  // an earlier kernel of this rank refused the step
   __syncthreads();
   if (a.entry_epoch != 0) {
     // Entry handshake: publish that my receive buffers may be written, then wait for the peers.
@@ -80,21 +81,32 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
     }
     const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.H);
     if (!a.fp8) {
-      for (int c = lane; c < chunks; c += 32) {
-        const uint4 v = __ldg(src + c);
-        float f[8];
-        if (a.row_scale) unpack8(v, f);
+      // Four 16-byte chunks per lane in flight before the first store: the loop is bound by the
+      // latency of the local loads otherwise.
+      constexpr int U = 4;
+      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+        uint4 v[U];
 #pragma unroll
-        for (int j = 0; j < kMaxK; ++j) {
-          if (j >= a.K) break;
-          uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + (static_cast<long long>(row_of[j]) * a.H) * 2) + c;
-          if (a.row_scale) {
-            float g[8];
+        for (int u = 0; u < U; ++u)
+          if (c0 + 32 * u < chunks) v[u] = __ldg(src + c0 + 32 * u);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) g[i] = f[i] * scale[j];
-            *out = pack8(g);
-          } else {
-            *out = v;
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + 32 * u;
+          if (c >= chunks) break;
+          float f[8];
+          if (a.row_scale) unpack8(v[u], f);
+#pragma unroll
+          for (int j = 0; j < kMaxK; ++j) {
+            if (j >= a.K) break;
+            uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + (static_cast<long long>(row_of[j]) * a.H) * 2) + c;
+            if (a.row_scale) {
+              float g[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) g[i] = f[i] * scale[j];
+              *out = pack8(g);
+            } else {
+              *out = v[u];
+            }
           }
         }
       }
@@ -140,6 +152,7 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
   __shared__ int s_ok;
   const int El = a.num_experts / a.world;
   if (threadIdx.x == 0) s_ok = 1;
+  if (*reinterpret_cast<volatile unsigned long long*>(&a.status->abort) != 0ull) return;
   __syncthreads();
   if (a.ready_epoch != 0) {
     const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(static_cast<unsigned char*>(a.peer_table[a.rank]) + a.ready_flags_heap_off);
@@ -165,21 +178,29 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
     }
     if (a.dot_out == nullptr) {
       uint4* out = reinterpret_cast<uint4*>(a.out + static_cast<long long>(t) * a.H);
-      for (int c = lane; c < chunks; c += 32) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        uint4 v[kMaxK];
+      constexpr int U = 2;  // two chunks x K rows of peer loads in flight per lane
+      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+        uint4 v[U][kMaxK];
 #pragma unroll
-        for (int j = 0; j < kMaxK; ++j)
-          if (j < a.K) v[j] = __ldcg(rows[j] + c);
+        for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int j = 0; j < kMaxK; ++j) {
-          if (j >= a.K) break;
-          float f[8];
-          unpack8(v[j], f);
+          for (int j = 0; j < kMaxK; ++j)
+            if (j < a.K && c0 + 32 * u < chunks) v[u][j] = __ldcg(rows[j] + c0 + 32 * u);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[j], f[i], acc[i]);
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + 32 * u;
+          if (c >= chunks) break;
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+          for (int j = 0; j < kMaxK; ++j) {
+            if (j >= a.K) break;
+            float f[8];
+            unpack8(v[u][j], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[j], f[i], acc[i]);
+          }
+          out[c] = pack8(acc);
         }
-        out[c] = pack8(acc);
       }
     } else {
       const uint4* g = reinterpret_cast<const uint4*>(a.dot_with + static_cast<long long>(t) * a.H);

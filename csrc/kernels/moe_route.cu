@@ -129,9 +129,27 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
       tot += c;
       if (s < a.rank) before_me += c;
     }
-    s_tot[e] = (tot + 127) / 128 * 128;
+    s_tot[e] = (tot + a.row_align - 1) / a.row_align * a.row_align;
+  }
+  __shared__ int s_over;
+  if (e == 0) s_over = 0;
+  __syncthreads();
+  // Every rank sees the same count matrix, so every rank reaches the same verdict: if any rank's
+  // padded rows exceed the receive capacity, the step is refused everywhere (no rows are sent, the
+  // GEMMs get empty groups) and the status block says how many rows were needed.
+  if (e < W) {
+    int need = 0;
+    for (int q = 0; q < El; ++q) need += s_tot[e * El + q];
+    if (need > a.cap_rows) { atomicMax(&s_over, need); }
   }
   __syncthreads();
+  if (s_over) {
+    if (e == 0) report_failure(a.status, kStatusBadArg, kSiteCapacity, a.rank, static_cast<unsigned long long>(s_over), static_cast<unsigned long long>(a.cap_rows));
+    if (e < E) { a.send_base[e] = 0; a.send_cnt[e] = 0; }
+    if (e <= El) a.group_off[e] = 0;
+    if (e < El) a.group_rows[e] = 0;
+    return;
+  }
   if (e < E) {
     // Row where my first token for expert e lands on its owner: padded sizes of the owner's
     // earlier experts plus the rows of lower-ranked sources for e.
@@ -186,7 +204,7 @@ cudaError_t launch_route_topk(const float* logits, const float* bias, int T, int
 }
 
 cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream) {
-  if (a.num_experts < 1 || a.num_experts > 1024 || a.world < 1 || a.world > a.num_experts || a.num_experts % a.world) return cudaErrorInvalidValue;
+  if ((a.row_align != 128 && a.row_align != 256) || a.num_experts < 1 || a.num_experts > 1024 || a.world < 1 || a.world > a.num_experts || a.num_experts % a.world) return cudaErrorInvalidValue;
   int threads = (std::max(a.num_experts, a.world) + 31) / 32 * 32;
   splits_scan_kernel<<<1, threads, sizeof(int) * (a.num_experts + a.world), stream>>>(a);
   note_launch();

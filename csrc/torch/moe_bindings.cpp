@@ -54,7 +54,7 @@ struct TensorMap2D {
 
 void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2D& b, torch::Tensor group_off, int tiles_n, int fixed_m_tiles,
                   int red_len, int b_rows_per_group, int c_rows_per_group, torch::Tensor c, c10::optional<torch::Tensor> c2, int64_t status_ptr,
-                  uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target) {
+                  uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target, bool pair, int band_rows) {
   TORCH_CHECK(group_off.is_cuda() && group_off.dtype() == torch::kInt32 && group_off.is_contiguous() && group_off.numel() >= 2, "group_off: cuda int32[G+1]");
   TORCH_CHECK(c.is_cuda() && c.dtype() == torch::kBFloat16 && c.dim() == 2 && c.stride(1) == 1, "c: cuda bf16 [rows, cols]");
   TORCH_CHECK(red_len % 64 == 0 && tiles_n >= 1, "reduction length must be a multiple of 64");
@@ -70,13 +70,17 @@ void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2
   }
   g.status = reinterpret_cast<DeviceStatus*>(status_ptr);
   g.timeout_ns = timeout_ns;
+  g.band_rows = band_rows;
   if (gate_counter_ptr != 0) {
     TORCH_CHECK(gate_target.has_value() && gate_target->is_cuda() && gate_target->scalar_type() == torch::kInt64 && gate_target->numel() >= g.num_groups,
                 "gate_target: cuda int64[G]");
     g.gate_counter = reinterpret_cast<const unsigned long long*>(gate_counter_ptr);
     g.gate_target = reinterpret_cast<const unsigned long long*>(gate_target->data_ptr());
   }
-  cu_check(launch_grouped_gemm(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, g, ctas, stream_now()), "grouped_gemm launch");
+  if (pair)
+    cu_check(launch_grouped_gemm_pair(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, g, ctas, stream_now()), "grouped_gemm pair launch");
+  else
+    cu_check(launch_grouped_gemm(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, g, ctas, stream_now()), "grouped_gemm launch");
 }
 
 void route_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int K, torch::Tensor topk_idx, torch::Tensor topk_w,
@@ -93,8 +97,10 @@ void route_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int K, 
 
 void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint64_t epoch, torch::Tensor block_cnt, torch::Tensor block_base,
                  torch::Tensor send_base, torch::Tensor send_cnt, torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor arrive_target,
-                 c10::optional<torch::Tensor> traffic, int num_channels, const StatusPy& st, uint64_t timeout_ns) {
+                 c10::optional<torch::Tensor> traffic, int num_channels, int row_align, int cap_rows, const StatusPy& st, uint64_t timeout_ns) {
   SplitsArgs a{};
+  a.row_align = row_align;
+  a.cap_rows = cap_rows;
   a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
   a.num_experts = static_cast<int>(send_base.numel()); a.num_blocks = static_cast<int>(block_cnt.numel() / a.num_experts); a.num_channels = num_channels;
   a.counts_heap_off = counts_off; a.flags_heap_off = flags_off; a.epoch = epoch;
@@ -181,6 +187,24 @@ void bind_moe(py::module_& m) {
     want(q, torch::kUInt8, "q"); want(scales, torch::kFloat32, "scales"); want(out, torch::kBFloat16, "out");
     cu_check(launch_dequant_fp8(q.data_ptr<uint8_t>(), scales.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), q.size(0),
                                 static_cast<int>(q.size(1)), stream_now()), "dequant_fp8");
+  });
+  m.def("sumsq_add", [](torch::Tensor a, torch::Tensor b, double scale, torch::Tensor partial, torch::Tensor out) {
+    want(a, torch::kBFloat16, "a"); want(b, torch::kBFloat16, "b"); want(partial, torch::kFloat32, "partial"); want(out, torch::kFloat32, "out");
+    TORCH_CHECK(a.numel() == b.numel(), "sumsq_add: shapes");
+    cu_check(launch_sumsq_add(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), a.numel(),
+                              static_cast<float>(scale), partial.data_ptr<float>(), static_cast<int>(partial.numel()), out.data_ptr<float>(), stream_now()), "sumsq_add");
+  });
+  m.def("scaled_sum", [](torch::Tensor a, torch::Tensor b, torch::Tensor gscale, double factor, torch::Tensor out) {
+    want(a, torch::kBFloat16, "a"); want(b, torch::kBFloat16, "b"); want(gscale, torch::kFloat32, "gscale"); want(out, torch::kBFloat16, "out");
+    cu_check(launch_scaled_sum(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), a.numel(),
+                               gscale.data_ptr<float>(), static_cast<float>(factor), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), stream_now()), "scaled_sum");
+  });
+  m.def("embedding_bwd", [](torch::Tensor sorted_ids, torch::Tensor perm, torch::Tensor grad_out, torch::Tensor grad_table) {
+    want(sorted_ids, torch::kInt64, "sorted_ids"); want(perm, torch::kInt64, "perm"); want(grad_out, torch::kBFloat16, "grad_out");
+    want(grad_table, torch::kBFloat16, "grad_table");
+    cu_check(launch_embedding_bwd(reinterpret_cast<const long long*>(sorted_ids.data_ptr()), reinterpret_cast<const long long*>(perm.data_ptr()),
+                                  reinterpret_cast<const __nv_bfloat16*>(grad_out.data_ptr()), reinterpret_cast<__nv_bfloat16*>(grad_table.data_ptr()),
+                                  sorted_ids.numel(), static_cast<int>(grad_out.size(1)), stream_now()), "embedding_bwd");
   });
   m.def("adamw", [](torch::Tensor param, torch::Tensor master, torch::Tensor m1, torch::Tensor v, torch::Tensor grad, double lr, double b1, double b2,
                     double eps, double wd, int64_t step, double grad_scale) {

@@ -34,9 +34,13 @@ def main():
     ap.add_argument("--inter", type=int, default=14336)
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--kernel", default="pair", choices=["pair", "one"])
+    ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--sustain-s", type=float, default=0.0, help="also time back-to-back launches for this many seconds (power-capped regime)")
     a = ap.parse_args()
+    gemm.USE_PAIR = a.kernel == "pair"
     G, H, I = a.experts, a.hidden, a.inter
-    per = a.rows // G // 128 * 128
+    per = a.rows // G // 256 * 256
     R = per * G
     dev = "cuda"
     off = torch.arange(G + 1, device=dev, dtype=torch.int32) * per
@@ -61,9 +65,27 @@ def main():
     }
     out = {}
     for name, (fn, flops) in cases.items():
+        if a.sustain_s > 0:
+            break
         ms = _time(fn, a.iters)
         out[name] = {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1)}
     gemm.check()
+    if a.sustain_s > 0:
+        def sustained(fn, flops):
+            ms1 = _time(fn, 3, 1)
+            n = max(3, int(a.sustain_s * 1e3 / ms1))
+            ms = _time(fn, n, 0)
+            return {"ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 1), "launches": n}
+        for name, (fn, flops) in cases.items():
+            out["sustained_" + name] = sustained(fn, flops)
+        if not a.no_cublas:
+            def cublas_fwd_s():
+                for g in range(G):
+                    torch.matmul(x[g * per:(g + 1) * per], w13[g].t(), out=gu[g * per:(g + 1) * per])
+            out["sustained_cublas_fwd_w13"] = sustained(cublas_fwd_s, 2 * R * H * 2 * I)
+    if a.no_cublas:
+        print(json.dumps({"kernel": a.kernel, "rows": R, "hidden": H, "inter": I, "experts": G, **out}))
+        return
     # cuBLAS reference for the same math, expert by expert
     def cublas_fwd():
         for g in range(G):
@@ -75,7 +97,7 @@ def main():
             torch.matmul(gu[g * per:(g + 1) * per].t(), x[g * per:(g + 1) * per], out=dw13[g])
     ms = _time(cublas_wgrad, a.iters)
     out["cublas_wgrad_w13"] = {"ms": round(ms, 3), "tflops": round(2 * R * H * 2 * I / ms / 1e9, 1)}
-    print(json.dumps({"rows": R, "hidden": H, "inter": I, "experts": G, **out}))
+    print(json.dumps({"kernel": a.kernel, "rows": R, "hidden": H, "inter": I, "experts": G, **out}))
 
 
 if __name__ == "__main__":

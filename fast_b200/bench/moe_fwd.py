@@ -1,0 +1,177 @@
+"""MoE expert-parallel forward latency (DeepSeek-V3-like shapes): dispatch, experts, combine.
+
+    torchrun --nproc-per-node N -m fast_b200.bench.moe_fwd [--tokens 4096 --hidden 7168 --inter 2048
+        --experts-per-gpu 32 --top-k 8 --fp8]
+
+4096 tokens per rank, 32 routed experts per GPU, top-8 softmax routing of N(0,1) gate logits plus a
+per-expert N(0,1.5) bias (skew), dispatch in bf16 or e4m3 with 1x128 scales, SwiGLU experts with
+random-init bf16 weights (std 0.02), top-k weighted bf16 combine. Device-timed per phase with CUDA
+events, max over ranks. The NCCL column runs the same layer with torch.distributed
+all_to_all_single for both exchanges and torch ops for permute / reduce.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .. import runtime
+from ..parallel import Communicator
+from ..parallel.ep import ExpertParallel
+
+
+def _max_over_ranks(vals, world):
+    t = torch.tensor(vals, device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
+
+
+def nccl_reference_layer(x, idx, w, w13, w2, world, E):
+    """dispatch -> experts -> combine with NCCL all-to-all and torch ops (the baseline path)."""
+    from ..models.moe import split_gate_up
+
+    T, K = idx.shape
+    El = E // world
+    flat = idx.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    tok = order // K
+    send = x[tok]
+    counts = torch.bincount(flat, minlength=E)
+    recv_counts = torch.empty_like(counts)
+    if world > 1:
+        dist.all_to_all_single(recv_counts, counts)
+    else:
+        recv_counts.copy_(counts)
+    in_splits = counts.view(world, El).sum(1).tolist()
+    out_splits = recv_counts.view(world, El).sum(1).tolist()
+    recv = torch.empty(sum(out_splits), x.shape[1], dtype=x.dtype, device=x.device)
+    if world > 1:
+        dist.all_to_all_single(recv, send, out_splits, in_splits)
+    else:
+        recv.copy_(send)
+    # rows arrive grouped by source rank then expert; regroup by expert
+    rc = recv_counts.view(world, El)
+    eid = torch.repeat_interleave(torch.arange(El, device=x.device).repeat(world), rc.reshape(-1))
+    perm = torch.argsort(eid, stable=True)
+    h = recv[perm]
+    w1, w3 = split_gate_up(w13)
+    out = torch.empty_like(h)
+    start = 0
+    per_e = rc.sum(0).tolist()
+    for e in range(El):
+        n = per_e[e]
+        if n:
+            seg = h[start:start + n]
+            out[start:start + n] = (torch.nn.functional.silu(seg @ w1[e].t()) * (seg @ w3[e].t())) @ w2[e].t()
+        start += n
+    back = torch.empty_like(out)
+    back[perm] = out
+    ret = torch.empty_like(send)
+    if world > 1:
+        dist.all_to_all_single(ret, back, in_splits, out_splits)
+    else:
+        ret.copy_(back)
+    y = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
+    y.index_add_(0, tok, ret.float() * w.reshape(-1)[order].unsqueeze(1))
+    return y.to(x.dtype)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--inter", type=int, default=2048)
+    ap.add_argument("--experts-per-gpu", type=int, default=32)
+    ap.add_argument("--top-k", type=int, default=8)
+    ap.add_argument("--fp8", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--skip-nccl", action="store_true")
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    E, K, H, I, T = a.experts_per_gpu * world, a.top_k, a.hidden, a.inter, a.tokens
+    El = a.experts_per_gpu
+    cap = world * T * min(K, El) + 256 * El
+    comm = Communicator(heap_bytes=int(cap * H * (3 if a.fp8 else 4.2)) + (256 << 20), device=local, timeout_s=20.0)
+    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=a.fp8, training=False)
+    g = torch.Generator(device="cuda").manual_seed(7)      # same on every rank: gate and bias are replicated
+    bias = torch.randn(E, generator=g, device="cuda") * 1.5
+    gr = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x = torch.randn(T, H, generator=gr, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=gr, device="cuda")
+    w13 = (torch.randn(El, 2 * I, H, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(El, H, I, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
+    C = runtime.ext()
+
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    acc = [0.0] * 4
+    out = None
+    for it in range(a.warmup + a.iters):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev[0].record()
+        rs = eng.route(logits, bias)
+        ev[1].record()
+        eng.dispatch(x, rs)
+        if a.fp8:
+            pass
+        C.wait_counters(eng._arrive_ptr(0), eng.arrive_target[0], eng.status, eng.timeout_ns)  # phase boundary for timing only
+        ev[2].record()
+        eng.experts_forward(w13, w2, rs)
+        ev[3].record()
+        out = eng.combine(rs, rs.topk_w)
+        ev[4].record()
+        torch.cuda.synchronize()
+        if it >= a.warmup:
+            for p in range(4):
+                acc[p] += ev[p].elapsed_time(ev[p + 1]) * 1e3 / a.iters
+    comm.check()
+    route_us, dispatch_us, experts_us, combine_us = _max_over_ranks(acc, world)
+    tm = eng.traffic_matrix().cpu().numpy()
+    res = {"bench": "moe_forward", "world": world, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K, "dispatch_dtype": "fp8_e4m3_1x128" if a.fp8 else "bf16",
+           "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1), "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1),
+           "layer_us": round(route_us + dispatch_us + experts_us + combine_us, 1),
+           "max_rows_in": int(tm.sum(0).max()), "max_rows_out": int(tm.sum(1).max())}
+    row_bytes = H * (1 if a.fp8 else 2) + (H // 128 * 4 if a.fp8 else 0)
+    off_in = int((tm.sum(0) - tm.diagonal()).max()) if world > 1 else 0
+    off_out = int((tm.sum(1) - tm.diagonal()).max()) if world > 1 else 0
+    if world > 1:
+        res["dispatch_bound_us_at_770GBps"] = round(max(off_in, off_out) * row_bytes / 770e9 * 1e6, 1)
+        res["combine_bound_us_at_770GBps"] = round(max(off_in, off_out) * H * 2 / 770e9 * 1e6, 1)
+    flops = 2.0 * int(tm.sum(0)[rank]) * H * I * 3
+    res["experts_tflops_rank0"] = round(flops / (experts_us * 1e-6) / 1e12, 1) if rank == 0 else None
+    if not a.skip_nccl:
+        idx, w = rs.topk_idx, rs.topk_w
+        for _ in range(2):
+            ref = nccl_reference_layer(x, idx, w, w13, w2, world, E)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = max(3, a.iters // 4)
+        e0.record()
+        for _ in range(n):
+            ref = nccl_reference_layer(x, idx, w, w13, w2, world, E)
+        e1.record()
+        torch.cuda.synchronize()
+        res["nccl_torch_layer_us"] = round(_max_over_ranks([e0.elapsed_time(e1) * 1e3 / n], world)[0], 1)
+        err = ((out.float() - ref.float()).abs().max() / (ref.float().abs().max() + 1e-9)).item()
+        res["max_rel_err_vs_nccl_torch"] = round(err, 5)
+    if rank == 0:
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

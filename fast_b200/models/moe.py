@@ -11,6 +11,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
+from ..ops import fused
 from ..parallel.comm import Communicator
 from ..parallel.ep import ExpertParallel
 
@@ -98,10 +99,9 @@ class MixtralBlockModel(nn.Module):
         return [self.moe.w13, self.moe.w2]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        h = torch.nn.functional.embedding(token_ids.reshape(-1), self.embed)
+        h = fused.embedding(token_ids.reshape(-1), self.embed)
         hn = torch.nn.functional.rms_norm(h, (h.shape[-1],), self.norm_w, self.eps)
-        out = h + self.moe(hn)
-        return out.float().pow(2).mean()
+        return fused.residual_mean_square(h, self.moe(hn))
 
 
 @torch.no_grad()

@@ -6,6 +6,7 @@ between a group's real end and its padded end are zero.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -15,6 +16,16 @@ from .. import runtime
 FORWARD, DGRAD, WGRAD = 0, 1, 2
 STORE, SWIGLU = 0, 1
 _BM, _BN, _BK = 128, 256, 64
+# CTA-pair kernel (256 x 256 tiles, cta_group::2); set False to fall back to the one-CTA kernel.
+USE_PAIR = os.environ.get("FASTB_GEMM", "pair") != "one"
+# Rows of a raster band (see csrc/kernels/gemm_common.cuh); 0 = kernel default.
+BAND_ROWS = int(os.environ.get("FASTB_BAND", "0"))
+
+
+def row_align() -> int:
+    """Rows every group must be padded to for the kernel in use."""
+    return 256 if USE_PAIR else 128
+
 
 _status = None
 _maps: dict = {}
@@ -51,8 +62,9 @@ def _ctas() -> int:
 
 
 def pad_group_offsets(counts: torch.Tensor) -> torch.Tensor:
-    """int32[G+1] offsets with every group rounded up to 128 rows (host/torch helper for tests)."""
-    padded = (counts.to(torch.int64) + 127) // 128 * 128
+    """int32[G+1] offsets with every group rounded up to row_align() rows (host/torch helper for tests)."""
+    ra = row_align()
+    padded = (counts.to(torch.int64) + ra - 1) // ra * ra
     off = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=counts.device)
     off[1:] = torch.cumsum(padded, 0)
     return off.to(torch.int32)
@@ -71,8 +83,8 @@ def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, 
     assert a.shape[1] == K and K % _BK == 0 and N % _BN == 0 and a.shape[0] % _BM == 0
     assert out.shape[0] == a.shape[0] and out.shape[1] == (N // 2 if swiglu else N)
     C = runtime.ext()
-    C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), _BN), group_off, N // _BN, 0, K, N, 0, out,
-                   gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)))
+    C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), 128 if USE_PAIR else _BN), group_off, N // _BN, 0, K, N,
+                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
     return out
 
 
@@ -82,7 +94,7 @@ def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tenso
     assert dy.shape[1] == N and N % _BK == 0 and K % _BN == 0 and dy.shape[0] % _BM == 0
     C = runtime.ext()
     C.grouped_gemm(DGRAD, STORE, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)))
+                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
     return out
 
 
@@ -90,8 +102,9 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, group_off: torch.Tenso
     """out[g] = dy[rows of g].T @ x[rows of g]  (dy [R, N], x [R, K], out [G, N, K]). Rows between a
     group's real end and its padded end must be zero in at least one operand and finite in both."""
     G, N, K = out.shape
-    assert dy.shape[1] == N and x.shape[1] == K and N % _BM == 0 and K % _BN == 0
+    bm = 256 if USE_PAIR else _BM
+    assert dy.shape[1] == N and x.shape[1] == K and N % bm == 0 and K % _BN == 0
     C = runtime.ext()
-    C.grouped_gemm(WGRAD, STORE, _tmap(dy, _BK), _tmap(x, _BK), group_off, K // _BN, N // _BM, 0, 0, N, out.view(G * N, K), None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas(), 0, None)
+    C.grouped_gemm(WGRAD, STORE, _tmap(dy, _BK), _tmap(x, _BK), group_off, K // _BN, N // bm, 0, 0, N, out.view(G * N, K), None, _st().ptr(),
+                   int(timeout_s * 1e9), _ctas(), 0, None, USE_PAIR, BAND_ROWS)
     return out

@@ -39,17 +39,19 @@ class RouteState:
 
 class ExpertParallel:
     def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
-                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: int = 64):
+                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None):
         C = runtime.ext()
         self._C, self.comm = C, comm
         W = comm.world
         assert num_experts % W == 0 and hidden % 256 == 0 and inter % 128 == 0 and top_k <= 8
         assert not training or inter % 256 == 0, "training needs inter % 256 == 0 (dgrad output tiles are 256 wide)"
         self.E, self.El, self.H, self.I, self.K, self.T = num_experts, num_experts // W, hidden, inter, top_k, max_tokens
-        self.fp8, self.training, self.comm_ctas = fp8_dispatch, training, comm_ctas
-        worst = W * max_tokens * min(top_k, self.El) + 128 * self.El
+        self.fp8, self.training = fp8_dispatch, training
+        # dispatch / combine run alone on the stream: fill the machine (4 CTAs of 256 threads per SM)
+        self.comm_ctas = comm_ctas or 4 * torch.cuda.get_device_properties(comm.device).multi_processor_count
+        worst = W * max_tokens * min(top_k, self.El) + 256 * self.El
         self.cap = int(capacity_rows) if capacity_rows else worst
-        self.cap = (min(self.cap, worst) + 127) // 128 * 128
+        self.cap = (min(self.cap, worst) + 255) // 256 * 256
         dev = comm.device
         i32 = dict(dtype=torch.int32, device=dev)
         # symmetric: control words
@@ -124,7 +126,8 @@ class ExpertParallel:
         C.route_topk(logits.contiguous(), bias, self.K, topk_idx, topk_w, self.slot_in_block, self.block_cnt[:nb])
         self.epoch += 1
         C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
-                      self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1, self.status,
+                      self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1,
+                      gemm.row_align(), self.cap, self.status,
                       self.timeout_ns)
         return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows, self.epoch)
 

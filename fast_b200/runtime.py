@@ -34,7 +34,7 @@ def available() -> bool:
 
 
 SITE_NAMES = {1: "entry-ready", 2: "balance-arrival", 3: "rail-arrival", 4: "output-arrival", 5: "counts-arrival",
-              6: "combine-ready", 7: "buffer-reuse", 8: "mbarrier", 9: "test-probe"}
+              6: "combine-ready", 7: "buffer-reuse", 8: "mbarrier", 9: "test-probe", 10: "receive-capacity"}
 
 
 class CollectiveTimeout(RuntimeError):
@@ -42,4 +42,7 @@ class CollectiveTimeout(RuntimeError):
 
     def __init__(self, code, site, detail, seen, want):
         self.code, self.site, self.detail, self.seen, self.want = code, site, detail, seen, want
-        super().__init__(f"device wait gave up at {SITE_NAMES.get(site, site)} (detail {detail}): saw {seen}, wanted {want}")
+        if site == 10:
+            super().__init__(f"MoE step refused: a rank needs {seen} receive rows but capacity_rows is {want}")
+        else:
+            super().__init__(f"device wait gave up at {SITE_NAMES.get(site, site)} (detail {detail}): saw {seen}, wanted {want}")

@@ -1,0 +1,84 @@
+"""CPU rank model of the executor: correctness of the multi-rank wait/signal logic and host-made
+failures (absent rank, withheld signal, mismatched matrices over gloo)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from fast_b200 import sched
+from fast_b200.parallel.host_executor import HostExecutor, HostTimeout
+from fast_b200.sched import PlanKind, Topology
+
+
+def _inputs(plan, ub, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, 256, int(plan.buffers[r, 0]) * ub, dtype=np.uint8) for r in range(plan.matrix.shape[0])]
+
+
+@pytest.mark.parametrize("servers,gpus", [(4, 1), (2, 2), (2, 3), (1, 4)])
+@pytest.mark.parametrize("kind", [PlanKind.STAGED, PlanKind.SINGLE_BURST, PlanKind.FANOUT, PlanKind.SPREAD_OUT])
+def test_threads_match_sequential_replay(servers, gpus, kind):
+    n = servers * gpus
+    m = sched.workload_uniform(n, 200, 5 + n)
+    plan = sched.build_plan(m, Topology(servers, gpus), kind=kind)
+    ub = 3
+    ins = _inputs(plan, ub)
+    want = [np.zeros(int(plan.buffers[r, 1]) * ub, dtype=np.uint8) for r in range(n)]
+    plan.execute_on_host(ub, ins, want)
+    got = HostExecutor(plan, unit_bytes=ub, chunk_bytes=64).run(ins)
+    for r in range(n):
+        assert np.array_equal(got[r], want[r])
+
+
+def test_absent_rank_is_reported_not_hung():
+    m = sched.workload_uniform(4, 50, 1, zero_diag=True)
+    plan = sched.build_plan(m, Topology.flat(4))
+    ex = HostExecutor(plan, timeout_s=0.2, faults={"absent_rank": 2})
+    with pytest.raises(HostTimeout) as e:
+        ex.run(_inputs(plan, 1))
+    assert e.value.site in (1, 4) and (e.value.site != 1 or e.value.detail == 2)
+
+
+def test_withheld_signal_times_out_at_the_receiver():
+    m = np.array([[0, 100], [100, 0]], dtype=np.int64)
+    plan = sched.build_plan(m, Topology.flat(2), kind=PlanKind.FANOUT)
+    ex = HostExecutor(plan, chunk_bytes=32, timeout_s=0.2, faults={"drop_signal": (0, 1)})
+    with pytest.raises(HostTimeout) as e:
+        ex.run(_inputs(plan, 1))
+    assert e.value.rank == 1 and e.value.site == 4 and e.value.seen == 100 - 32 and e.value.want == 100
+
+
+def test_hierarchical_withheld_rail_signal_blocks_redistribution():
+    m = np.zeros((4, 4), dtype=np.int64)
+    m[0, 3] = 64  # server 0 gpu 0 -> server 1 gpu 1: rail to (1,0) then redistribute
+    plan = sched.build_plan(m, Topology(2, 2))
+    rail_src = int(plan.ops[plan.ops[:, 0] == sched.PHASE_RAIL][0, 2])
+    ex = HostExecutor(plan, chunk_bytes=1 << 20, timeout_s=0.2, faults={"drop_signal": (rail_src, 0)})
+    with pytest.raises(HostTimeout) as e:
+        ex.run(_inputs(plan, 1))
+    assert e.value.site in (2, 3, 4)
+
+
+def test_mismatched_matrices_detected_over_gloo(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text(
+        "import os, sys, numpy as np, torch.distributed as dist\n"
+        f"sys.path.insert(0, {os.path.dirname(os.path.dirname(os.path.abspath(__file__)))!r})\n"
+        "from fast_b200.parallel.host_executor import check_same_plan_inputs\n"
+        "dist.init_process_group('gloo')\n"
+        "r = dist.get_rank()\n"
+        "m = np.full((2, 2), 7, dtype=np.int64)\n"
+        "check_same_plan_inputs(m)\n"
+        "m[0, 1] += r\n"
+        "try:\n"
+        "    check_same_plan_inputs(m)\n"
+        "    print('MISSED')\n"
+        "except RuntimeError as e:\n"
+        "    print('DETECTED')\n"
+        "dist.destroy_process_group()\n")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29571", str(script)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.count("DETECTED") == 2 and "MISSED" not in r.stdout

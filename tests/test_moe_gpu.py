@@ -103,6 +103,24 @@ def test_elementwise_kernels():
     assert torch.equal(pb, master.to(torch.bfloat16))
 
 
+def test_fused_embedding_and_loss_match_torch():
+    from fast_b200.ops import fused
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    table = (torch.randn(300, 256, generator=g, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    ids = torch.randint(0, 300, (4, 500), generator=g, device="cuda")
+    other = (torch.randn(2000, 256, generator=g, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    loss = fused.residual_mean_square(fused.embedding(ids.reshape(-1), table), other)
+    loss.backward()
+    t2 = table.detach().clone().requires_grad_()
+    o2 = other.detach().clone().requires_grad_()
+    ref = (torch.nn.functional.embedding(ids.reshape(-1), t2) + o2).float().pow(2).mean()
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 1e-3 * abs(ref.item())
+    assert _rel(other.grad, o2.grad) < 2e-2
+    assert _rel(table.grad, t2.grad) < 2e-2
+
+
 @pytest.mark.parametrize("E,K,H,I,T,fp8", [(4, 2, 256, 256, 300, False), (8, 2, 512, 384, 1000, False), (32, 8, 256, 128, 513, False), (8, 2, 256, 256, 300, True)])
 def test_moe_forward_single_rank(E, K, H, I, T, fp8):
     from fast_b200.models import MoELayer
@@ -124,6 +142,25 @@ def test_moe_forward_single_rank(E, K, H, I, T, fp8):
     assert torch.equal(out, out2)
     tm = layer.engine.traffic_matrix()
     assert int(tm.sum().item()) == T * K
+
+
+def test_receive_capacity_guard_refuses_step():
+    """A step that needs more receive rows than the buffers hold is refused on the device
+    (no row is written out of bounds) and reported through the status block."""
+    from fast_b200 import runtime
+    from fast_b200.models import MoELayer
+    from fast_b200.parallel import Communicator
+
+    comm = Communicator(heap_bytes=128 << 20, device=0)
+    layer = MoELayer(comm, 256, 256, 4, 2, max_tokens=1024, training=False, capacity_rows=512)
+    layer.eval()
+    x = torch.randn(900, 256, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        layer(x)  # needs ~1800 rows (+ padding) > 512
+    with pytest.raises(runtime.CollectiveTimeout) as e:
+        comm.check()
+    assert e.value.site == 10 and e.value.want == 512 and e.value.seen > 512
+    assert int((torch.ones(8, device="cuda") * 3).sum().item()) == 24  # context still healthy
 
 
 def test_moe_backward_single_rank():
