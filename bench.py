@@ -41,6 +41,13 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.t_begin, self.t_end = 0.0, float("inf")
+
+    def window_begin(self):
+        self.t_begin = time.monotonic()
+
+    def window_end(self):
+        self.t_end = time.monotonic()
 
     def start(self):
         try:
@@ -53,7 +60,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -64,7 +71,8 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons, pw = [], [], set(), []
-        for r in self.rows:
+        inside = [r for t, r in self.rows if self.t_begin <= t <= self.t_end + 0.15]
+        for r in inside or [r for _, r in self.rows[-3:]]:  # nvidia-smi can start slowly: fall back to the latest samples
             if len(r) < 7:
                 continue
             try:
@@ -95,6 +103,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=SEQS)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--capacity-factor", type=float, default=0.0, help="receive rows per rank as a multiple of tokens*top_k (0 = worst case)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the skewed all-to-all(v) comparison that follows the training benchmark when N > 1")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -118,7 +127,7 @@ def main():
     El = EXPERTS // world
     worst = world * tokens * min(TOP_K, El) + 256 * El  # every expert's rows are padded to 256
     cap = worst if args.capacity_factor <= 0 else min(worst, int(args.capacity_factor * tokens * TOP_K) + 256 * El)
-    heap = 4 * cap * HIDDEN * 2 + (256 << 20)
+    heap = 4 * cap * HIDDEN * 2 + (256 << 20) + (0 if world == 1 or args.no_extras else (1100 << 20))
     comm = Communicator(heap_bytes=heap, device=local, timeout_s=20.0)
     model = MixtralBlockModel(comm, vocab=VOCAB, hidden=HIDDEN, inter=FFN, num_experts=EXPERTS, top_k=TOP_K, max_tokens=tokens, capacity_rows=cap)
     opt_experts = FusedAdamW(model.expert_parameters(), lr=1e-4, weight_decay=0.01)
@@ -148,14 +157,15 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    sampler.start()  # started before the warm-up so that it is already streaming when the timed region begins
     for i in range(warmup):
         train_step(dev_ids[i % n_batches])
     comm.check()
 
     # ---- device-timed: K steps, CUDA events, max over ranks ------------------------------------
-    sampler = ClockSampler(local)
     fence()
-    sampler.start()
+    sampler.window_begin()
     launches0 = C.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -163,6 +173,7 @@ def main():
         train_step(dev_ids[i % n_batches])
     e1.record()
     fence()
+    sampler.window_end()
     launches = C.launch_count() - launches0
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
@@ -179,6 +190,14 @@ def main():
     fence()
     e2e_s = time.perf_counter() - t0
     comm.check()
+
+    # ---- collective sub-metric (N > 1): skewed all-to-all(v), this runtime vs NCCL on the same ranks ----
+    a2av = None
+    if world > 1 and not args.no_extras:
+        from fast_b200.bench.a2a import skewed_point
+
+        a2av = skewed_point(comm, 256 << 20, 1.0, matrices=3, iters=5, warmup=3)
+        a2av["speedup_vs_nccl"] = round(a2av["nccl_alltoallv"]["ms"] / min(a2av["ours_fanout"]["ms"], a2av["ours_staged"]["ms"]), 3)
 
     t = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
     if world > 1:
@@ -198,6 +217,7 @@ def main():
             "clocks": clocks,
             "e2e": {"value": round(total_tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
                     "h2d_bytes_per_step": host_ids[0].numel() * host_ids[0].element_size(), "d2h_bytes_per_step": 4, "last_loss": last},
+            "alltoallv_skewed": a2av,
             "gpu_launches": int(launches),
             "gpu_launches_per_step": launches / max(args.steps, 1),
         }

@@ -48,31 +48,33 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
     return c;
   };
   auto emit_interleaved = [&](const std::vector<const Op*>& ops) {
-    // Round-robin over the ops of a slot, one chunk each, until all are exhausted.
-    std::vector<int64_t> done(ops.size(), 0);
-    bool any = true;
-    while (any) {
-      any = false;
-      for (size_t k = 0; k < ops.size(); ++k) {
-        const Op& o = *ops[k];
-        const int64_t total = o.len * ub;
-        if (done[k] >= total) continue;
-        const int64_t c = std::min(chunk_of(total), total - done[k]);
-        WorkItem w{};
-        w.src_off = o.src_off * ub + done[k];
-        w.dst_off = o.dst_off * ub + done[k];
-        w.bytes = c;
-        w.dst_rank = o.dst_rank;
-        w.src_buf = static_cast<uint8_t>(o.src_buf);
-        w.dst_buf = static_cast<uint8_t>(o.dst_buf);
-        w.wait_kind = o.src_buf == Buf::kBalance ? 1 : o.src_buf == Buf::kRail ? 2 : 0;
-        w.signal_kind = o.dst_buf == Buf::kBalance ? 1 : o.dst_buf == Buf::kRail ? 2 : 3;
-        w.stage = o.stage;
-        w.wait_stage = o.src_buf == Buf::kRail ? o.stage : -1;
-        prog.items.push_back(w);
-        done[k] += c;
-        any = true;
-      }
+    // Proportional interleave: chunk j of an op with c chunks gets key (j + 1/2) / c and chunks are
+    // issued in key order, so every op of the slot advances at a rate proportional to its size
+    // and all of them finish together (equal ops degenerate to plain round-robin). A heavy pair
+    // is then in flight from the first chunk on instead of trailing alone at the end.
+    struct Slice { double key; size_t op; int64_t begin, bytes; };
+    std::vector<Slice> slices;
+    for (size_t k = 0; k < ops.size(); ++k) {
+      const int64_t total = ops[k]->len * ub;
+      const int64_t c = chunk_of(total);
+      const int64_t n = (total + c - 1) / c;
+      for (int64_t j = 0; j < n; ++j) slices.push_back(Slice{(static_cast<double>(j) + 0.5) / static_cast<double>(n), k, j * c, std::min(c, total - j * c)});
+    }
+    std::stable_sort(slices.begin(), slices.end(), [](const Slice& a, const Slice& b) { return a.key < b.key; });
+    for (const Slice& sl : slices) {
+      const Op& o = *ops[sl.op];
+      WorkItem w{};
+      w.src_off = o.src_off * ub + sl.begin;
+      w.dst_off = o.dst_off * ub + sl.begin;
+      w.bytes = sl.bytes;
+      w.dst_rank = o.dst_rank;
+      w.src_buf = static_cast<uint8_t>(o.src_buf);
+      w.dst_buf = static_cast<uint8_t>(o.dst_buf);
+      w.wait_kind = o.src_buf == Buf::kBalance ? 1 : o.src_buf == Buf::kRail ? 2 : 0;
+      w.signal_kind = o.dst_buf == Buf::kBalance ? 1 : o.dst_buf == Buf::kRail ? 2 : 3;
+      w.stage = o.stage;
+      w.wait_stage = o.src_buf == Buf::kRail ? o.stage : -1;
+      prog.items.push_back(w);
     }
   };
   for (int s = 0; s < K + 3; ++s) {

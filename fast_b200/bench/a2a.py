@@ -57,16 +57,56 @@ def nccl_sendrecv_group(out, inp, in_splits, out_splits, rank, world):
         w.wait()
 
 
+def skewed_point(comm, row_bytes: int, skew: float, matrices: int = 3, iters: int = 5, warmup: int = 3, chunk: int = 1 << 20):
+    """One (row size, skew) point on an existing communicator: mean over seeded matrices of the
+    device-timed completion (max over ranks) for NCCL all_to_all_single and for this runtime's
+    fan-out and staged plans. Returns a dict of per-variant ms / per-rank algorithm GB/s."""
+    rank, world = comm.rank, comm.world
+    mats = [sched.workload_zipf_rows(world, skew, row_bytes, 1000 * mi + 7, 16) for mi in range(matrices)]
+    need = max(int(m.sum(0).max()) for m in mats) + (1 << 20)
+    out = comm.alloc(need, torch.uint8)
+    g = torch.Generator(device="cuda").manual_seed(4321 + rank)
+    inp = torch.randn(row_bytes // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
+    nccl_out = torch.empty(need, dtype=torch.uint8, device="cuda")
+    acc = {}
+    for m in mats:
+        in_splits = [int(x) for x in m[rank]]
+        out_splits = [int(x) for x in m[:, rank]]
+        sent = int(m[rank].sum())
+        bound = int(max((m.sum(0) - np.diag(m)).max(), (m.sum(1) - np.diag(m)).max()))
+        variants = {"nccl_alltoallv": lambda: nccl_alltoallv(nccl_out[: sum(out_splits)], inp[:sent], in_splits, out_splits)}
+        for name, kind in (("ours_fanout", PlanKind.FANOUT), ("ours_staged", PlanKind.STAGED)):
+            s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=chunk)
+            variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
+        for name, fn in variants.items():
+            acc.setdefault(name, []).append((_time_ms(fn, iters, warmup), sent, bound))
+    comm.check()
+    comm.free(out)
+    res = {"row_bytes": row_bytes, "skew": skew, "matrices": matrices, "world": world}
+    for name, xs in acc.items():
+        res[name] = {"ms": round(float(np.mean([x[0] for x in xs])), 4), "algbw_GBps": round(float(np.mean([x[1] / x[0] / 1e6 for x in xs])), 2),
+                     "frac_of_770GBps_port_bound": round(float(np.mean([x[2] / 770e9 / (x[0] * 1e-3) for x in xs])), 4)}
+    return res
+
+
 def run(args):
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
     dist.init_process_group("nccl")
     max_row = max(args.sizes)
-    comm = Communicator(heap_bytes=int(max_row * 2.5) + (64 << 20), topo=Topology.flat(world), ctas=args.ctas, threads=args.threads)
-    out = comm.alloc(int(max_row * 2.2), torch.uint8)
+    # Receive buffers must hold the heaviest column of any matrix that will be drawn.
+    need = max_row
+    if args.mode == "skewed":
+        for size in args.sizes:
+            for skew in args.skews:
+                for mi in range(args.matrices):
+                    need = max(need, int(sched.workload_zipf_rows(world, skew, size, 1000 * mi + 7, 16).sum(0).max()))
+    need = need + (1 << 20)
+    comm = Communicator(heap_bytes=need + (128 << 20), topo=Topology.flat(world), ctas=args.ctas, threads=args.threads)
+    out = comm.alloc(need, torch.uint8)
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
     inp = torch.randn(max_row // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
-    nccl_out = torch.empty(int(max_row * 2.2), dtype=torch.uint8, device="cuda")
+    nccl_out = torch.empty(need, dtype=torch.uint8, device="cuda")
     results = []
     for size in args.sizes:
         skews = args.skews if args.mode == "skewed" else [None]

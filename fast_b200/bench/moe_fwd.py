@@ -135,10 +135,22 @@ def main():
             for p in range(4):
                 acc[p] += ev[p].elapsed_time(ev[p + 1]) * 1e3 / a.iters
     comm.check()
+    # Combine alone: every peer's rows are final by now, so this is the pure pull + reduce time
+    # (inside the layer, a rank's combine also absorbs the wait for the slowest peer's experts).
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(a.iters):
+        out = eng.combine(rs, rs.topk_w)
+    c1.record()
+    torch.cuda.synchronize()
+    combine_alone_us = _max_over_ranks([c0.elapsed_time(c1) * 1e3 / a.iters], world)[0]
     route_us, dispatch_us, experts_us, combine_us = _max_over_ranks(acc, world)
     tm = eng.traffic_matrix().cpu().numpy()
     res = {"bench": "moe_forward", "world": world, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K, "dispatch_dtype": "fp8_e4m3_1x128" if a.fp8 else "bf16",
-           "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1), "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1),
+           "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1), "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1), "combine_alone_us": round(combine_alone_us, 1),
            "layer_us": round(route_us + dispatch_us + experts_us + combine_us, 1),
            "max_rows_in": int(tm.sum(0).max()), "max_rows_out": int(tm.sum(1).max())}
     row_bytes = H * (1 if a.fp8 else 2) + (H // 128 * 4 if a.fp8 else 0)
