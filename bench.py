@@ -103,7 +103,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=SEQS)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--capacity-factor", type=float, default=0.0, help="receive rows per rank as a multiple of tokens*top_k (0 = worst case)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the skewed all-to-all(v) comparison that follows the training benchmark when N > 1")
+    ap.add_argument("--no-extras", action="store_true", help="skip the sub-metrics measured after the training benchmark (skewed all-to-all(v) vs NCCL when N > 1; MoE forward dispatch+combine)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -199,6 +199,16 @@ def main():
         a2av = skewed_point(comm, 256 << 20, 1.0, matrices=3, iters=5, warmup=3)
         a2av["speedup_vs_nccl"] = round(a2av["nccl_alltoallv"]["ms"] / min(a2av["ours_fanout"]["ms"], a2av["ours_staged"]["ms"]), 3)
 
+    # ---- MoE forward sub-metric: dispatch + combine latency on DeepSeek-V3-like shapes, fp8 dispatch ----
+    moe_fwd = None
+    if not args.no_extras:
+        from fast_b200.bench import moe_fwd as mf
+
+        del model, opt_experts, opt_repl
+        torch.cuda.empty_cache()
+        comm2 = Communicator(heap_bytes=mf.heap_bytes_needed(world, 4096, 7168, 8, 32, True), device=local, timeout_s=20.0)
+        moe_fwd = mf.measure(comm2, fp8=True, iters=10, warmup=3, skip_nccl=True)
+
     t = torch.tensor([ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -218,6 +228,7 @@ def main():
             "e2e": {"value": round(total_tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
                     "h2d_bytes_per_step": host_ids[0].numel() * host_ids[0].element_size(), "d2h_bytes_per_step": 4, "last_loss": last},
             "alltoallv_skewed": a2av,
+            "moe_forward_fp8_dispatch": moe_fwd,
             "gpu_launches": int(launches),
             "gpu_launches_per_step": launches / max(args.steps, 1),
         }

@@ -80,6 +80,93 @@ def nccl_reference_layer(x, idx, w, w13, w2, world, E):
     return y.to(x.dtype)
 
 
+def heap_bytes_needed(world, tokens, hidden, top_k, experts_per_gpu, fp8):
+    cap = world * tokens * min(top_k, experts_per_gpu) + 256 * experts_per_gpu
+    return int(cap * hidden * (3 if fp8 else 4.2)) + (256 << 20)
+
+
+def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False):
+    """Runs the forward layer on an existing communicator and returns the result dict (every rank)."""
+    rank, world = comm.rank, comm.world
+    E, K, H, I, T, El = experts_per_gpu * world, top_k, hidden, inter, tokens, experts_per_gpu
+    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False)
+    g = torch.Generator(device="cuda").manual_seed(7)      # same on every rank: the bias is replicated
+    bias = torch.randn(E, generator=g, device="cuda") * 1.5
+    gr = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x = torch.randn(T, H, generator=gr, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=gr, device="cuda")
+    w13 = (torch.randn(El, 2 * I, H, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(El, H, I, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
+    C = runtime.ext()
+
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    acc = [0.0] * 4
+    out = None
+    for it in range(warmup + iters):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev[0].record()
+        rs = eng.route(logits, bias)
+        ev[1].record()
+        eng.dispatch(x, rs)
+        C.wait_counters(eng._arrive_ptr(0), eng.arrive_target[0], eng.status, eng.timeout_ns)  # phase boundary for timing only
+        ev[2].record()
+        eng.experts_forward(w13, w2, rs)
+        ev[3].record()
+        out = eng.combine(rs, rs.topk_w)
+        ev[4].record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            for p in range(4):
+                acc[p] += ev[p].elapsed_time(ev[p + 1]) * 1e3 / iters
+    comm.check()
+    # Combine alone: every peer's rows are final by now, so this is the pure pull + reduce time
+    # (inside the layer, a rank's combine also absorbs the wait for the slowest peer's experts).
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(iters):
+        out = eng.combine(rs, rs.topk_w)
+    c1.record()
+    torch.cuda.synchronize()
+    combine_alone_us = _max_over_ranks([c0.elapsed_time(c1) * 1e3 / iters], world)[0]
+    route_us, dispatch_us, experts_us, combine_us = _max_over_ranks(acc, world)
+    tm = eng.traffic_matrix().cpu().numpy()
+    res = {"bench": "moe_forward", "world": world, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K,
+           "dispatch_dtype": "fp8_e4m3_1x128" if fp8 else "bf16", "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1),
+           "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1), "combine_alone_us": round(combine_alone_us, 1),
+           "dispatch_plus_combine_us": round(dispatch_us + combine_alone_us, 1),
+           "layer_us": round(route_us + dispatch_us + experts_us + combine_us, 1),
+           "max_rows_in": int(tm.sum(0).max()), "max_rows_out": int(tm.sum(1).max())}
+    row_bytes = H * (1 if fp8 else 2) + (H // 128 * 4 if fp8 else 0)
+    if world > 1:
+        off_in = int((tm.sum(0) - tm.diagonal()).max())
+        off_out = int((tm.sum(1) - tm.diagonal()).max())
+        res["dispatch_bound_us_at_770GBps"] = round(max(off_in, off_out) * row_bytes / 770e9 * 1e6, 1)
+        res["combine_bound_us_at_770GBps"] = round(max(off_in, off_out) * H * 2 / 770e9 * 1e6, 1)
+    if not skip_nccl:
+        idx, w = rs.topk_idx, rs.topk_w
+        for _ in range(2):
+            ref = nccl_reference_layer(x, idx, w, w13, w2, world, E)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = max(3, iters // 4)
+        e0.record()
+        for _ in range(n):
+            ref = nccl_reference_layer(x, idx, w, w13, w2, world, E)
+        e1.record()
+        torch.cuda.synchronize()
+        res["nccl_torch_layer_us"] = round(_max_over_ranks([e0.elapsed_time(e1) * 1e3 / n], world)[0], 1)
+        err = ((out.float() - ref.float()).abs().max() / (ref.float().abs().max() + 1e-9)).item()
+        res["max_rel_err_vs_nccl_torch"] = round(err, 5)
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
@@ -97,87 +184,8 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    E, K, H, I, T = a.experts_per_gpu * world, a.top_k, a.hidden, a.inter, a.tokens
-    El = a.experts_per_gpu
-    cap = world * T * min(K, El) + 256 * El
-    comm = Communicator(heap_bytes=int(cap * H * (3 if a.fp8 else 4.2)) + (256 << 20), device=local, timeout_s=20.0)
-    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=a.fp8, training=False)
-    g = torch.Generator(device="cuda").manual_seed(7)      # same on every rank: gate and bias are replicated
-    bias = torch.randn(E, generator=g, device="cuda") * 1.5
-    gr = torch.Generator(device="cuda").manual_seed(100 + rank)
-    x = torch.randn(T, H, generator=gr, device="cuda").to(torch.bfloat16)
-    logits = torch.randn(T, E, generator=gr, device="cuda")
-    w13 = (torch.randn(El, 2 * I, H, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
-    w2 = (torch.randn(El, H, I, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
-    C = runtime.ext()
-
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
-    acc = [0.0] * 4
-    out = None
-    for it in range(a.warmup + a.iters):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ev[0].record()
-        rs = eng.route(logits, bias)
-        ev[1].record()
-        eng.dispatch(x, rs)
-        if a.fp8:
-            pass
-        C.wait_counters(eng._arrive_ptr(0), eng.arrive_target[0], eng.status, eng.timeout_ns)  # phase boundary for timing only
-        ev[2].record()
-        eng.experts_forward(w13, w2, rs)
-        ev[3].record()
-        out = eng.combine(rs, rs.topk_w)
-        ev[4].record()
-        torch.cuda.synchronize()
-        if it >= a.warmup:
-            for p in range(4):
-                acc[p] += ev[p].elapsed_time(ev[p + 1]) * 1e3 / a.iters
-    comm.check()
-    # Combine alone: every peer's rows are final by now, so this is the pure pull + reduce time
-    # (inside the layer, a rank's combine also absorbs the wait for the slowest peer's experts).
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    c0.record()
-    for _ in range(a.iters):
-        out = eng.combine(rs, rs.topk_w)
-    c1.record()
-    torch.cuda.synchronize()
-    combine_alone_us = _max_over_ranks([c0.elapsed_time(c1) * 1e3 / a.iters], world)[0]
-    route_us, dispatch_us, experts_us, combine_us = _max_over_ranks(acc, world)
-    tm = eng.traffic_matrix().cpu().numpy()
-    res = {"bench": "moe_forward", "world": world, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K, "dispatch_dtype": "fp8_e4m3_1x128" if a.fp8 else "bf16",
-           "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1), "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1), "combine_alone_us": round(combine_alone_us, 1),
-           "layer_us": round(route_us + dispatch_us + experts_us + combine_us, 1),
-           "max_rows_in": int(tm.sum(0).max()), "max_rows_out": int(tm.sum(1).max())}
-    row_bytes = H * (1 if a.fp8 else 2) + (H // 128 * 4 if a.fp8 else 0)
-    off_in = int((tm.sum(0) - tm.diagonal()).max()) if world > 1 else 0
-    off_out = int((tm.sum(1) - tm.diagonal()).max()) if world > 1 else 0
-    if world > 1:
-        res["dispatch_bound_us_at_770GBps"] = round(max(off_in, off_out) * row_bytes / 770e9 * 1e6, 1)
-        res["combine_bound_us_at_770GBps"] = round(max(off_in, off_out) * H * 2 / 770e9 * 1e6, 1)
-    flops = 2.0 * int(tm.sum(0)[rank]) * H * I * 3
-    res["experts_tflops_rank0"] = round(flops / (experts_us * 1e-6) / 1e12, 1) if rank == 0 else None
-    if not a.skip_nccl:
-        idx, w = rs.topk_idx, rs.topk_w
-        for _ in range(2):
-            ref = nccl_reference_layer(x, idx, w, w13, w2, world, E)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n = max(3, a.iters // 4)
-        e0.record()
-        for _ in range(n):
-            ref = nccl_reference_layer(x, idx, w, w13, w2, world, E)
-        e1.record()
-        torch.cuda.synchronize()
-        res["nccl_torch_layer_us"] = round(_max_over_ranks([e0.elapsed_time(e1) * 1e3 / n], world)[0], 1)
-        err = ((out.float() - ref.float()).abs().max() / (ref.float().abs().max() + 1e-9)).item()
-        res["max_rel_err_vs_nccl_torch"] = round(err, 5)
+    comm = Communicator(heap_bytes=heap_bytes_needed(world, a.tokens, a.hidden, a.top_k, a.experts_per_gpu, a.fp8), device=local, timeout_s=20.0)
+    res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl)
     if rank == 0:
         print(json.dumps(res), flush=True)
     if world > 1:
