@@ -79,10 +79,19 @@ def main():
         for name, (fn, flops) in cases.items():
             out["sustained_" + name] = sustained(fn, flops)
         if not a.no_cublas:
-            def cublas_fwd_s():
-                for g in range(G):
-                    torch.matmul(x[g * per:(g + 1) * per], w13[g].t(), out=gu[g * per:(g + 1) * per])
-            out["sustained_cublas_fwd_w13"] = sustained(cublas_fwd_s, 2 * R * H * 2 * I)
+            sl = lambda t, g: t[g * per:(g + 1) * per]
+            cub = {
+                "fwd_w13": (lambda: [torch.matmul(sl(x, g), w13[g].t(), out=sl(gu, g)) for g in range(G)], 2 * R * H * 2 * I),
+                "fwd_w2": (lambda: [torch.matmul(sl(act, g), w2[g].t(), out=sl(y, g)) for g in range(G)], 2 * R * H * I),
+                "dgrad_w2": (lambda: [torch.matmul(sl(y, g), w2[g], out=sl(dact, g)) for g in range(G)], 2 * R * H * I),
+                "wgrad_w2": (lambda: [torch.matmul(sl(y, g).t(), sl(act, g), out=dw2[g]) for g in range(G)], 2 * R * H * I),
+                "dgrad_w13": (lambda: [torch.matmul(sl(gu, g), w13[g], out=sl(dx, g)) for g in range(G)], 2 * R * H * 2 * I),
+                "wgrad_w13": (lambda: [torch.matmul(sl(gu, g).t(), sl(x, g), out=dw13[g]) for g in range(G)], 2 * R * H * 2 * I),
+            }
+            for name, (fn, flops) in cub.items():
+                out["sustained_cublas_" + name] = sustained(fn, flops)
+            print(json.dumps({"kernel": a.kernel, "rows": R, "hidden": H, "inter": I, "experts": G, **out}))
+            return
     if a.no_cublas:
         print(json.dumps({"kernel": a.kernel, "rows": R, "hidden": H, "inter": I, "experts": G, **out}))
         return
