@@ -1,0 +1,61 @@
+"""Cross-check of this scheduler against the reference's own CPU simulator (unmodified sources,
+built with baseline/build_ref_sim.sh). Skipped where the reference tree is not mounted."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from fast_b200 import sched
+from fast_b200.sched import Topology
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("FASTB_REFERENCE", "/root/reference")
+
+
+@pytest.fixture(scope="module")
+def ref_sim():
+    if not os.path.isdir(os.path.join(REF, "simulation")):
+        pytest.skip("reference tree not available")
+    r = subprocess.run(["bash", os.path.join(ROOT, "baseline", "build_ref_sim.sh"), REF], capture_output=True, text=True)
+    if r.returncode != 0:
+        pytest.skip("reference simulator does not build here: " + r.stderr[-300:])
+    return r.stdout.strip().splitlines()[-1]
+
+
+def _run_ref(exe, m, S, G, inter, intra, mbpu):
+    text = f"{S} {G} {inter.alpha_us} {inter.beta_us_per_mb} {intra.alpha_us} {intra.beta_us_per_mb} {mbpu}\n" + " ".join(str(int(x)) for x in m.reshape(-1))
+    out = subprocess.run([exe], input=text, capture_output=True, text=True, check=True).stdout
+    return json.loads(out.strip().splitlines()[-1])
+
+
+def test_config1_flat_zipf_matches_reference(ref_sim):
+    """8 ranks, Zipf(1.2) rows of 256 MiB: same line sum, both decompositions exact, ours is faster."""
+    m = sched.workload_zipf_rows(8, 1.2, 256 << 20, 1)
+    nv = sched.nvlink_model(900.0, 2.0)
+    ref = _run_ref(ref_sim, m, 8, 1, nv, nv, 1e-6)
+    d = sched.decompose(m)
+    assert ref["exact"] and d["exact"]
+    assert ref["freq_sum"] == d["line_sum"] == max(m.sum(0).max(), m.sum(1).max())
+    assert len(d["stages"]) <= 8 * 8 - 2 * 8 + 2 and ref["stages"] <= 8 * 8 - 2 * 8 + 2
+    p = sched.build_plan(m, Topology.flat(8))
+    c = p.cost(nv, nv, 1e-6)
+    # the reference charges every stage its padded weight, this model the real bytes: never slower
+    assert c["total_us"] <= ref["pipeline2_us"] * 1.001 + 2.0 * abs(p.num_stages - ref["stages"])
+    assert abs(c["spread_out_us"] - ref["spread_out_us"]) / ref["spread_out_us"] < 1e-6
+
+
+@pytest.mark.parametrize("S,G", [(2, 8), (4, 4), (3, 2)])
+def test_hierarchical_model_tracks_reference(ref_sim, S, G):
+    inter, intra = sched.gbps_model(400, 0.7), sched.LinkModel(0.1, 2.3)
+    ratios = []
+    for seed in range(4):
+        m = sched.workload_uniform(S * G, 10000, seed + 11 * S)
+        ref = _run_ref(ref_sim, m, S, G, inter, intra, 1.0)
+        p = sched.build_plan(m, Topology(S, G))
+        c = p.cost(inter, intra, 1.0)
+        assert ref["exact"]
+        assert abs(c["spread_out_us"] - ref["spread_out_us"]) / ref["spread_out_us"] < 1e-6
+        ratios.append(c["total_us"] / ref["pipeline2_us"])
+    assert 0.85 < float(np.mean(ratios)) < 1.1, ratios
