@@ -177,8 +177,9 @@ cudaError_t launch_swiglu_fwd(const __nv_bfloat16* gate_up, __nv_bfloat16* act, 
 // d_gate_up = d(silu(g) * u) given d_act. rows_dev (optional, device) caps the rows processed.
 cudaError_t launch_swiglu_bwd(const __nv_bfloat16* gate_up, const __nv_bfloat16* d_act, __nv_bfloat16* d_gate_up, long long rows, int inter,
                               const int* rows_dev, cudaStream_t stream);
-// Dequantises e4m3 rows with one fp32 scale per 128 elements to bf16.
-cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, cudaStream_t stream);
+// Dequantises e4m3 rows with one fp32 scale per 128 elements to bf16. rows_dev (optional, device) caps the rows processed.
+cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, const int* rows_dev,
+                               cudaStream_t stream);
 // out = scale * sum((a + b)^2) with (a + b) rounded to bf16 first (loss of a residual sum); partial is scratch of partial_len floats.
 cudaError_t launch_sumsq_add(const __nv_bfloat16* a, const __nv_bfloat16* b, long long n, float scale, float* partial, int partial_len, float* out,
                              cudaStream_t stream);

@@ -63,7 +63,9 @@ __global__ void swiglu_bwd_kernel(const uint4* __restrict__ gu, const uint4* __r
   }
 }
 
-__global__ void dequant_fp8_kernel(const uint2* __restrict__ q, const float* __restrict__ scales, uint4* __restrict__ out, long long rows, int H) {
+__global__ void dequant_fp8_kernel(const uint2* __restrict__ q, const float* __restrict__ scales, uint4* __restrict__ out, long long rows, int H,
+                                   const int* __restrict__ rows_dev) {
+  if (rows_dev) rows = min(rows, static_cast<long long>(*rows_dev));
   const int cpr = H / 8;
   const long long total = rows * cpr;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -235,10 +237,11 @@ cudaError_t launch_embedding_bwd(const long long* sorted_ids, const long long* p
   note_launch();
   return cudaGetLastError();
 }
-cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, cudaStream_t stream) {
+cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, const int* rows_dev,
+                               cudaStream_t stream) {
   if (H % 128) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
-  dequant_fp8_kernel<<<grid_for(rows * H / 8), 256, 0, stream>>>(reinterpret_cast<const uint2*>(q), scales, reinterpret_cast<uint4*>(out), rows, H);
+  dequant_fp8_kernel<<<grid_for(rows * H / 8), 256, 0, stream>>>(reinterpret_cast<const uint2*>(q), scales, reinterpret_cast<uint4*>(out), rows, H, rows_dev);
   note_launch();
   return cudaGetLastError();
 }

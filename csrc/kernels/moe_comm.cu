@@ -111,29 +111,44 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
         }
       }
     } else {
-      // 128 elements = 16 lanes x 8 elements share one scale (amax / 448).
+      // 16 elements per lane (one 16-byte store of e4m3); 8 consecutive lanes = 128 elements share
+      // one scale (amax / 448).
       const int sgroups = a.H / 128;
-      for (int c = lane; c < chunks; c += 32) {
-        float f[8];
-        unpack8(__ldg(src + c), f);
+      const int chunks16 = a.H / 16;
+      // The whole warp walks the row together (the shuffles below need every lane); lanes past
+      // the end of a short row carry zeros and store nothing.
+      for (int c0 = 0; c0 < chunks16; c0 += 32) {
+        const int c = c0 + lane;
+        const bool active = c < chunks16;
+        float f[16];
+        if (active) {
+          float lo[8], hi[8];
+          unpack8(__ldg(src + 2 * c), lo);
+          unpack8(__ldg(src + 2 * c + 1), hi);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = 0.0f;
+        }
         float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
 #pragma unroll
-        for (int o = 8; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         const float sc = fmaxf(amax, 1e-12f) * (1.0f / 448.0f);
         const float inv = 1.0f / sc;
-        uint2 q;
+        uint4 q;
         unsigned char* qb = reinterpret_cast<unsigned char*>(&q);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
+        for (int i = 0; i < 16; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
-          if (j >= a.K) break;
-          uint2* out = reinterpret_cast<uint2*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
+          if (j >= a.K || !active) break;
+          uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
           *out = q;
-          if ((lane & 15) == 0)
-            reinterpret_cast<float*>(dst[j] + a.scale_heap_off)[static_cast<long long>(row_of[j]) * sgroups + c / 16] = sc;
+          if ((lane & 7) == 0)
+            reinterpret_cast<float*>(dst[j] + a.scale_heap_off)[static_cast<long long>(row_of[j]) * sgroups + c / 8] = sc;
         }
       }
     }

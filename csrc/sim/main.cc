@@ -7,6 +7,7 @@
 //   skew      modeled speed-up vs Zipf skew
 //   size      modeled speed-up vs transfer size with and without coarsening
 //   fabric    modeled speed-up and exposed intra-server share vs intra-server link speed
+//   overhead  scheduler time and staging memory relative to the payload, per cluster size
 // Covers the reference simulator's drivers (simulation/test.cpp:15-60 DecompositionTester,
 // :73-116 run, :119-264 grid, :346-498 fabric, :501-592 skew, :595-684 size).
 #include <chrono>
@@ -160,6 +161,26 @@ int cmd_size(const Args& a) {
   }
   return 0;
 }
+// Scheduler cost and staging memory against the plain send/receive buffers, per cluster size
+// (the reference's overhead test, amd/test_alltoall.cpp:2750-2823).
+int cmd_overhead(const Args& a) {
+  const int G = static_cast<int>(a.integer("gpus", 8));
+  for (int S = 2; S <= static_cast<int>(a.integer("max-servers", 8)); ++S) {
+    Matrix m = workload_uniform(S * G, a.integer("max-entry", 10000), 40 + S, false);
+    const int reps = static_cast<int>(a.integer("reps", 20));
+    const double t0 = now_us();
+    size_t ops = 0;
+    Plan p;
+    for (int r = 0; r < reps; ++r) { p = build_plan(m, Topology{S, G}, PlanOptions{}); ops += p.ops.size(); }
+    const double us = (now_us() - t0) / reps;
+    int64_t payload = 0, staging = 0;
+    for (const RankBuffers& b : p.buffers) { payload += b.input_units + b.output_units; staging += b.balance_units + b.rail_units; }
+    std::printf("{\"cmd\":\"overhead\",\"servers\":%d,\"gpus\":%d,\"scheduler_us\":%.1f,\"stages\":%d,\"ops\":%zu,\"staging_over_payload\":%.4f}\n", S, G, us,
+                p.num_stages, p.ops.size(), payload ? static_cast<double>(staging) / static_cast<double>(payload) : 0.0);
+    (void)ops;
+  }
+  return 0;
+}
 int cmd_fabric(const Args& a) {
   const int S = static_cast<int>(a.integer("servers", 16)), G = static_cast<int>(a.integer("gpus", 8));
   Matrix m = workload_uniform(S * G, 10000, 11, false);
@@ -174,7 +195,7 @@ int cmd_fabric(const Args& a) {
 
 int main(int argc, char** argv) {
   if (argc < 2) {
-    std::fprintf(stderr, "usage: fastb-sim {plan|verify|grid|skew|size|fabric} [--key value ...]\n");
+    std::fprintf(stderr, "usage: fastb-sim {plan|verify|grid|skew|size|fabric|overhead} [--key value ...]\n");
     return 2;
   }
   Args a = parse(argc, argv);
@@ -186,6 +207,7 @@ int main(int argc, char** argv) {
     if (c == "skew") return cmd_skew(a);
     if (c == "size") return cmd_size(a);
     if (c == "fabric") return cmd_fabric(a);
+    if (c == "overhead") return cmd_overhead(a);
   } catch (const std::exception& e) {
     std::fprintf(stderr, "fastb-sim: %s\n", e.what());
     return 1;

@@ -183,10 +183,10 @@ void bind_moe(py::module_& m) {
                                reinterpret_cast<__nv_bfloat16*>(dgu.data_ptr()), gu.size(0), static_cast<int>(dact.size(1)), reinterpret_cast<const int*>(rows_dev_ptr),
                                stream_now()), "swiglu_bwd");
   });
-  m.def("dequant_fp8", [](torch::Tensor q, torch::Tensor scales, torch::Tensor out) {
+  m.def("dequant_fp8", [](torch::Tensor q, torch::Tensor scales, torch::Tensor out, int64_t rows_dev_ptr) {
     want(q, torch::kUInt8, "q"); want(scales, torch::kFloat32, "scales"); want(out, torch::kBFloat16, "out");
     cu_check(launch_dequant_fp8(q.data_ptr<uint8_t>(), scales.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), q.size(0),
-                                static_cast<int>(q.size(1)), stream_now()), "dequant_fp8");
+                                static_cast<int>(q.size(1)), reinterpret_cast<const int*>(rows_dev_ptr), stream_now()), "dequant_fp8");
   });
   m.def("sumsq_add", [](torch::Tensor a, torch::Tensor b, double scale, torch::Tensor partial, torch::Tensor out) {
     want(a, torch::kBFloat16, "a"); want(b, torch::kBFloat16, "b"); want(partial, torch::kFloat32, "partial"); want(out, torch::kFloat32, "out");

@@ -102,7 +102,10 @@ def run(args):
                 for mi in range(args.matrices):
                     need = max(need, int(sched.workload_zipf_rows(world, skew, size, 1000 * mi + 7, 16).sum(0).max()))
     need = need + (1 << 20)
-    comm = Communicator(heap_bytes=need + (128 << 20), topo=Topology.flat(world), ctas=args.ctas, threads=args.threads)
+    # --servers S > 0 runs the two-tier plan (balance, rail stages, redistribute) over S virtual
+    # servers of world/S GPUs; its staging needs up to ~2x the payload.
+    topo = Topology(args.servers, world // args.servers) if args.servers else Topology.flat(world)
+    comm = Communicator(heap_bytes=need * (4 if args.servers else 1) + (128 << 20), topo=topo, ctas=args.ctas or None, threads=args.threads)
     out = comm.alloc(need, torch.uint8)
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
     inp = torch.randn(max_row // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
@@ -129,7 +132,7 @@ def run(args):
                     variants["nccl_sendrecv"] = lambda: nccl_sendrecv_group(nccl_out, inp, in_splits, out_splits, rank, world)
                 for name, kind, opts in [("ours_fanout", PlanKind.FANOUT, {}), ("ours_staged", PlanKind.STAGED, {}),
                                          ("ours_staged_bottleneck", PlanKind.STAGED, {"match": sched.MatchPolicy.BOTTLENECK}),
-                                         ("ours_spreadout", PlanKind.SPREAD_OUT, {})]:
+                                         ("ours_spreadout", PlanKind.SPREAD_OUT, {})] + ([("ours_single_burst", PlanKind.SINGLE_BURST, {})] if args.servers else []):
                     s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk, **opts)
                     variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
                 for name, fn in variants.items():
@@ -142,7 +145,7 @@ def run(args):
                     nccl_alltoallv(nccl_out[: sum(out_splits)], inp[:sent], in_splits, out_splits)
                     torch.cuda.synchronize()
                     assert torch.equal(out[: sum(out_splits)], nccl_out[: sum(out_splits)]), "mismatch vs NCCL"
-            row = {"mode": args.mode, "world": world, "row_bytes": size, "skew": skew, "matrices": nmat}
+            row = {"mode": args.mode, "world": world, "servers": args.servers or world, "row_bytes": size, "skew": skew, "matrices": nmat}
             for name, xs in acc.items():
                 ms = float(np.mean([x[0] for x in xs]))
                 row[name] = {"ms": round(ms, 4), "algbw_GBps": round(float(np.mean([x[1] / x[0] / 1e6 for x in xs])), 2),
@@ -163,10 +166,11 @@ def main():
     ap.add_argument("--matrices", type=int, default=4)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--ctas", type=int, default=64)
+    ap.add_argument("--ctas", type=int, default=0, help="CTAs of the push kernel (0 = one per SM)")
     ap.add_argument("--threads", type=int, default=512)
     ap.add_argument("--chunk", type=int, default=1 << 20)
     ap.add_argument("--sendrecv", action="store_true")
+    ap.add_argument("--servers", type=int, default=0, help="treat the ranks as this many virtual servers (hierarchical FAST plan + single-burst ablation)")
     ap.add_argument("--verify", action="store_true")
     run(ap.parse_args())
 

@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--kernel", default="pair", choices=["pair", "one"])
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--only", default="", help="comma-separated case names to run (default: all)")
     ap.add_argument("--sustain-s", type=float, default=0.0, help="also time back-to-back launches for this many seconds (power-capped regime)")
     a = ap.parse_args()
     gemm.USE_PAIR = a.kernel == "pair"
@@ -63,6 +64,8 @@ def main():
         "dgrad_w13": (lambda: gemm.grouped_gemm_dgrad(gu, w13, off, dx), 2 * R * H * 2 * I),
         "wgrad_w13": (lambda: gemm.grouped_gemm_wgrad(gu, x, off, dw13), 2 * R * H * 2 * I),
     }
+    if a.only:
+        cases = {k: v for k, v in cases.items() if k in a.only.split(",")}
     out = {}
     for name, (fn, flops) in cases.items():
         if a.sustain_s > 0:

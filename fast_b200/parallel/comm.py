@@ -61,7 +61,7 @@ class Communicator:
     ``LocalGroup`` for several virtual ranks on a single GPU (tests, single-GPU runs)."""
 
     def __init__(self, group=None, heap_bytes: int = 1 << 30, topo: Optional[Topology] = None, device=None,
-                 timeout_s: float = 5.0, ctas: int = 64, threads: int = 512, _heap=None, _rank=None, _world=None):
+                 timeout_s: float = 5.0, ctas: Optional[int] = None, threads: int = 512, _heap=None, _rank=None, _world=None):
         import torch.distributed as dist
 
         self._C = runtime.ext()
@@ -84,7 +84,9 @@ class Communicator:
         if self.topo.ranks != self.world:
             raise ValueError("topology does not match the world size")
         self.timeout_ns = int(timeout_s * 1e9)
-        self.ctas, self.threads = ctas, threads
+        # one CTA per SM: the collective runs alone on its stream (measured best at 8 GPUs)
+        self.ctas = ctas or torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.threads = threads
         self.status = self._C.StatusBlock()
         self.sig_off = self.heap.alloc(self._C.SIG_WORDS * 8)
         self.epoch = 0

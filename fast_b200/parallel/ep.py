@@ -146,7 +146,7 @@ class ExpertParallel:
         gate = (self._arrive_ptr(0), self.arrive_target[0])
         if self.fp8:
             C.wait_counters(self._arrive_ptr(0), self.arrive_target[0], self.status, self.timeout_ns)
-            C.dequant_fp8(self.xq_recv, self.xs_recv, self.x_recv)
+            C.dequant_fp8(self.xq_recv, self.xs_recv, self.x_recv, rs.group_off.data_ptr() + 4 * self.El)
             C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
             gate = None
         gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate)
