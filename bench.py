@@ -102,7 +102,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seqs", type=int, default=SEQS)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--hidden", type=int, default=HIDDEN, help="model width (default: the benchmark's 4096; smaller only for profiling runs)")
+    ap.add_argument("--ffn", type=int, default=FFN, help="expert FFN width (default: the benchmark's 14336)")
     ap.add_argument("--capacity-factor", type=float, default=0.0, help="receive rows per rank as a multiple of tokens*top_k (0 = worst case)")
+    ap.add_argument("--early-step", action="store_true", help="apply W2's AdamW update inside the backward pass on a side stream (measured neutral under the 1000 W cap)")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-metrics measured after the training benchmark (skewed all-to-all(v) vs NCCL when N > 1; MoE forward dispatch+combine)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -127,11 +130,13 @@ def main():
     El = EXPERTS // world
     worst = world * tokens * min(TOP_K, El) + 256 * El  # every expert's rows are padded to 256
     cap = worst if args.capacity_factor <= 0 else min(worst, int(args.capacity_factor * tokens * TOP_K) + 256 * El)
-    heap = 4 * cap * HIDDEN * 2 + (256 << 20) + (0 if world == 1 or args.no_extras else (1100 << 20))
+    heap = 4 * cap * args.hidden * 2 + (256 << 20) + (0 if world == 1 or args.no_extras else (1100 << 20))
     comm = Communicator(heap_bytes=heap, device=local, timeout_s=20.0)
-    model = MixtralBlockModel(comm, vocab=VOCAB, hidden=HIDDEN, inter=FFN, num_experts=EXPERTS, top_k=TOP_K, max_tokens=tokens, capacity_rows=cap)
+    model = MixtralBlockModel(comm, vocab=VOCAB, hidden=args.hidden, inter=args.ffn, num_experts=EXPERTS, top_k=TOP_K, max_tokens=tokens, capacity_rows=cap)
     opt_experts = FusedAdamW(model.expert_parameters(), lr=1e-4, weight_decay=0.01)
     opt_repl = FusedAdamW(model.replicated_parameters(), lr=1e-4, weight_decay=0.0)
+    if args.early_step:
+        model.moe.attach_optimizer(opt_experts)  # W2's AdamW update overlaps the W13 backward GEMMs
 
     gen = torch.Generator().manual_seed(1234 + rank)
     n_batches = 4
@@ -220,7 +225,7 @@ def main():
             "metric": "moe_block_train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)",
-            "config": {"model": "Mixtral-8x7B-shaped MoE block (hidden 4096, FFN 14336 SwiGLU, 8 experts, top-2)", "global_batch": args.seqs * world,
+            "config": {"model": f"Mixtral-8x7B-shaped MoE block (hidden {args.hidden}, FFN {args.ffn} SwiGLU, 8 experts, top-2)", "global_batch": args.seqs * world,
                        "seq_len": args.seq_len, "parallelism": f"ep{world}", "tokens_per_gpu": tokens, "capacity_rows": cap,
                        "l2": "per-step working set (weights 2.8 GB/GPU at N=1, activations > 10 GB) far exceeds the 126 MB L2; no flush needed",
                        "optimizer": "AdamW, fp32 master weights, in the timed step", "timing": "CUDA events around K steps, max over ranks"},

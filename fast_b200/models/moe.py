@@ -34,7 +34,7 @@ class _MoEFunction(torch.autograd.Function):
         engine.dispatch(x, rs)
         engine.experts_forward(w13, w2, rs)
         out = engine.combine(rs, weights.detach().float().contiguous())
-        ctx.engine, ctx.rs = engine, rs
+        ctx.engine, ctx.rs, ctx.w2_param = engine, rs, w2
         ctx.save_for_backward(weights, w13, w2)
         return out
 
@@ -44,8 +44,28 @@ class _MoEFunction(torch.autograd.Function):
         eng = ctx.engine
         if not hasattr(eng, "_dw13") or eng._dw13.shape != w13.shape:
             eng._dw13, eng._dw2 = torch.empty_like(w13), torch.empty_like(w2)
-        gx, gw = eng.backward(grad_out.contiguous(), ctx.rs, weights.detach().float().contiguous(), w13, w2, eng._dw13, eng._dw2)
-        return gx, gw.to(weights.dtype), eng._dw13, eng._dw2, None, None
+        opt = getattr(eng, "optimizer_in_backward", None)
+        early = opt is not None and opt.owns(ctx.w2_param)
+        after = None
+        if early:
+            # W2's update runs on a side stream under the remaining GEMMs (W13 dgrad / wgrad): after the
+            # W2 wgrad nothing in this pass reads W2 any more.
+            main = torch.cuda.current_stream()
+            if not hasattr(eng, "_opt_stream"):
+                eng._opt_stream = torch.cuda.Stream(device=grad_out.device)
+
+            def after():
+                ev = torch.cuda.Event()
+                ev.record(main)
+                eng._opt_stream.wait_event(ev)
+                opt.step_param(ctx.w2_param, eng._dw2, stream=eng._opt_stream, early=True)
+
+        gx, gw = eng.backward(grad_out.contiguous(), ctx.rs, weights.detach().float().contiguous(), w13, w2, eng._dw13, eng._dw2, after_dw2=after)
+        if early:
+            done = torch.cuda.Event()
+            done.record(eng._opt_stream)
+            torch.cuda.current_stream().wait_event(done)  # the next kernels on this stream may read W2 / reuse dW2
+        return gx, gw.to(weights.dtype), eng._dw13, (None if early else eng._dw2), None, None
 
 
 class MoELayer(nn.Module):
@@ -65,6 +85,12 @@ class MoELayer(nn.Module):
         self.router_bias = nn.Parameter(torch.zeros(num_experts, device=dev), requires_grad=False) if router_bias else None
         self.engine = ExpertParallel(comm, num_experts, hidden, inter, top_k, max_tokens, fp8_dispatch=fp8_dispatch, training=training,
                                      capacity_rows=capacity_rows)
+
+    def attach_optimizer(self, opt) -> None:
+        """Optimizer-in-backward: ``opt`` (a FusedAdamW owning ``w2``) applies W2's update as soon as
+        its gradient exists, overlapped with the rest of the backward pass; ``opt.step()`` then
+        skips it. ``w2.grad`` stays None in that mode."""
+        self.engine.optimizer_in_backward = opt
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x: [tokens, hidden] bf16 -> [tokens, hidden] bf16."""

@@ -176,7 +176,8 @@ class Communicator:
         tensor goes through a library-owned receive buffer and one extra local copy."""
         src, dst, copy_back = self._launch_args(s, output, input)
         self.epoch += 1
-        self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, self.ctas, self.threads)
+        ctas = max(1, min(self.ctas, s.program.n_items))  # a handful of work items needs a handful of CTAs
+        self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, ctas, self.threads)
         if copy_back is not None:
             output.view(torch.uint8).reshape(-1)[: s.output_bytes].copy_(copy_back[: s.output_bytes])
         return output

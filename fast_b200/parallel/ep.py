@@ -171,8 +171,9 @@ class ExpertParallel:
 
     # ---- backward --------------------------------------------------------------------------------
     def backward(self, grad_out: torch.Tensor, rs: RouteState, weights: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, dw13: torch.Tensor,
-                 dw2: torch.Tensor):
-        """Returns (grad_x [T, H], grad_weights [T, K]); fills dw13 / dw2."""
+                 dw2: torch.Tensor, after_dw2=None):
+        """Returns (grad_x [T, H], grad_weights [T, K]); fills dw13 / dw2. ``after_dw2()`` is called
+        as soon as the W2 gradient kernel is queued (nothing later in the pass reads W2)."""
         C = self._C
         T = rs.topk_idx.shape[0]
         dev = grad_out.device
@@ -188,6 +189,8 @@ class ExpertParallel:
         gate = (self._arrive_ptr(1), self.arrive_target[1])
         gemm.grouped_gemm_dgrad(self.dy_recv, w2, rs.group_off, self.dact, gate=gate)
         gemm.grouped_gemm_wgrad(self.dy_recv, self.act, rs.group_off, dw2)
+        if after_dw2 is not None:
+            after_dw2()
         C.swiglu_bwd(self.gu, self.dact, self.dgu, rs.group_off.data_ptr() + 4 * self.El)
         gemm.grouped_gemm_dgrad(self.dgu, w13, rs.group_off, self.dx_recv)
         gemm.grouped_gemm_wgrad(self.dgu, self.x_recv, rs.group_off, dw13)

@@ -210,6 +210,31 @@ def test_block_model_trains():
     assert all(l == l for l in losses) and losses[-1] < losses[0]
 
 
+def test_optimizer_in_backward_matches_late_step():
+    """Applying W2's AdamW update inside the backward pass (side stream) gives bit-identical weights."""
+    from fast_b200.models import MixtralBlockModel
+    from fast_b200.parallel import Communicator
+    from fast_b200.utils import FusedAdamW
+
+    ids = torch.randint(0, 512, (2, 256), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    results = []
+    for early in (False, True):
+        comm = Communicator(heap_bytes=256 << 20, device=0)
+        model = MixtralBlockModel(comm, vocab=512, hidden=256, inter=256, num_experts=4, top_k=2, max_tokens=512, seed=3)
+        opt = FusedAdamW(model.expert_parameters(), lr=1e-2)
+        if early:
+            model.moe.attach_optimizer(opt)
+        for _ in range(3):
+            opt.zero_grad()
+            model(ids).backward()
+            opt.step()
+        comm.check()
+        torch.cuda.synchronize()
+        results.append((model.moe.w13.detach().clone(), model.moe.w2.detach().clone()))
+    assert torch.equal(results[0][0], results[1][0]) and torch.equal(results[0][1], results[1][1])
+    assert not torch.equal(results[0][1], torch.zeros_like(results[0][1]))
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_moe_multi_process():
     n = min(torch.cuda.device_count(), 8)
