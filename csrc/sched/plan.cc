@@ -149,7 +149,7 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
   }
 
   std::vector<int> last_stage_of_pair(static_cast<size_t>(S) * S, -1);
-  struct PendingRedis { Op op; };
+  
   auto emit_rail = [&](int k, int s, int t, int i, int64_t budget) {
     auto& q = hold_at(s, t, i);
     const int src_rank = s * G + i, dst_rank = t * G + i;

@@ -6,20 +6,20 @@ between a group's real end and its padded end are zero.
 """
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
 
 from .. import runtime
+from ..utils.config import CONFIG
 
 FORWARD, DGRAD, WGRAD = 0, 1, 2
 STORE, SWIGLU = 0, 1
 _BM, _BN, _BK = 128, 256, 64
 # CTA-pair kernel (256 x 256 tiles, cta_group::2); set False to fall back to the one-CTA kernel.
-USE_PAIR = os.environ.get("FASTB_GEMM", "pair") != "one"
+USE_PAIR = CONFIG.gemm != "one"
 # Rows of a raster band (see csrc/kernels/gemm_common.cuh); 0 = kernel default.
-BAND_ROWS = int(os.environ.get("FASTB_BAND", "0"))
+BAND_ROWS = CONFIG.band_rows
 
 
 def row_align() -> int:

@@ -16,6 +16,7 @@ import torch
 
 from .. import runtime, sched
 from ..sched import PlanKind, Topology
+from ..utils.config import CONFIG
 
 
 @dataclass
@@ -61,7 +62,7 @@ class Communicator:
     ``LocalGroup`` for several virtual ranks on a single GPU (tests, single-GPU runs)."""
 
     def __init__(self, group=None, heap_bytes: int = 1 << 30, topo: Optional[Topology] = None, device=None,
-                 timeout_s: float = 5.0, ctas: Optional[int] = None, threads: int = 512, _heap=None, _rank=None, _world=None):
+                 timeout_s: Optional[float] = None, ctas: Optional[int] = None, threads: int = 512, _heap=None, _rank=None, _world=None):
         import torch.distributed as dist
 
         self._C = runtime.ext()
@@ -83,7 +84,7 @@ class Communicator:
         self.topo = topo or Topology.flat(self.world)
         if self.topo.ranks != self.world:
             raise ValueError("topology does not match the world size")
-        self.timeout_ns = int(timeout_s * 1e9)
+        self.timeout_ns = int((CONFIG.timeout_s if timeout_s is None else timeout_s) * 1e9)
         # one CTA per SM: the collective runs alone on its stream (measured best at 8 GPUs)
         self.ctas = ctas or torch.cuda.get_device_properties(self.device).multi_processor_count
         self.threads = threads
@@ -144,6 +145,11 @@ class Communicator:
             prog = self._C.A2AProgram(torch.from_numpy(low["items"]), [int(x) for x in low["expect_rail_bytes"]],
                                       int(low["expect_output_bytes"]), int(low["expect_balance_bytes"]), self.device.index)
             s = Schedule(plan, unit_bytes, prog, low, self.rank)
+            if CONFIG.log and self.rank == 0:
+                nv = sched.nvlink_model(900.0, 2.0)
+                c = plan.cost(nv, nv, unit_bytes * 1e-6)
+                print(f"[fast_b200] scheduled {kind}: {plan.num_stages} stages, {plan.num_ops} ops, {prog.n_items} work items on rank 0, "
+                      f"modeled {c['total_us']:.1f} us, port bound {c['lower_bound_us']:.1f} us", flush=True)
             if len(self._sched_cache) > 512:
                 self._sched_cache.pop(next(iter(self._sched_cache)))
             self._sched_cache[key] = s
@@ -168,6 +174,17 @@ class Communicator:
         src = [input.data_ptr(), 0, base + bal_off, base + rail_off]
         dst = [0, out_off, bal_off, rail_off]
         return src, dst, copy_back
+
+    def init_buffers(self, s: Schedule):
+        """Library-owned buffers for a schedule: ``(send, recv)`` byte tensors, ``recv`` in the
+        symmetric heap (peers write it directly). Every rank must call this for the same schedule
+        (the reference's init_buffers / free_buffers pair, amd/flash.cpp:447-519)."""
+        send = torch.empty(max(s.max_bytes["input"], 1), dtype=torch.uint8, device=self.device)
+        recv = self.alloc(max(s.max_bytes["output"], 1), torch.uint8)
+        return send, recv
+
+    def free_buffers(self, recv: torch.Tensor) -> None:
+        self.free(recv)
 
     def all_to_all_v(self, output: torch.Tensor, input: torch.Tensor, s: Schedule) -> torch.Tensor:
         """Run a scheduled all-to-all(v) on the current stream. ``input`` holds the segments for

@@ -19,6 +19,7 @@ import torch
 
 from .. import runtime
 from ..ops import gemm
+from ..utils.config import nvtx_range
 from .comm import Communicator
 
 
@@ -163,11 +164,29 @@ class ExpertParallel:
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 weights: Optional[torch.Tensor] = None):
-        rs = self.route(logits, bias)
-        self.dispatch(x, rs)
-        self.experts_forward(w13, w2, rs)
-        out = self.combine(rs, rs.topk_w if weights is None else weights)
+        with nvtx_range("route"):
+            rs = self.route(logits, bias)
+        with nvtx_range("dispatch"):
+            self.dispatch(x, rs)
+        with nvtx_range("experts"):
+            self.experts_forward(w13, w2, rs)
+        with nvtx_range("combine"):
+            out = self.combine(rs, rs.topk_w if weights is None else weights)
         return out, rs
+
+    def plan_last_step(self, topo=None, **plan_opts):
+        """Host-side view of the last routed step: reads the device traffic matrix (this
+        synchronises), converts tokens to bytes and runs the scheduler on it. Returns
+        ``(plan, cost)`` with the cost under a 900 GB/s NVLink model - what a planned all-to-all(v)
+        of the same dispatch would look like (stages, modeled time, port bound)."""
+        from .. import sched
+
+        tokens = self.traffic.cpu().numpy().astype("int64")
+        row_bytes = self.H * (1 if self.fp8 else 2)
+        topo = topo or sched.Topology.flat(self.comm.world)
+        plan = sched.build_plan(tokens * row_bytes, topo, **plan_opts)
+        nv = sched.nvlink_model(900.0, 2.0)
+        return plan, plan.cost(nv, nv, 1e-6)
 
     # ---- backward --------------------------------------------------------------------------------
     def backward(self, grad_out: torch.Tensor, rs: RouteState, weights: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, dw13: torch.Tensor,

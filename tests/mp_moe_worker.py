@@ -56,6 +56,9 @@ def main():
         El = E // world
         assert _rel(layer.w13.grad, g13[rank * El:(rank + 1) * El]) < 3e-2, f"dw13 rank {rank}"
         assert _rel(layer.w2.grad, g2[rank * El:(rank + 1) * El]) < 3e-2, f"dw2 rank {rank}"
+        plan, cost = layer.engine.plan_last_step()
+        assert plan.validate() == "" and int(plan.matrix.sum()) == int(layer.engine.traffic_matrix().sum().item()) * H * 2
+        assert cost["total_us"] >= cost["lower_bound_us"] > 0
         dist.barrier()
     if rank == 0:
         print("MOE_MP_OK")

@@ -11,7 +11,7 @@ from fast_b200 import sched
 from fast_b200.sched import Topology
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("FASTB_REFERENCE", "/root/reference")
+REF = os.environ.get("FASTB_REFERENCE", os.path.join(ROOT, "..", "reference"))  # a checkout of the reference next to this repository
 
 
 @pytest.fixture(scope="module")
