@@ -9,6 +9,8 @@
 // the rail GPU is the destination, staging regions are never reused inside a collective (no
 // ping-pong credits), counters only grow inside a collective and are cleared by the last CTA
 // after every wait has been satisfied, and each wait is bounded.
+#include <atomic>
+
 #include "api.h"
 
 namespace fastb {
@@ -50,7 +52,14 @@ __device__ __forceinline__ void copy_bytes(unsigned char* __restrict__ dst, cons
 
 __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
   __shared__ int s_ok;
+  // Bytes this CTA has stored into each peer's OUTPUT and not yet announced. Output arrivals are
+  // only consumed at the end of the collective, so they are announced once per CTA (one fence for
+  // the whole list instead of one per work item); staged data is announced item by item because a
+  // forwarder is waiting for it.
+  __shared__ unsigned long long s_pending[kSigMaxWorld];
   const int tid = threadIdx.x;
+  for (int i = tid; i < kSigMaxWorld; i += blockDim.x) s_pending[i] = 0ull;
+  __syncthreads();
   unsigned char* my_slab = static_cast<unsigned char*>(a.peer_table[a.rank]);
   unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(my_slab + a.sig_heap_off);
   unsigned long long* my_cnt = my_sig + kSigCounterOff;
@@ -79,11 +88,21 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
     }
     __syncthreads();  // every thread's stores precede thread 0's release below
     if (alive && tid == 0) {
-      unsigned long long* dst_cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[w.dst_rank]) + a.sig_heap_off) + kSigCounterOff;
-      const int slot = w.signal_kind == 1 ? 0 : (w.signal_kind == 2 ? 2 + w.stage : 1);
-      fence_sys();
-      red_add_release_sys(dst_cnt + slot, static_cast<unsigned long long>(w.bytes));
+      if (w.signal_kind == 3) {
+        s_pending[w.dst_rank] += static_cast<unsigned long long>(w.bytes);
+      } else {
+        unsigned long long* dst_cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[w.dst_rank]) + a.sig_heap_off) + kSigCounterOff;
+        const int slot = w.signal_kind == 1 ? 0 : 2 + w.stage;
+        fence_sys();
+        red_add_release_sys(dst_cnt + slot, static_cast<unsigned long long>(w.bytes));
+      }
     }
+  }
+  __syncthreads();  // all copies of this CTA are issued; announce the output bytes, one peer per thread
+  if (tid < a.world && s_pending[tid] != 0ull) {
+    unsigned long long* dst_cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[tid]) + a.sig_heap_off) + kSigCounterOff;
+    fence_sys();
+    red_add_release_sys(dst_cnt + 1, s_pending[tid]);
   }
   // The collective is over for this rank once everything addressed to its output has landed.
   if (tid == 0) {
@@ -112,9 +131,9 @@ __global__ void wait_probe_kernel(const unsigned long long* flag, unsigned long 
 
 }  // namespace
 
-namespace { unsigned long long g_launches = 0; }
-unsigned long long launch_count() { return g_launches; }
-void note_launch(int n) { g_launches += static_cast<unsigned long long>(n); }
+namespace { std::atomic<unsigned long long> g_launches{0}; }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+void note_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
 cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* device_args, int virtual_ranks, int ctas, int threads,
                             cudaStream_t stream) {

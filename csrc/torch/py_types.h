@@ -22,7 +22,9 @@ struct HeapPy {
   torch::Tensor tensor(int64_t offset, std::vector<int64_t> shape, py::object dtype) const {
     auto dt = torch::python::detail::py_object_to_dtype(dtype);
     auto opts = torch::TensorOptions().dtype(dt).device(torch::kCUDA, device);
-    return torch::from_blob(static_cast<char*>(h->local_base()) + offset, shape, opts);
+    // The deleter holds a reference to the heap: the slab outlives every tensor carved from it.
+    auto keep = h;
+    return torch::from_blob(static_cast<char*>(h->local_base()) + offset, shape, [keep](void*) {}, opts);
   }
 };
 

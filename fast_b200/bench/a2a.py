@@ -57,7 +57,7 @@ def nccl_sendrecv_group(out, inp, in_splits, out_splits, rank, world):
         w.wait()
 
 
-def skewed_point(comm, row_bytes: int, skew: float, matrices: int = 3, iters: int = 5, warmup: int = 3, chunk: int = 1 << 20):
+def skewed_point(comm, row_bytes: int, skew: float, matrices: int = 3, iters: int = 5, warmup: int = 3, chunk=None):
     """One (row size, skew) point on an existing communicator: mean over seeded matrices of the
     device-timed completion (max over ranks) for NCCL all_to_all_single and for this runtime's
     fan-out and staged plans. Returns a dict of per-variant ms / per-rank algorithm GB/s."""
@@ -133,14 +133,14 @@ def run(args):
                 for name, kind, opts in [("ours_fanout", PlanKind.FANOUT, {}), ("ours_staged", PlanKind.STAGED, {}),
                                          ("ours_staged_bottleneck", PlanKind.STAGED, {"match": sched.MatchPolicy.BOTTLENECK}),
                                          ("ours_spreadout", PlanKind.SPREAD_OUT, {})] + ([("ours_single_burst", PlanKind.SINGLE_BURST, {})] if args.servers else []):
-                    s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk, **opts)
+                    s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk or None, **opts)
                     variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
                 for name, fn in variants.items():
                     ms = _time_ms(fn, iters, args.warmup)
                     acc.setdefault(name, []).append((ms, sent, bound_bytes))
                 comm.check()
                 if mi == 0 and args.verify:
-                    s = comm.schedule(m, unit_bytes=1, kind=PlanKind.STAGED, chunk_bytes=args.chunk)
+                    s = comm.schedule(m, unit_bytes=1, kind=PlanKind.STAGED, chunk_bytes=args.chunk or None)
                     comm.all_to_all_v(out, inp, s)
                     nccl_alltoallv(nccl_out[: sum(out_splits)], inp[:sent], in_splits, out_splits)
                     torch.cuda.synchronize()
@@ -168,7 +168,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ctas", type=int, default=0, help="CTAs of the push kernel (0 = one per SM)")
     ap.add_argument("--threads", type=int, default=512)
-    ap.add_argument("--chunk", type=int, default=1 << 20)
+    ap.add_argument("--chunk", type=int, default=0, help="work-item bytes (0 = chosen from the matrix)")
     ap.add_argument("--sendrecv", action="store_true")
     ap.add_argument("--servers", type=int, default=0, help="treat the ranks as this many virtual servers (hierarchical FAST plan + single-burst ablation)")
     ap.add_argument("--verify", action="store_true")

@@ -124,7 +124,7 @@ class Communicator:
         return self._staging[name][0]
 
     # ---- scheduling -----------------------------------------------------------------------------
-    def schedule(self, matrix, unit_bytes: int = 1, transpose: bool = False, kind=PlanKind.STAGED, chunk_bytes: int = 1 << 20,
+    def schedule(self, matrix, unit_bytes: int = 1, transpose: bool = False, kind=PlanKind.STAGED, chunk_bytes: Optional[int] = None,
                  **plan_opts) -> Schedule:
         """Plan the collective for ``matrix`` (units; ``matrix[i, j]`` = rank i -> rank j).
 
@@ -132,6 +132,13 @@ class Communicator:
         boundaries whenever the unit size allows it.
         """
         m = np.ascontiguousarray(matrix, dtype=np.int64)
+        if chunk_bytes is None:
+            # Work items: about 8 per CTA for the busiest rank (an uneven last round of 1 MiB items costs
+            # up to half the bandwidth at 148 CTAs), between 64 KiB and 1 MiB, a power of two.
+            busiest = int(max(m.sum(1).max(), m.sum(0).max())) * unit_bytes
+            chunk_bytes = 1 << 16
+            while chunk_bytes < (1 << 20) and chunk_bytes * 2 * self.ctas * 8 <= busiest:
+                chunk_bytes *= 2
         if "split_align" not in plan_opts:
             plan_opts["split_align"] = max(1, 16 // np.gcd(16, unit_bytes))
         key = (sched.matrix_hash(m), unit_bytes, transpose, str(kind), chunk_bytes, tuple(sorted((k, str(v)) for k, v in plan_opts.items())))

@@ -101,6 +101,15 @@ class ExpertParallel:
 
             dist.barrier(group=comm.group)
 
+    def close(self) -> None:
+        """Return this engine's symmetric allocations to the heap (collective: every rank, same order)."""
+        torch.cuda.synchronize(self.comm.device)
+        for name in ("dx_recv", "dy_recv", "y", "x_recv", "xs_recv", "xq_recv", "arrive", "flags", "counts"):
+            t = getattr(self, name, None)
+            if t is not None and hasattr(t, "_symm_off"):
+                self.comm.free(t)
+                setattr(self, name, None)
+
     # ---- helpers -----------------------------------------------------------------------------
     def _off(self, t: torch.Tensor) -> int:
         return t._symm_off
