@@ -114,6 +114,8 @@ struct SplitsArgs {
   int* block_base;             // [num_blocks][E] out
   int* send_base;              // [E] out: destination row of my first token for expert e
   int* send_cnt;               // [E] out: tokens I send to expert e
+  int* send_pos;               // [E] out (may be null): first index of expert e's entries in the sorted send list,
+                               // experts ordered by (local expert index, owner rank)
   int* group_off;              // [E/world + 1] out: padded row offsets of my experts
   int* group_rows;             // [E/world] out: real rows of my experts
   unsigned long long* arrive_target;  // [num_channels][E/world] in/out: cumulative rows expected
@@ -122,6 +124,9 @@ struct SplitsArgs {
   unsigned long long timeout_ns;
 };
 cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream);
+// list[send_pos[e] + rank of (t, j) among my entries for e] = t*K + j  (see SplitsArgs::send_pos).
+cudaError_t launch_build_send_list(const int* topk_idx, const int* slot_in_block, const int* block_base, const int* send_pos, int T, int K, int E,
+                                   int* list, cudaStream_t stream);
 cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* group_off, const int* group_rows, int groups, cudaStream_t stream);
 
 struct DispatchArgs {
@@ -133,6 +138,7 @@ struct DispatchArgs {
   const int* slot_in_block;    // [T, K]
   const int* block_base;       // [blocks][E]
   const int* send_base;        // [E]
+  const int* send_list;        // [T*K] or null: (token*K + slot) entries in sending order (sorted mode)
   int* dest_row;               // [T, K]: written when compute_rows != 0, else read
   int compute_rows;
   int fp8;                     // 1: send e4m3 bytes + one fp32 scale per 128 elements

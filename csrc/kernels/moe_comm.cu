@@ -56,14 +56,22 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
   constexpr int tpb = kRouteTokensPerBlock;
   const int chunks = a.H / 8;  // 16-byte chunks per row
-  for (int t = blockIdx.x * wpb + warp; t < a.T; t += gridDim.x * wpb) {
+  // Unsorted mode: one warp per token, the row is read once and stored to its K destinations.
+  // Sorted mode (send_list != null): one warp per (token, slot) entry, entries ordered by
+  // (local expert index, destination rank), so that every rank's expert 0 fills first, then
+  // expert 1, ... and the gated GEMM of the receivers can start while later experts still arrive.
+  const long long n_work = a.send_list ? static_cast<long long>(a.T) * a.K : a.T;
+  for (long long wi = blockIdx.x * wpb + warp; wi < n_work; wi += static_cast<long long>(gridDim.x) * wpb) {
+    int t, jbeg, jend;
+    if (a.send_list) { const int tj = a.send_list[wi]; t = tj / a.K; jbeg = tj % a.K; jend = jbeg + 1; }
+    else { t = static_cast<int>(wi); jbeg = 0; jend = a.K; }
     unsigned char* dst[kMaxK];
     float scale[kMaxK];
     int row_of[kMaxK];
 #pragma unroll
     for (int j = 0; j < kMaxK; ++j) {
       dst[j] = nullptr; scale[j] = 1.0f; row_of[j] = 0;
-      if (j < a.K) {
+      if (j >= jbeg && j < jend) {
         const long long tj = static_cast<long long>(t) * a.K + j;
         const int e = a.topk_idx[tj];
         int row;
@@ -97,7 +105,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
           if (a.row_scale) unpack8(v[u], f);
 #pragma unroll
           for (int j = 0; j < kMaxK; ++j) {
-            if (j >= a.K) break;
+            if (j < jbeg || j >= jend) continue;
             uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + (static_cast<long long>(row_of[j]) * a.H) * 2) + c;
             if (a.row_scale) {
               float g[8];
@@ -144,7 +152,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
         for (int i = 0; i < 16; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
-          if (j >= a.K || !active) break;
+          if (j < jbeg || j >= jend || !active) continue;
           uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
           *out = q;
           if ((lane & 7) == 0)

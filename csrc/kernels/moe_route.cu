@@ -158,6 +158,15 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
     for (int q = 0; q < le; ++q) base += s_tot[d * El + q];
     a.send_base[e] = base + before_me;
     a.send_cnt[e] = mine;
+    if (a.send_pos) {
+      // Entries are sent expert-slot by expert-slot: all ranks' local expert 0, then 1, ...
+      int pos = 0;
+      for (int q = 0; q < E; ++q) {
+        const int key_q = (q % El) * W + q / El, key_e = le * W + d;
+        if (key_q < key_e) pos += *reinterpret_cast<volatile int*>(my_counts + a.rank * E + q);
+      }
+      a.send_pos[e] = pos;
+    }
     if (d == a.rank) {
       a.group_off[le] = base;
       a.group_rows[le] = tot;
@@ -174,6 +183,15 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
       for (int q = 0; q < El; ++q) sent += *reinterpret_cast<volatile int*>(my_counts + s * E + d * El + q);
       a.traffic_matrix[i] = sent;
     }
+}
+
+__global__ void build_send_list_kernel(const int* __restrict__ topk_idx, const int* __restrict__ slot_in_block, const int* __restrict__ block_base,
+                                       const int* __restrict__ send_pos, int T, int K, int E, int* __restrict__ list) {
+  const long long tj = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (tj >= static_cast<long long>(T) * K) return;
+  const int e = topk_idx[tj];
+  const int t = static_cast<int>(tj / K);
+  list[send_pos[e] + block_base[static_cast<long long>(t / kTokensPerBlock) * E + e] + slot_in_block[tj]] = static_cast<int>(tj);
 }
 
 // Zeroes the rows between each group's real end and its padded end.
@@ -207,6 +225,15 @@ cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream) {
   if ((a.row_align != 128 && a.row_align != 256) || a.num_experts < 1 || a.num_experts > 1024 || a.world < 1 || a.world > a.num_experts || a.num_experts % a.world) return cudaErrorInvalidValue;
   int threads = (std::max(a.num_experts, a.world) + 31) / 32 * 32;
   splits_scan_kernel<<<1, threads, sizeof(int) * (a.num_experts + a.world), stream>>>(a);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_build_send_list(const int* topk_idx, const int* slot_in_block, const int* block_base, const int* send_pos, int T, int K, int E,
+                                   int* list, cudaStream_t stream) {
+  const long long n = static_cast<long long>(T) * K;
+  if (n == 0) return cudaSuccess;
+  build_send_list_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(topk_idx, slot_in_block, block_base, send_pos, T, K, E, list);
   note_launch();
   return cudaGetLastError();
 }

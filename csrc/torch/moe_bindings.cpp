@@ -97,7 +97,8 @@ void route_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int K, 
 
 void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint64_t epoch, torch::Tensor block_cnt, torch::Tensor block_base,
                  torch::Tensor send_base, torch::Tensor send_cnt, torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor arrive_target,
-                 c10::optional<torch::Tensor> traffic, int num_channels, int row_align, int cap_rows, const StatusPy& st, uint64_t timeout_ns) {
+                 c10::optional<torch::Tensor> traffic, int num_channels, int row_align, int cap_rows, const StatusPy& st, uint64_t timeout_ns,
+                 c10::optional<torch::Tensor> send_pos) {
   SplitsArgs a{};
   a.row_align = row_align;
   a.cap_rows = cap_rows;
@@ -113,6 +114,7 @@ void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint
   a.send_cnt = send_cnt.data_ptr<int>(); a.group_off = group_off.data_ptr<int>(); a.group_rows = group_rows.data_ptr<int>();
   a.arrive_target = reinterpret_cast<unsigned long long*>(arrive_target.data_ptr());
   a.traffic_matrix = ptr_or_null<int>(traffic);
+  a.send_pos = ptr_or_null<int>(send_pos);
   a.status = st.d; a.timeout_ns = timeout_ns;
   cu_check(launch_splits_scan(a, stream_now()), "splits_scan");
 }
@@ -125,7 +127,8 @@ void zero_pad_rows(torch::Tensor buf, torch::Tensor group_off, torch::Tensor gro
 
 void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, c10::optional<torch::Tensor> row_scale, torch::Tensor slot_in_block,
                    torch::Tensor block_base, torch::Tensor send_base, torch::Tensor dest_row, bool compute_rows, bool fp8, int64_t recv_off,
-                   int64_t scale_off, int64_t arrive_off, int64_t entry_flags_off, uint64_t entry_epoch, const StatusPy& st, uint64_t timeout_ns, int ctas) {
+                   int64_t scale_off, int64_t arrive_off, int64_t entry_flags_off, uint64_t entry_epoch, const StatusPy& st, uint64_t timeout_ns, int ctas,
+                   c10::optional<torch::Tensor> send_list) {
   want(x, torch::kBFloat16, "x"); want(topk_idx, torch::kInt32, "topk_idx"); want(dest_row, torch::kInt32, "dest_row");
   DispatchArgs a{};
   a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
@@ -134,6 +137,7 @@ void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, 
   a.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()); a.topk_idx = topk_idx.data_ptr<int>(); a.row_scale = ptr_or_null<const float>(row_scale);
   a.slot_in_block = slot_in_block.data_ptr<int>(); a.block_base = block_base.data_ptr<int>(); a.send_base = send_base.data_ptr<int>();
   a.dest_row = dest_row.data_ptr<int>(); a.compute_rows = compute_rows; a.fp8 = fp8;
+  a.send_list = ptr_or_null<const int>(send_list);
   a.recv_heap_off = recv_off; a.scale_heap_off = scale_off; a.arrive_heap_off = arrive_off;
   a.entry_flags_heap_off = entry_flags_off; a.entry_epoch = entry_epoch; a.status = st.d; a.timeout_ns = timeout_ns;
   cu_check(launch_dispatch_push(a, ctas, stream_now()), "dispatch_push");
@@ -163,6 +167,13 @@ void bind_moe(py::module_& m) {
   m.def("route_topk", &route_topk);
   m.def("splits_scan", &splits_scan);
   m.def("zero_pad_rows", &zero_pad_rows);
+  m.def("build_send_list", [](torch::Tensor topk_idx, torch::Tensor slot_in_block, torch::Tensor block_base, torch::Tensor send_pos, torch::Tensor list) {
+    want(topk_idx, torch::kInt32, "topk_idx"); want(send_pos, torch::kInt32, "send_pos"); want(list, torch::kInt32, "list");
+    TORCH_CHECK(list.numel() >= topk_idx.numel(), "build_send_list: list too short");
+    cu_check(launch_build_send_list(topk_idx.data_ptr<int>(), slot_in_block.data_ptr<int>(), block_base.data_ptr<int>(), send_pos.data_ptr<int>(),
+                                    static_cast<int>(topk_idx.size(0)), static_cast<int>(topk_idx.size(1)), static_cast<int>(send_pos.numel()),
+                                    list.data_ptr<int>(), stream_now()), "build_send_list");
+  });
   m.def("dispatch_push", &dispatch_push);
   m.def("combine_pull", &combine_pull);
   m.def("peer_signal", [](const HeapPy& heap, int64_t flags_off, uint64_t epoch) {

@@ -85,11 +85,11 @@ def heap_bytes_needed(world, tokens, hidden, top_k, experts_per_gpu, fp8):
     return int(cap * hidden * (3 if fp8 else 4.2)) + (256 << 20)
 
 
-def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False):
+def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False, overlap=False):
     """Runs the forward layer on an existing communicator and returns the result dict (every rank)."""
     rank, world = comm.rank, comm.world
     E, K, H, I, T, El = experts_per_gpu * world, top_k, hidden, inter, tokens, experts_per_gpu
-    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False)
+    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False, overlap_dispatch=overlap)
     g = torch.Generator(device="cuda").manual_seed(7)      # same on every rank: the bias is replicated
     bias = torch.randn(E, generator=g, device="cuda") * 1.5
     gr = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -110,7 +110,8 @@ def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_
         rs = eng.route(logits, bias)
         ev[1].record()
         eng.dispatch(x, rs)
-        C.wait_counters(eng._arrive_ptr(0), eng.arrive_target[0], eng.status, eng.timeout_ns)  # phase boundary for timing only
+        if not overlap:
+            C.wait_counters(eng._arrive_ptr(0), eng.arrive_target[0], eng.status, eng.timeout_ns)  # phase boundary for timing only
         ev[2].record()
         eng.experts_forward(w13, w2, rs)
         ev[3].record()
@@ -135,7 +136,7 @@ def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_
     combine_alone_us = _max_over_ranks([c0.elapsed_time(c1) * 1e3 / iters], world)[0]
     route_us, dispatch_us, experts_us, combine_us = _max_over_ranks(acc, world)
     tm = eng.traffic_matrix().cpu().numpy()
-    res = {"bench": "moe_forward", "world": world, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K,
+    res = {"bench": "moe_forward", "world": world, "overlap_dispatch": overlap, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K,
            "dispatch_dtype": "fp8_e4m3_1x128" if fp8 else "bf16", "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1),
            "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1), "combine_alone_us": round(combine_alone_us, 1),
            "dispatch_plus_combine_us": round(dispatch_us + combine_alone_us, 1),
@@ -178,6 +179,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--skip-nccl", action="store_true")
+    ap.add_argument("--overlap", action="store_true", help="send rows expert by expert on a side stream while the gated GEMM runs (dispatch_us then only times the launch)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -185,7 +187,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Communicator(heap_bytes=heap_bytes_needed(world, a.tokens, a.hidden, a.top_k, a.experts_per_gpu, a.fp8), device=local, timeout_s=20.0)
-    res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl)
+    res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap)
     if rank == 0:
         print(json.dumps(res), flush=True)
     if world > 1:

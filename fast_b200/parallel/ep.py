@@ -40,7 +40,7 @@ class RouteState:
 
 class ExpertParallel:
     def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
-                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None):
+                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None, overlap_dispatch: bool = False):
         C = runtime.ext()
         self._C, self.comm = C, comm
         W = comm.world
@@ -48,6 +48,10 @@ class ExpertParallel:
         assert not training or inter % 256 == 0, "training needs inter % 256 == 0 (dgrad output tiles are 256 wide)"
         self.E, self.El, self.H, self.I, self.K, self.T = num_experts, num_experts // W, hidden, inter, top_k, max_tokens
         self.fp8, self.training = fp8_dispatch, training
+        # overlap_dispatch: rows are sent expert by expert on a side stream while the gated expert GEMM of
+        # the main stream already consumes the experts that are complete (forward dispatch only).
+        self.overlap = overlap_dispatch
+        self.side = torch.cuda.Stream(device=comm.device) if overlap_dispatch else None
         # dispatch / combine run alone on the stream: fill the machine (4 CTAs of 256 threads per SM)
         self.comm_ctas = comm_ctas or 4 * torch.cuda.get_device_properties(comm.device).multi_processor_count
         worst = W * max_tokens * min(top_k, self.El) + 256 * self.El
@@ -88,6 +92,8 @@ class ExpertParallel:
         self.slot_in_block = torch.zeros(blocks * C.ROUTE_TOKENS_PER_BLOCK, top_k, **i32)
         self.send_base = torch.zeros(self.E, **i32)
         self.send_cnt = torch.zeros(self.E, **i32)
+        self.send_pos = torch.zeros(self.E, **i32)
+        self.send_list = torch.zeros(max_tokens * top_k, **i32) if overlap_dispatch else None
         self.group_off = torch.zeros(self.El + 1, **i32)
         self.group_rows = torch.zeros(self.El, **i32)
         self.arrive_target = torch.zeros(2, self.El, dtype=torch.int64, device=dev)
@@ -138,18 +144,44 @@ class ExpertParallel:
         C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
                       self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1,
                       gemm.row_align(), self.cap, self.status,
-                      self.timeout_ns)
+                      self.timeout_ns, self.send_pos if self.overlap else None)
         return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows, self.epoch)
 
     def dispatch(self, x: torch.Tensor, rs: RouteState) -> None:
         C = self._C
-        if self.fp8:
-            C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, True,
-                            self._off(self.xq_recv), self._off(self.xs_recv), self.arrive._symm_off, 0, 0, self.status, self.timeout_ns, self.comm_ctas)
-        else:
-            C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
-            C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, False,
-                            self._off(self.x_recv), 0, self.arrive._symm_off, 0, 0, self.status, self.timeout_ns, self.comm_ctas)
+        send_list = None
+        if not self.fp8:
+            C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)  # on the main stream: ordered before any consumer
+        if self.overlap:
+            # Side stream: ordered after routing, concurrent with whatever the main stream queues next
+            # (the gated expert GEMM). The main stream re-joins in experts_forward.
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self.side.wait_event(ev)
+            x.record_stream(self.side)
+            ctx = torch.cuda.stream(self.side)
+            ctx.__enter__()
+            C.build_send_list(rs.topk_idx, rs.slot_in_block, rs.block_base, self.send_pos, self.send_list)
+            send_list = self.send_list
+        try:
+            if self.fp8:
+                C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, True,
+                                self._off(self.xq_recv), self._off(self.xs_recv), self.arrive._symm_off, 0, 0, self.status, self.timeout_ns,
+                                self.comm_ctas, send_list)
+            else:
+                C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, False,
+                                self._off(self.x_recv), 0, self.arrive._symm_off, 0, 0, self.status, self.timeout_ns, self.comm_ctas, send_list)
+        finally:
+            if self.overlap:
+                self._dispatch_done = torch.cuda.Event()
+                self._dispatch_done.record(self.side)
+                ctx.__exit__(None, None, None)
+
+    def _join_dispatch(self) -> None:
+        """Main stream waits for the side-stream dispatch (its dest_row table and its use of x)."""
+        if self.overlap and getattr(self, "_dispatch_done", None) is not None:
+            torch.cuda.current_stream().wait_event(self._dispatch_done)
+            self._dispatch_done = None
 
     def experts_forward(self, w13: torch.Tensor, w2: torch.Tensor, rs: RouteState) -> None:
         C = self._C
@@ -161,6 +193,7 @@ class ExpertParallel:
             gate = None
         gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate)
         gemm.grouped_gemm_fwd(self.act, w2, rs.group_off, self.y)
+        self._join_dispatch()
         C.peer_signal(self.comm.heap, self._flag_off(1), rs.epoch)
 
     def combine(self, rs: RouteState, weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -213,7 +246,7 @@ class ExpertParallel:
         C.zero_pad_rows(self.dy_recv, rs.group_off, rs.group_rows)
         C.dispatch_push(self.comm.heap, grad_out, rs.topk_idx, weights, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, False, False,
                         self._off(self.dy_recv), 0, self.arrive._symm_off + self.El * 8, self._flag_off(2), rs.epoch, self.status, self.timeout_ns,
-                        self.comm_ctas)
+                        self.comm_ctas, None)
         gate = (self._arrive_ptr(1), self.arrive_target[1])
         gemm.grouped_gemm_dgrad(self.dy_recv, w2, rs.group_off, self.dact, gate=gate)
         gemm.grouped_gemm_wgrad(self.dy_recv, self.act, rs.group_off, dw2)

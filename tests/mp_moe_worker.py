@@ -17,8 +17,8 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl")
     comm = Communicator(heap_bytes=512 << 20)
-    for (E, K, H, I, T, fp8) in [(8, 2, 256, 256, 700, False), (16, 4, 512, 256, 333 + 17 * rank, False), (8, 2, 256, 256, 500, True)]:
-        layer = MoELayer(comm, H, I, E, K, max_tokens=1024, fp8_dispatch=fp8, training=not fp8)
+    for ci, (E, K, H, I, T, fp8) in enumerate([(8, 2, 256, 256, 700, False), (16, 4, 512, 256, 333 + 17 * rank, False), (8, 2, 256, 256, 500, True)]):
+        layer = MoELayer(comm, H, I, E, K, max_tokens=1024, fp8_dispatch=fp8, training=not fp8, overlap_dispatch=(ci == 1))
         g = torch.Generator(device="cuda").manual_seed(100 + rank)
         x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16).requires_grad_(not fp8)
         gout = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
