@@ -96,6 +96,13 @@ def run(args):
     max_row = max(args.sizes)
     # Receive buffers must hold the heaviest column of any matrix that will be drawn.
     need = max_row
+    def draw(size, skew, mi):
+        if args.mode == "random":
+            return sched.workload_uniform(world, 2 * size // world // 16, 1000 * mi + 7, True) * 16
+        return sched.workload_zipf_rows(world, skew, size, 1000 * mi + 7, 16)
+
+    if args.mode == "random":
+        need = max(int(draw(size, None, mi).sum(0).max()) for size in args.sizes for mi in range(args.matrices))
     if args.mode == "skewed":
         for size in args.sizes:
             for skew in args.skews:
@@ -108,20 +115,20 @@ def run(args):
     comm = Communicator(heap_bytes=need * (4 if args.servers else 1) + (128 << 20), topo=topo, ctas=args.ctas or None, threads=args.threads)
     out = comm.alloc(need, torch.uint8)
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    inp = torch.randn(max_row // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
+    inp = torch.randn(max(max_row, need) // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
     nccl_out = torch.empty(need, dtype=torch.uint8, device="cuda")
     results = []
     for size in args.sizes:
         skews = args.skews if args.mode == "skewed" else [None]
         for skew in skews:
             acc = {}
-            nmat = args.matrices if args.mode == "skewed" else 1
+            nmat = args.matrices if args.mode != "uniform" else 1
             for mi in range(nmat):
                 if args.mode == "uniform":
                     per = max(size // world // 16 * 16, 16)
                     m = np.full((world, world), per, dtype=np.int64)
                 else:
-                    m = sched.workload_zipf_rows(world, skew, size, 1000 * mi + 7, 16)
+                    m = draw(size, skew, mi)
                 in_splits = [int(x) for x in m[rank]]
                 out_splits = [int(x) for x in m[:, rank]]
                 sent = int(m[rank].sum())
@@ -160,7 +167,7 @@ def run(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="skewed", choices=["uniform", "skewed"])
+    ap.add_argument("--mode", default="skewed", choices=["uniform", "skewed", "random"], help="uniform: equal splits; skewed: Zipf rows; random: i.i.d. uniform entries (mean row = size)")
     ap.add_argument("--sizes", type=int, nargs="+", default=[64 << 20])
     ap.add_argument("--skews", type=float, nargs="+", default=[0.0, 0.5, 1.0, 1.5])
     ap.add_argument("--matrices", type=int, default=4)

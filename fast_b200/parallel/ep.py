@@ -39,6 +39,15 @@ class RouteState:
 
 
 class ExpertParallel:
+    """One MoE layer's expert-parallel state on one rank.
+
+    The receive, activation and gradient buffers belong to the engine and are overwritten by the
+    next ``route``: a forward pass must be followed by its backward pass (or be forward-only)
+    before the next forward of the same engine; use one engine per layer. Every rank of the
+    communicator must call the same sequence of methods (the count exchange inside ``route`` is the
+    hand-shake that makes buffer reuse safe across ranks).
+    """
+
     def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
                  capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None, overlap_dispatch: bool = False):
         C = runtime.ext()
