@@ -102,7 +102,7 @@ def run(args):
         return sched.workload_zipf_rows(world, skew, size, 1000 * mi + 7, 16)
 
     if args.mode == "random":
-        need = max(int(draw(size, None, mi).sum(0).max()) for size in args.sizes for mi in range(args.matrices))
+        need = max(int(max(draw(size, None, mi).sum(0).max(), draw(size, None, mi).sum(1).max())) for size in args.sizes for mi in range(args.matrices))
     if args.mode == "skewed":
         for size in args.sizes:
             for skew in args.skews:
