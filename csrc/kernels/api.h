@@ -107,6 +107,7 @@ struct SplitsArgs {
   int rank, world, num_experts, num_blocks, num_channels;
   int row_align;               // group row ranges are padded to this many rows (128 or 256)
   int cap_rows;                // rows of the receive buffers; a step that needs more is refused on every rank
+  int counts_in_smem;          // set by the launcher: the [world][E] count matrix fits in shared memory
   long long counts_heap_off;   // int [world][E] on every rank
   long long flags_heap_off;    // u64 [world] on every rank: epoch of the last counts row received from each rank
   unsigned long long epoch;

@@ -98,9 +98,14 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
   unsigned long long* my_flags = reinterpret_cast<unsigned long long*>(my_slab + a.flags_heap_off);  // [W]
   int mine = 0;
   if (e < E) {
-    for (int b = 0; b < a.num_blocks; ++b) {
-      a.block_base[static_cast<long long>(b) * E + e] = mine;
-      mine += a.block_cnt[static_cast<long long>(b) * E + e];
+    // Eight independent loads in flight per round (the running sum is the only serial part).
+    for (int b0 = 0; b0 < a.num_blocks; b0 += 8) {
+      int c[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) c[u] = b0 + u < a.num_blocks ? __ldg(a.block_cnt + static_cast<long long>(b0 + u) * E + e) : 0;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (b0 + u < a.num_blocks) { a.block_base[static_cast<long long>(b0 + u) * E + e] = mine; mine += c[u]; }
     }
     // All-gather by stores: my row of the count matrix goes to every rank (myself included).
     for (int r = 0; r < W; ++r) {
@@ -122,15 +127,20 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
   }
   __syncthreads();
   if (!s_ok) return;
+  // The count matrix is read once (coalesced, W independent loads per thread) and kept in shared
+  // memory when it fits; every later loop reads the copy.
+  int* s_cnt = s_tot + E;  // [W][E] when a.counts_in_smem
   int tot = 0, before_me = 0;
   if (e < E) {
     for (int s = 0; s < W; ++s) {
       const int c = *reinterpret_cast<volatile int*>(my_counts + s * E + e);
+      if (a.counts_in_smem) s_cnt[s * E + e] = c;
       tot += c;
       if (s < a.rank) before_me += c;
     }
     s_tot[e] = (tot + a.row_align - 1) / a.row_align * a.row_align;
   }
+  auto count_at = [&](int s, int q) { return a.counts_in_smem ? s_cnt[s * E + q] : *reinterpret_cast<volatile int*>(my_counts + s * E + q); };
   __shared__ int s_over;
   if (e == 0) s_over = 0;
   __syncthreads();
@@ -163,7 +173,7 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
       int pos = 0;
       for (int q = 0; q < E; ++q) {
         const int key_q = (q % El) * W + q / El, key_e = le * W + d;
-        if (key_q < key_e) pos += *reinterpret_cast<volatile int*>(my_counts + a.rank * E + q);
+        if (key_q < key_e) pos += count_at(a.rank, q);
       }
       a.send_pos[e] = pos;
     }
@@ -180,7 +190,7 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
     for (int i = threadIdx.x; i < W * W; i += blockDim.x) {
       const int s = i / W, d = i % W;
       int sent = 0;
-      for (int q = 0; q < El; ++q) sent += *reinterpret_cast<volatile int*>(my_counts + s * E + d * El + q);
+      for (int q = 0; q < El; ++q) sent += count_at(s, d * El + q);
       a.traffic_matrix[i] = sent;
     }
 }
@@ -224,7 +234,10 @@ cudaError_t launch_route_topk(const float* logits, const float* bias, int T, int
 cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream) {
   if ((a.row_align != 128 && a.row_align != 256) || a.num_experts < 1 || a.num_experts > 1024 || a.world < 1 || a.world > a.num_experts || a.num_experts % a.world) return cudaErrorInvalidValue;
   int threads = (std::max(a.num_experts, a.world) + 31) / 32 * 32;
-  splits_scan_kernel<<<1, threads, sizeof(int) * (a.num_experts + a.world), stream>>>(a);
+  SplitsArgs b = a;
+  b.counts_in_smem = static_cast<long long>(a.world) * a.num_experts <= 8192 ? 1 : 0;  // 32 KiB of the 48 KiB default
+  const size_t smem = sizeof(int) * (a.num_experts + a.world + (b.counts_in_smem ? a.world * a.num_experts : 0));
+  splits_scan_kernel<<<1, threads, smem, stream>>>(b);
   note_launch();
   return cudaGetLastError();
 }
