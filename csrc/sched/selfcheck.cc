@@ -1,0 +1,81 @@
+// Native self-check of the scheduler library (no Python, no GPU): random matrices over a range of
+// topologies; every plan must validate, deliver the matrix exactly, survive a binary round trip
+// and replay bit-exactly on host buffers. Exit code 0 = all good. Mirrors the role of the
+// reference's DecompositionTester (simulation/test.cpp:15-60) for the whole planner.
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "plan.h"
+
+using namespace fastb;
+
+static int failures = 0;
+#define CHECK(cond, ...)                                   \
+  do {                                                     \
+    if (!(cond)) { ++failures; std::printf("FAIL %s:%d: ", __FILE__, __LINE__); std::printf(__VA_ARGS__); std::printf("\n"); } \
+  } while (0)
+
+static void replay_check(const Plan& p, int unit_bytes, uint64_t seed) {
+  const int n = p.matrix.n;
+  std::vector<std::vector<uint8_t>> in(n), out(n);
+  std::vector<const uint8_t*> ip;
+  std::vector<uint8_t*> op;
+  uint64_t x = seed * 0x9e3779b97f4a7c15ull + 1;
+  for (int r = 0; r < n; ++r) {
+    in[r].resize(static_cast<size_t>(p.buffers[r].input_units) * unit_bytes);
+    out[r].assign(static_cast<size_t>(p.buffers[r].output_units) * unit_bytes, 0xEE);
+    for (auto& b : in[r]) { x = x * 6364136223846793005ull + 1442695040888963407ull; b = static_cast<uint8_t>(x >> 56); }
+    ip.push_back(in[r].data());
+    op.push_back(out[r].data());
+  }
+  const int64_t written = execute_on_host(p, unit_bytes, ip, op);
+  CHECK(written == p.matrix.total() * unit_bytes, "replay wrote %lld bytes, matrix has %lld", static_cast<long long>(written), static_cast<long long>(p.matrix.total() * unit_bytes));
+  for (int d = 0; d < n; ++d)
+    for (int s = 0; s < n; ++s) {
+      const int64_t len = p.matrix.at(s, d) * unit_bytes;
+      const uint8_t* a = in[s].data() + p.in_disp[static_cast<size_t>(s) * n + d] * unit_bytes;
+      const uint8_t* b = out[d].data() + p.out_disp[static_cast<size_t>(d) * n + s] * unit_bytes;
+      CHECK(len == 0 || std::memcmp(a, b, static_cast<size_t>(len)) == 0, "segment %d->%d differs", s, d);
+    }
+}
+
+int main() {
+  const int topo[][2] = {{1, 1}, {1, 4}, {4, 1}, {2, 2}, {2, 4}, {3, 3}, {8, 1}, {4, 2}};
+  const PlanKind kinds[] = {PlanKind::kStaged, PlanKind::kSingleBurst, PlanKind::kFanout, PlanKind::kSpreadOut};
+  int plans = 0;
+  for (auto& t : topo) {
+    const int S = t[0], G = t[1], n = S * G;
+    for (uint64_t seed = 0; seed < 6; ++seed) {
+      Matrix m = seed % 3 == 2 && n > 1 ? workload_zipf_rows(n, 1.2, 50000, seed, 4) : workload_uniform(n, 400, seed * 7 + n, seed % 2 == 1);
+      Decomposition d = decompose(m, seed % 2 ? MatchPolicy::kBottleneck : MatchPolicy::kFirstFit, 1);
+      CHECK(verify_decomposition(d), "decomposition not exact (n=%d seed=%llu)", n, static_cast<unsigned long long>(seed));
+      CHECK(d.line_sum == m.max_line_sum(), "line sum mismatch");
+      for (PlanKind k : kinds)
+        for (int64_t align : {int64_t{1}, int64_t{16}}) {
+          PlanOptions o;
+          o.kind = k; o.split_align = align; o.transpose = seed % 2 == 0;
+          Plan p = build_plan(m, Topology{S, G}, o);
+          const std::string err = validate_plan(p);
+          CHECK(err.empty(), "invalid plan S=%d G=%d kind=%d: %s", S, G, static_cast<int>(k), err.c_str());
+          CHECK(delivered_matrix(p) == p.matrix, "delivery differs from the matrix");
+          Plan q = plan_from_bytes(plan_to_bytes(p));
+          CHECK(validate_plan(q).empty() && q.ops.size() == p.ops.size() && q.matrix_hash == p.matrix_hash, "binary round trip");
+          replay_check(p, 3, seed);
+          for (int r = 0; r < n; ++r) {
+            LowerOptions lo; lo.unit_bytes = 2; lo.chunk_bytes = 256;
+            RankProgram g = lower_for_rank(p, r, lo);
+            int64_t sent = 0;
+            for (const WorkItem& w : g.items) sent += w.bytes;
+            int64_t want = 0;
+            for (const Op& op : p.ops) if (op.src_rank == r) want += op.len * 2;
+            CHECK(sent == want, "lowering lost bytes on rank %d", r);
+            CHECK(g.expect_output_bytes == p.matrix.col_sum(r) * 2, "expected output bytes on rank %d", r);
+          }
+          ++plans;
+        }
+    }
+  }
+  std::printf("{\"selfcheck\":\"sched\",\"plans\":%d,\"failures\":%d}\n", plans, failures);
+  return failures ? 1 : 0;
+}

@@ -61,6 +61,16 @@ def build_sim(force=False):
     return out
 
 
+def build_selfcheck(force=False):
+    """Native self-check executable of the scheduler library (build/fastb-selfcheck)."""
+    out = ROOT / "build" / "fastb-selfcheck"
+    out.parent.mkdir(exist_ok=True)
+    srcs = [CSRC / "sched" / "selfcheck.cc"] + [CSRC / "sched" / f"{s}.cc" for s in SCHED_SRCS]
+    if force or _stale(out, srcs + _headers("sched")):
+        _run(["g++", "-std=c++17", "-O2", "-Wall", *srcs, "-o", out])
+    return out
+
+
 def cuda_sources():
     return sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "runtime").glob("*.cu"))
 
@@ -108,6 +118,7 @@ def build_cuda(force=False, verbose=False):
 def build_all(force=False, verbose=False):
     build_sched(force)
     build_sim(force)
+    build_selfcheck(force)
     if cuda_sources():
         build_cuda(force, verbose)
 

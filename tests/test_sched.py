@@ -249,3 +249,13 @@ def test_simulator_cli_config1(tmp_path):
     assert j["modeled_us"] >= j["lower_bound_us"] > 0
     out = subprocess.run([str(exe), "verify", "--max-dim", "32", "--reps", "2"], capture_output=True, text=True, check=True).stdout
     assert json.loads(out.splitlines()[-1])["failures"] == 0
+
+
+def test_native_selfcheck():
+    """The C++ self-check of the scheduler library (plans, replay, lowering, serialisation) passes."""
+    from fast_b200 import _build
+
+    exe = _build.build_selfcheck()
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["failures"] == 0
