@@ -111,6 +111,9 @@ struct SplitsArgs {
   long long counts_heap_off;   // int [world][E] on every rank
   long long flags_heap_off;    // u64 [world] on every rank: epoch of the last counts row received from each rank
   unsigned long long epoch;
+  // Graph-replayable epochs: when non-null, the kernel increments *epoch_dev and uses the new value
+  // instead of `epoch` (a value baked into a captured launch would repeat on every replay).
+  unsigned long long* epoch_dev;
   const int* block_cnt;        // [num_blocks][E]
   int* block_base;             // [num_blocks][E] out
   int* send_base;              // [E] out: destination row of my first token for expert e
@@ -162,6 +165,7 @@ struct CombineArgs {
   long long src_heap_off;      // bf16 [cap, H] on every rank
   long long ready_flags_heap_off;  // u64 [world] in my slab: peer d's rows are final once flags[d] >= ready_epoch
   unsigned long long ready_epoch;
+  const unsigned long long* epoch_dev;  // when non-null, *epoch_dev replaces ready_epoch (see SplitsArgs)
   __nv_bfloat16* out;          // [T, H] sum_j w * row_j (null in dot mode)
   const __nv_bfloat16* dot_with;  // dot mode: [T, H]
   float* dot_out;              // dot mode: [T, K] = <dot_with[t], row_j>
@@ -171,7 +175,8 @@ struct CombineArgs {
 cudaError_t launch_combine_pull(const CombineArgs& a, int ctas, cudaStream_t stream);
 
 // Writes `epoch` (release, system scope) into slot `rank` of the flag array of every rank.
-cudaError_t launch_peer_signal(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch, cudaStream_t stream);
+cudaError_t launch_peer_signal(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch,
+                               const unsigned long long* epoch_dev, cudaStream_t stream);
 // Bounded wait until counter[i] >= target[i] for all i < n (one thread each).
 cudaError_t launch_wait_counters(const unsigned long long* counter, const unsigned long long* target, int n, DeviceStatus* status,
                                  unsigned long long timeout_ns, cudaStream_t stream);

@@ -177,9 +177,10 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
   if (threadIdx.x == 0) s_ok = 1;
   if (*reinterpret_cast<volatile unsigned long long*>(&a.status->abort) != 0ull) return;
   __syncthreads();
-  if (a.ready_epoch != 0) {
+  const unsigned long long ready_epoch = a.epoch_dev ? *a.epoch_dev : a.ready_epoch;
+  if (ready_epoch != 0) {
     const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(static_cast<unsigned char*>(a.peer_table[a.rank]) + a.ready_flags_heap_off);
-    if (threadIdx.x < a.world && !wait_ge_bounded(flags + threadIdx.x, a.ready_epoch, a.status, kSiteCombineReady, threadIdx.x, a.timeout_ns)) s_ok = 0;
+    if (threadIdx.x < a.world && !wait_ge_bounded(flags + threadIdx.x, ready_epoch, a.status, kSiteCombineReady, threadIdx.x, a.timeout_ns)) s_ok = 0;
     __syncthreads();
     if (!s_ok) return;
   }
@@ -254,7 +255,9 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
   }
 }
 
-__global__ void peer_signal_kernel(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch) {
+__global__ void peer_signal_kernel(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch,
+                                   const unsigned long long* epoch_dev) {
+  if (epoch_dev) epoch = *epoch_dev;
   if (threadIdx.x < world) {
     __threadfence_system();
     unsigned long long* dst = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(peer_table[threadIdx.x]) + flags_heap_off);
@@ -286,8 +289,9 @@ cudaError_t launch_combine_pull(const CombineArgs& a, int ctas, cudaStream_t str
   return cudaGetLastError();
 }
 
-cudaError_t launch_peer_signal(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch, cudaStream_t stream) {
-  peer_signal_kernel<<<1, 64, 0, stream>>>(peer_table, rank, world, flags_heap_off, epoch);
+cudaError_t launch_peer_signal(void* const* peer_table, int rank, int world, long long flags_heap_off, unsigned long long epoch,
+                               const unsigned long long* epoch_dev, cudaStream_t stream) {
+  peer_signal_kernel<<<1, 64, 0, stream>>>(peer_table, rank, world, flags_heap_off, epoch, epoch_dev);
   note_launch();
   return cudaGetLastError();
 }

@@ -96,6 +96,10 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
   unsigned char* my_slab = static_cast<unsigned char*>(a.peer_table[a.rank]);
   int* my_counts = reinterpret_cast<int*>(my_slab + a.counts_heap_off);                       // [W][E]
   unsigned long long* my_flags = reinterpret_cast<unsigned long long*>(my_slab + a.flags_heap_off);  // [W]
+  __shared__ unsigned long long s_epoch;
+  if (e == 0) s_epoch = a.epoch_dev ? (*a.epoch_dev = *a.epoch_dev + 1ull) : a.epoch;
+  __syncthreads();
+  const unsigned long long epoch = s_epoch;
   int mine = 0;
   if (e < E) {
     // Eight independent loads in flight per round (the running sum is the only serial part).
@@ -117,13 +121,13 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
   __syncthreads();
   if (e < W) {
     unsigned long long* dst = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[e]) + a.flags_heap_off);
-    st_release_sys(dst + a.rank, a.epoch);
+    st_release_sys(dst + a.rank, epoch);
   }
   __shared__ int s_ok;
   if (e == 0) s_ok = 1;
   __syncthreads();
   if (e < W) {
-    if (!wait_ge_bounded(my_flags + e, a.epoch, a.status, kSiteCountsArrive, e, a.timeout_ns)) s_ok = 0;
+    if (!wait_ge_bounded(my_flags + e, epoch, a.status, kSiteCountsArrive, e, a.timeout_ns)) s_ok = 0;
   }
   __syncthreads();
   if (!s_ok) return;

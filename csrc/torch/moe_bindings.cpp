@@ -98,7 +98,7 @@ void route_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int K, 
 void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint64_t epoch, torch::Tensor block_cnt, torch::Tensor block_base,
                  torch::Tensor send_base, torch::Tensor send_cnt, torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor arrive_target,
                  c10::optional<torch::Tensor> traffic, int num_channels, int row_align, int cap_rows, const StatusPy& st, uint64_t timeout_ns,
-                 c10::optional<torch::Tensor> send_pos) {
+                 c10::optional<torch::Tensor> send_pos, int64_t epoch_dev_ptr) {
   SplitsArgs a{};
   a.row_align = row_align;
   a.cap_rows = cap_rows;
@@ -115,6 +115,7 @@ void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint
   a.arrive_target = reinterpret_cast<unsigned long long*>(arrive_target.data_ptr());
   a.traffic_matrix = ptr_or_null<int>(traffic);
   a.send_pos = ptr_or_null<int>(send_pos);
+  a.epoch_dev = reinterpret_cast<unsigned long long*>(epoch_dev_ptr);
   a.status = st.d; a.timeout_ns = timeout_ns;
   cu_check(launch_splits_scan(a, stream_now()), "splits_scan");
 }
@@ -145,12 +146,13 @@ void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, 
 
 void combine_pull(const HeapPy& heap, int num_experts, torch::Tensor topk_idx, torch::Tensor dest_row, c10::optional<torch::Tensor> weights, int64_t src_off,
                   int64_t ready_off, uint64_t ready_epoch, c10::optional<torch::Tensor> out, c10::optional<torch::Tensor> dot_with,
-                  c10::optional<torch::Tensor> dot_out, int H, const StatusPy& st, uint64_t timeout_ns, int ctas) {
+                  c10::optional<torch::Tensor> dot_out, int H, const StatusPy& st, uint64_t timeout_ns, int ctas, int64_t epoch_dev_ptr) {
   CombineArgs a{};
   a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world(); a.num_experts = num_experts;
   a.T = static_cast<int>(topk_idx.size(0)); a.K = static_cast<int>(topk_idx.size(1)); a.H = H;
   a.topk_idx = topk_idx.data_ptr<int>(); a.dest_row = dest_row.data_ptr<int>(); a.weights = ptr_or_null<const float>(weights);
   a.src_heap_off = src_off; a.ready_flags_heap_off = ready_off; a.ready_epoch = ready_epoch;
+  a.epoch_dev = reinterpret_cast<const unsigned long long*>(epoch_dev_ptr);
   a.out = ptr_or_null<__nv_bfloat16>(out); a.dot_with = ptr_or_null<const __nv_bfloat16>(dot_with); a.dot_out = ptr_or_null<float>(dot_out);
   TORCH_CHECK((a.out != nullptr) != (a.dot_out != nullptr), "combine_pull: give either out or dot_out");
   a.status = st.d; a.timeout_ns = timeout_ns;
@@ -176,8 +178,9 @@ void bind_moe(py::module_& m) {
   });
   m.def("dispatch_push", &dispatch_push);
   m.def("combine_pull", &combine_pull);
-  m.def("peer_signal", [](const HeapPy& heap, int64_t flags_off, uint64_t epoch) {
-    cu_check(launch_peer_signal(heap.h->device_peer_table(), heap.h->rank(), heap.h->world(), flags_off, epoch, stream_now()), "peer_signal");
+  m.def("peer_signal", [](const HeapPy& heap, int64_t flags_off, uint64_t epoch, int64_t epoch_dev_ptr) {
+    cu_check(launch_peer_signal(heap.h->device_peer_table(), heap.h->rank(), heap.h->world(), flags_off, epoch,
+                                reinterpret_cast<const unsigned long long*>(epoch_dev_ptr), stream_now()), "peer_signal");
   });
   m.def("wait_counters", [](int64_t counter_ptr, torch::Tensor target, const StatusPy& st, uint64_t timeout_ns) {
     cu_check(launch_wait_counters(reinterpret_cast<const unsigned long long*>(counter_ptr), reinterpret_cast<const unsigned long long*>(target.data_ptr()),

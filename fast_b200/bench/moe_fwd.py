@@ -169,6 +169,39 @@ def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_
     return res
 
 
+def measure_graph(comm, tokens, hidden, inter, experts_per_gpu, top_k, iters=50):
+    """Whole forward layer (gate GEMM to combined output) launched eagerly vs replayed from one CUDA
+    graph; the difference is launch and host overhead, which dominates at small token counts."""
+    from ..models import MoELayer
+
+    world = comm.world
+    layer = MoELayer(comm, hidden, inter, experts_per_gpu * world, top_k, max_tokens=tokens, training=False, graph_mode=True)
+    layer.eval()
+    layer.capture(tokens)
+    x = torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16)
+
+    def timed(fn):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return _max_over_ranks([e0.elapsed_time(e1) * 1e3 / iters], world)[0]
+
+    with torch.no_grad():
+        eager = timed(lambda: layer._infer(x))
+        graph = timed(lambda: layer.forward_graphed(x))
+    comm.check()
+    return {"bench": "moe_forward_graph", "world": world, "tokens_per_rank": tokens, "hidden": hidden, "inter": inter,
+            "experts": experts_per_gpu * world, "top_k": top_k, "eager_layer_us": round(eager, 1), "graph_layer_us": round(graph, 1)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
@@ -180,6 +213,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--skip-nccl", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="time the whole forward layer eagerly and as one CUDA graph replay")
     ap.add_argument("--overlap", action="store_true", help="send rows expert by expert on a side stream while the gated GEMM runs (dispatch_us then only times the launch)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -188,7 +222,10 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Communicator(heap_bytes=heap_bytes_needed(world, a.tokens, a.hidden, a.top_k, a.experts_per_gpu, a.fp8), device=local, timeout_s=20.0)
-    res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap)
+    if a.graph:
+        res = measure_graph(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, max(a.iters, 20))
+    else:
+        res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap)
     if rank == 0:
         print(json.dumps(res), flush=True)
     if world > 1:

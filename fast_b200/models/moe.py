@@ -73,7 +73,7 @@ class MoELayer(nn.Module):
 
     def __init__(self, comm: Communicator, hidden: int, inter: int, num_experts: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
                  router_bias: bool = False, training: bool = True, capacity_rows: Optional[int] = None, init_std: float = 0.02, seed: int = 0,
-                 overlap_dispatch: bool = False):
+                 overlap_dispatch: bool = False, graph_mode: bool = False):
         super().__init__()
         self.comm, self.hidden, self.inter, self.num_experts, self.top_k = comm, hidden, inter, num_experts, top_k
         El = num_experts // comm.world
@@ -85,7 +85,41 @@ class MoELayer(nn.Module):
         self.w2 = nn.Parameter((torch.randn(El, hidden, inter, generator=ge, device=dev) * init_std).to(torch.bfloat16))
         self.router_bias = nn.Parameter(torch.zeros(num_experts, device=dev), requires_grad=False) if router_bias else None
         self.engine = ExpertParallel(comm, num_experts, hidden, inter, top_k, max_tokens, fp8_dispatch=fp8_dispatch, training=training,
-                                     capacity_rows=capacity_rows, overlap_dispatch=overlap_dispatch)
+                                     capacity_rows=capacity_rows, overlap_dispatch=overlap_dispatch, graph_mode=graph_mode)
+
+    @torch.no_grad()
+    def capture(self, tokens: int) -> None:
+        """Capture the forward-only layer for ``tokens`` rows in a CUDA graph (needs ``graph_mode=True``).
+        Collective: every rank captures, and later replays, the same number of times."""
+        assert self.engine.graph_mode, "construct the layer with graph_mode=True"
+        dev = self.gate.device
+        self._gx = torch.zeros(tokens, self.hidden, dtype=torch.bfloat16, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up outside the capture: lazy allocations, tensor maps, status blocks
+                self._gout = self._infer(self._gx)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._gout = self._infer(self._gx)
+
+    @torch.no_grad()
+    def forward_graphed(self, x: torch.Tensor) -> torch.Tensor:
+        """Replay the captured layer on ``x`` (same shape as at capture). The result lives in a buffer
+        owned by the graph and is overwritten by the next replay."""
+        self._gx.copy_(x)
+        self._graph.replay()
+        return self._gout
+
+    def _infer(self, x: torch.Tensor) -> torch.Tensor:
+        logits = (x @ self.gate.t()).float()
+        rs = self.engine.route(logits, self.router_bias)
+        self.last_route = rs
+        self.engine.dispatch(x, rs)
+        self.engine.experts_forward(self.w13, self.w2, rs)
+        return self.engine.combine(rs, rs.topk_w)
 
     def attach_optimizer(self, opt) -> None:
         """Optimizer-in-backward: ``opt`` (a FusedAdamW owning ``w2``) applies W2's update as soon as

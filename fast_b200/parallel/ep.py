@@ -49,7 +49,8 @@ class ExpertParallel:
     """
 
     def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
-                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None, overlap_dispatch: bool = False):
+                 capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None, overlap_dispatch: bool = False,
+                 graph_mode: bool = False):
         C = runtime.ext()
         self._C, self.comm = C, comm
         W = comm.world
@@ -57,6 +58,11 @@ class ExpertParallel:
         assert not training or inter % 256 == 0, "training needs inter % 256 == 0 (dgrad output tiles are 256 wide)"
         self.E, self.El, self.H, self.I, self.K, self.T = num_experts, num_experts // W, hidden, inter, top_k, max_tokens
         self.fp8, self.training = fp8_dispatch, training
+        # graph_mode (forward only): the step's epoch lives in device memory and is advanced by the split-scan
+        # kernel, and the routing outputs are static buffers, so the whole layer can be captured in a CUDA
+        # graph and replayed.
+        assert not (graph_mode and training), "graph_mode covers the forward-only layer"
+        self.graph_mode = graph_mode
         # overlap_dispatch: rows are sent expert by expert on a side stream while the gated expert GEMM of
         # the main stream already consumes the experts that are complete (forward dispatch only).
         self.overlap = overlap_dispatch
@@ -108,6 +114,10 @@ class ExpertParallel:
         self.arrive_target = torch.zeros(2, self.El, dtype=torch.int64, device=dev)
         self.traffic = torch.zeros(W, W, **i32)
         self.epoch = 0
+        self.epoch_dev = torch.zeros(1, dtype=torch.int64, device=dev)
+        if graph_mode:
+            self._static_route = (torch.empty(max_tokens, top_k, **i32), torch.empty(max_tokens, top_k, dtype=torch.float32, device=dev),
+                                  torch.empty(max_tokens, top_k, **i32))
         self.status = comm.status
         self.timeout_ns = comm.timeout_ns
         torch.cuda.synchronize(dev)
@@ -144,17 +154,22 @@ class ExpertParallel:
         C = self._C
         T = logits.shape[0]
         assert T <= self.T and logits.shape[1] == self.E and logits.dtype == torch.float32
-        topk_idx = torch.empty(T, self.K, dtype=torch.int32, device=logits.device)
-        topk_w = torch.empty(T, self.K, dtype=torch.float32, device=logits.device)
-        dest_row = torch.empty(T, self.K, dtype=torch.int32, device=logits.device)
+        if self.graph_mode:
+            topk_idx, topk_w, dest_row = (t[:T] for t in self._static_route)
+        else:
+            topk_idx = torch.empty(T, self.K, dtype=torch.int32, device=logits.device)
+            topk_w = torch.empty(T, self.K, dtype=torch.float32, device=logits.device)
+            dest_row = torch.empty(T, self.K, dtype=torch.int32, device=logits.device)
         nb = (T + C.ROUTE_TOKENS_PER_BLOCK - 1) // C.ROUTE_TOKENS_PER_BLOCK
         C.route_topk(logits.contiguous(), bias, self.K, topk_idx, topk_w, self.slot_in_block, self.block_cnt[:nb])
         self.epoch += 1
+        ed = self.epoch_dev.data_ptr() if self.graph_mode else 0
         C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
                       self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1,
                       gemm.row_align(), self.cap, self.status,
-                      self.timeout_ns, self.send_pos if self.overlap else None)
-        return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows, self.epoch)
+                      self.timeout_ns, self.send_pos if self.overlap else None, ed)
+        return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows,
+                          0 if self.graph_mode else self.epoch)
 
     def dispatch(self, x: torch.Tensor, rs: RouteState) -> None:
         C = self._C
@@ -203,14 +218,14 @@ class ExpertParallel:
         gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate)
         gemm.grouped_gemm_fwd(self.act, w2, rs.group_off, self.y)
         self._join_dispatch()
-        C.peer_signal(self.comm.heap, self._flag_off(1), rs.epoch)
+        C.peer_signal(self.comm.heap, self._flag_off(1), rs.epoch, self.epoch_dev.data_ptr() if self.graph_mode else 0)
 
     def combine(self, rs: RouteState, weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         T = rs.topk_idx.shape[0]
         if out is None:
             out = torch.empty(T, self.H, dtype=torch.bfloat16, device=rs.topk_idx.device)
         self._C.combine_pull(self.comm.heap, self.E, rs.topk_idx, rs.dest_row, weights, self._off(self.y), self._flag_off(1), rs.epoch, out, None, None,
-                             self.H, self.status, self.timeout_ns, self.comm_ctas)
+                             self.H, self.status, self.timeout_ns, self.comm_ctas, self.epoch_dev.data_ptr() if self.graph_mode else 0)
         return out
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -250,7 +265,7 @@ class ExpertParallel:
         grad_w = torch.empty(T, self.K, dtype=torch.float32, device=dev)
         # d(weights): <grad_out[t], y_row(t, j)> - the expert outputs are still in place on the peers.
         C.combine_pull(self.comm.heap, self.E, rs.topk_idx, rs.dest_row, None, self._off(self.y), self._flag_off(1), rs.epoch, None, grad_out, grad_w,
-                       self.H, self.status, self.timeout_ns, self.comm_ctas)
+                       self.H, self.status, self.timeout_ns, self.comm_ctas, 0)
         # Transposed combine: push w * grad_out to the expert rows (channel 1).
         C.zero_pad_rows(self.dy_recv, rs.group_off, rs.group_rows)
         C.dispatch_push(self.comm.heap, grad_out, rs.topk_idx, weights, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, False, False,
@@ -264,9 +279,9 @@ class ExpertParallel:
         C.swiglu_bwd(self.gu, self.dact, self.dgu, rs.group_off.data_ptr() + 4 * self.El)
         gemm.grouped_gemm_dgrad(self.dgu, w13, rs.group_off, self.dx_recv)
         gemm.grouped_gemm_wgrad(self.dgu, self.x_recv, rs.group_off, dw13)
-        C.peer_signal(self.comm.heap, self._flag_off(3), rs.epoch)
+        C.peer_signal(self.comm.heap, self._flag_off(3), rs.epoch, 0)
         grad_x = torch.empty(T, self.H, dtype=torch.bfloat16, device=dev)
         # Transposed dispatch: every token pulls and sums the gradients of its k rows.
         C.combine_pull(self.comm.heap, self.E, rs.topk_idx, rs.dest_row, None, self._off(self.dx_recv), self._flag_off(3), rs.epoch, grad_x, None, None,
-                       self.H, self.status, self.timeout_ns, self.comm_ctas)
+                       self.H, self.status, self.timeout_ns, self.comm_ctas, 0)
         return grad_x, grad_w

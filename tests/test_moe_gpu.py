@@ -145,6 +145,27 @@ def test_moe_forward_single_rank(E, K, H, I, T, fp8, overlap):
     assert int(tm.sum().item()) == T * K
 
 
+def test_forward_layer_in_cuda_graph():
+    """The forward-only layer captured in a CUDA graph replays correctly on new inputs (the step's
+    epoch lives in device memory, so a replay is a new step)."""
+    from fast_b200.models import MoELayer
+    from fast_b200.parallel import Communicator
+
+    E, K, H, I, T = 8, 2, 256, 256, 384
+    comm = Communicator(heap_bytes=256 << 20, device=0)
+    layer = MoELayer(comm, H, I, E, K, max_tokens=512, training=False, graph_mode=True)
+    layer.eval()
+    layer.capture(T)
+    g = torch.Generator(device="cuda").manual_seed(21)
+    for it in range(3):
+        x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+        out = layer.forward_graphed(x).clone()
+        comm.check()
+        ref, _, _ = _ref_forward(x, layer.gate, layer.w13, layer.w2, K, idx=layer.last_route.topk_idx[:T].long())
+        assert _rel(out, ref) < 2e-2, f"replay {it}"
+    assert int(layer.engine.epoch_dev.item()) == 2 + 3  # two warm-up steps + three replays
+
+
 def test_receive_capacity_guard_refuses_step():
     """A step that needs more receive rows than the buffers hold is refused on the device
     (no row is written out of bounds) and reported through the status block."""
