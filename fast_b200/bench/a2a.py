@@ -142,6 +142,14 @@ def run(args):
                                          ("ours_spreadout", PlanKind.SPREAD_OUT, {})] + ([("ours_single_burst", PlanKind.SINGLE_BURST, {})] if args.servers else []):
                     s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk or None, **opts)
                     variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
+                if args.p2p_baseline:
+                    # The reference's executor style: the staged plan run phase by phase over library
+                    # send/recv groups (here NCCL), host-synchronised between phases.
+                    from ..parallel.p2p_executor import P2PExecutor
+
+                    pex = P2PExecutor()
+                    plan_p2p = sched.build_plan(m, topo, kind=PlanKind.STAGED, split_align=16)
+                    variants["staged_plan_over_nccl_sendrecv"] = lambda: pex.run(plan_p2p, 1, inp, nccl_out)
                 for name, fn in variants.items():
                     ms = _time_ms(fn, iters, args.warmup)
                     acc.setdefault(name, []).append((ms, sent, bound_bytes))
@@ -177,6 +185,7 @@ def main():
     ap.add_argument("--threads", type=int, default=512)
     ap.add_argument("--chunk", type=int, default=0, help="work-item bytes (0 = chosen from the matrix)")
     ap.add_argument("--sendrecv", action="store_true")
+    ap.add_argument("--p2p-baseline", action="store_true", help="also run the staged plan over NCCL send/recv groups (the reference's executor style)")
     ap.add_argument("--servers", type=int, default=0, help="treat the ranks as this many virtual servers (hierarchical FAST plan + single-burst ablation)")
     ap.add_argument("--verify", action="store_true")
     run(ap.parse_args())

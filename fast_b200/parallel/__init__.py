@@ -1,1 +1,2 @@
 from .comm import Communicator, LocalGroup, Schedule  # noqa: F401
+from .p2p_executor import P2PExecutor  # noqa: F401

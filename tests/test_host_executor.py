@@ -82,3 +82,13 @@ def test_mismatched_matrices_detected_over_gloo(tmp_path):
                         "--master-port", "29571", str(script)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.count("DETECTED") == 2 and "MISSED" not in r.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_p2p_executor_gloo(world):
+    """Multi-process CPU ranks (gloo) execute flat and two-tier plans, forward and transposed."""
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_p2p_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+                        "--master-port", str(29580 + world), worker], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
+    assert "P2P_OK" in r.stdout
