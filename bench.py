@@ -226,7 +226,9 @@ def main():
             "warmup": warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)",
             "config": {"model": f"Mixtral-8x7B-shaped MoE block (hidden {args.hidden}, FFN {args.ffn} SwiGLU, 8 experts, top-2)", "global_batch": args.seqs * world,
-                       "seq_len": args.seq_len, "parallelism": f"ep{world}", "tokens_per_gpu": tokens, "capacity_rows": cap,
+                       "seq_len": args.seq_len, "parallelism": f"ep{world}", "tokens_per_gpu": tokens,
+                       "baseline_config": "BASELINE.json configs[4] (Mixtral-8x7B-shaped MoE block training step, tokens/s at 1/2/4/8 B200); the headline "
+                                          "collective metrics of configs[2] and configs[3] are the sub-metrics alltoallv_skewed and moe_forward_fp8_dispatch", "capacity_rows": cap,
                        "l2": "per-step working set (weights 2.8 GB/GPU at N=1, activations > 10 GB) far exceeds the 126 MB L2; no flush needed",
                        "optimizer": "AdamW, fp32 master weights, in the timed step", "timing": "CUDA events around K steps, max over ranks"},
             "clocks": clocks,
