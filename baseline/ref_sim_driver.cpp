@@ -38,8 +38,20 @@ int main() {
   for (auto& p : a2a.p_sets) freq_sum += p.get_freq();
   const bool exact = a2a.verify_decomposition();
   struct pipeline_result_t r = gs.pipeline2(mbpu);
+  // pipeline3 = pipeline2 with a pluggable intra-server fabric cost; it consumes the schedulers'
+  // state, so each call gets a fresh set.
+  auto with_fabric = [&](intra_transfer_topo_fn fn) {
+    std::vector<LocalScheduler*> ls;
+    for (unsigned s = 0; s < S; ++s) ls.push_back(new LocalScheduler(m.data() + static_cast<size_t>(s) * G * n, G, S, s, intra));
+    GlobalScheduler g3(S, G, ls, inter, intra, false, mbpu);
+    return g3.pipeline3(mbpu, fn).t;
+  };
+  const double full_mesh = with_fabric(&intra_transfer_full_mesh);
+  const double ring2 = G == 8 ? with_fabric(&intra_transfer_2ring) : -1.0;
+  const double cube = G == 8 ? with_fabric(&intra_transfer_hybrid_cude_mesh) : -1.0;
   const double spread = spread_out_baseline(m.data(), S, G, inter, intra, mbpu);
-  printf("{\"stages\":%zu,\"freq_sum\":%llu,\"exact\":%s,\"decompose_us\":%.2f,\"pipeline2_us\":%.4f,\"spread_out_us\":%.4f}\n", a2a.p_sets.size(), freq_sum,
-         exact ? "true" : "false", std::chrono::duration<double, std::micro>(t1 - t0).count(), r.t, spread);
+  printf("{\"stages\":%zu,\"freq_sum\":%llu,\"exact\":%s,\"decompose_us\":%.2f,\"pipeline2_us\":%.4f,\"spread_out_us\":%.4f,"
+         "\"pipeline3_full_mesh_us\":%.4f,\"pipeline3_2ring_us\":%.4f,\"pipeline3_hybrid_cube_mesh_us\":%.4f}\n", a2a.p_sets.size(), freq_sum,
+         exact ? "true" : "false", std::chrono::duration<double, std::micro>(t1 - t0).count(), r.t, spread, full_mesh, ring2, cube);
   return 0;
 }

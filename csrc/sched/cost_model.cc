@@ -23,7 +23,82 @@ double spread_out_time(const std::vector<int64_t>& m, int dim, LinkModel l, doub
   }
   return t;
 }
+double full_mesh_time(const std::vector<int64_t>& m, int dim, LinkModel l, double mbpu) {
+  int64_t mx = 0;
+  for (int i = 0; i < dim; ++i)
+    for (int j = 0; j < dim; ++j)
+      if (i != j) mx = std::max(mx, m[static_cast<size_t>(i) * dim + j]);
+  return mx ? l.alpha_us + static_cast<double>(mx) * l.beta_us_per_mb * mbpu : 0.0;
+}
+
+// Offsets 1 .. (dim-1)/2 travel forward, the rest backward; an offset of h hops pays h times its
+// slowest transfer; the two directions use different links and overlap.
+double ring_time(const std::vector<int64_t>& m, int dim, LinkModel l, double mbpu) {
+  double fwd = 0, rev = 0;
+  for (int d = 1; d < dim; ++d) {
+    int64_t mx = 0;
+    for (int j = 0; j < dim; ++j) mx = std::max(mx, m[static_cast<size_t>(j) * dim + (j + d) % dim]);
+    if (!mx) continue;
+    const bool forward = d <= (dim - 1) / 2;
+    const int hops = forward ? d : dim - d;
+    (forward ? fwd : rev) += (l.alpha_us + static_cast<double>(mx) * l.beta_us_per_mb * mbpu) * hops;
+  }
+  return std::max(fwd, rev);
+}
+
+// Phase 1: all directly linked pairs at once (a pair with k links moves k times faster).
+// Phase 2: every unlinked pair relays through the neighbour with the widest path; the relays that
+// feed one destination share its links, so their second hops add up.
+double link_graph_time(const std::vector<int64_t>& m, int dim, const std::vector<int>& links, LinkModel l, double mbpu) {
+  if (static_cast<int>(links.size()) != dim * dim) return spread_out_time(m, dim, l, mbpu);
+  auto mult = [&](int i, int j) { return links[static_cast<size_t>(i) * dim + j]; };
+  double direct = 0, relay = 0;
+  for (int i = 0; i < dim; ++i)
+    for (int j = 0; j < dim; ++j) {
+      const int64_t x = m[static_cast<size_t>(i) * dim + j];
+      if (i == j || !x || !mult(i, j)) continue;
+      direct = std::max(direct, l.alpha_us + static_cast<double>(x) * l.beta_us_per_mb * mbpu / mult(i, j));
+    }
+  for (int j = 0; j < dim; ++j) {
+    double first = 0, second = 0;
+    bool any = false;
+    for (int i = 0; i < dim; ++i) {
+      const int64_t x = m[static_cast<size_t>(i) * dim + j];
+      if (i == j || !x || mult(i, j)) continue;
+      int best = -1, width = 0;
+      for (int r = 0; r < dim; ++r) {
+        const int w = std::min(mult(i, r), mult(r, j));
+        if (w > width) { width = w; best = r; }
+      }
+      if (best < 0) return spread_out_time(m, dim, l, mbpu);  // disconnected description: fall back
+      any = true;
+      first = std::max(first, static_cast<double>(x) * l.beta_us_per_mb * mbpu / mult(i, best));
+      second += static_cast<double>(x) * l.beta_us_per_mb * mbpu / mult(best, j);
+    }
+    if (any) relay = std::max(relay, 2 * l.alpha_us + first + second);
+  }
+  return direct + relay;
+}
+
+double intra_time(const std::vector<int64_t>& m, int dim, const CostModel& cm) {
+  switch (cm.intra_topology) {
+    case IntraTopology::kFullMesh: return full_mesh_time(m, dim, cm.intra, cm.mb_per_unit);
+    case IntraTopology::kRing: return ring_time(m, dim, cm.intra, cm.mb_per_unit);
+    case IntraTopology::kLinkGraph: return link_graph_time(m, dim, cm.links, cm.intra, cm.mb_per_unit);
+    default: return spread_out_time(m, dim, cm.intra, cm.mb_per_unit);
+  }
+}
 }  // namespace
+
+std::vector<int> hybrid_cube_mesh_links() {
+  std::vector<int> l(64, 0);
+  auto set = [&](int a, int b, int k) { l[a * 8 + b] = k; l[b * 8 + a] = k; };
+  const int dbl[][2] = {{0, 1}, {0, 2}, {2, 3}, {1, 4}, {3, 6}, {4, 5}, {5, 7}, {6, 7}};
+  const int sgl[][2] = {{0, 3}, {1, 2}, {1, 3}, {0, 5}, {2, 7}, {4, 6}, {4, 7}, {5, 6}};
+  for (auto& p : dbl) set(p[0], p[1], 2);
+  for (auto& p : sgl) set(p[0], p[1], 1);
+  return l;
+}
 
 PlanCost model_cost(const Plan& p, const CostModel& cm) {
   const int n = p.matrix.n, S = p.topo.servers, G = p.topo.gpus;
@@ -116,12 +191,12 @@ PlanCost model_cost(const Plan& p, const CostModel& cm) {
     double t = 0;
     for (int d = 0; d < S; ++d) {
       const auto& m = bal[static_cast<size_t>(s) * S + d];
-      if (!m.empty()) t += spread_out_time(m, G, cm.intra, mb);
+      if (!m.empty()) t += intra_time(m, G, cm);
     }
     c.balance_us = std::max(c.balance_us, t);
   }
   double intrinsic_us = 0;
-  for (int s = 0; s < S; ++s) intrinsic_us = std::max(intrinsic_us, spread_out_time(intrinsic[s], G, cm.intra, mb));
+  for (int s = 0; s < S; ++s) intrinsic_us = std::max(intrinsic_us, intra_time(intrinsic[s], G, cm));
 
   c.stage_inter_us.assign(K, 0);
   c.stage_redistribute_us.assign(K, 0);
@@ -129,7 +204,7 @@ PlanCost model_cost(const Plan& p, const CostModel& cm) {
     if (stage_max[k]) c.stage_inter_us[k] = cm.inter.alpha_us + static_cast<double>(stage_max[k]) * cm.inter.beta_us_per_mb * mb;
     for (int s = 0; s < S; ++s) {
       const auto& m = redis[static_cast<size_t>(k) * S + s];
-      if (!m.empty()) c.stage_redistribute_us[k] = std::max(c.stage_redistribute_us[k], spread_out_time(m, G, cm.intra, mb));
+      if (!m.empty()) c.stage_redistribute_us[k] = std::max(c.stage_redistribute_us[k], intra_time(m, G, cm));
     }
     c.inter_us += c.stage_inter_us[k];
   }

@@ -109,11 +109,24 @@ int64_t execute_on_host(const Plan& p, int unit_bytes, const std::vector<const u
                         const std::vector<uint8_t*>& outputs, int64_t drop_op = -1);
 
 // ---- cost model -----------------------------------------------------------------------------
+// How the GPUs of one server reach each other (simulation/scheduler/config.cpp:61-179 has one
+// hand-written cost function per fabric; here one routine is driven by this description).
+enum class IntraTopology : int {
+  kSwitch = 0,     // one port per GPU into a switch: ring-offset rounds, a round costs its slowest pair
+  kFullMesh = 1,   // a dedicated link per pair: everything in flight at once
+  kRing = 2,       // bidirectional ring: a transfer takes the shorter way, paying every hop
+  kLinkGraph = 3,  // arbitrary point-to-point links (multiplicity matrix); unlinked pairs relay over one hop
+};
 struct CostModel {
   LinkModel inter{0.7, 22.0};  // defaults: 400 GbE class NIC (the reference simulator's ETHER400)
   LinkModel intra{0.1, 1.2};   // defaults: the reference simulator's B100 entry
   double mb_per_unit = 1.0;
+  IntraTopology intra_topology = IntraTopology::kSwitch;
+  std::vector<int> links;      // kLinkGraph: gpus x gpus link multiplicities (0 = no direct link)
 };
+// Link multiplicities of the 8-GPU hybrid cube mesh (6 links per GPU, the fabric the reference's
+// intra_transfer_hybrid_cude_mesh hard-codes).
+std::vector<int> hybrid_cube_mesh_links();
 struct PlanCost {
   double total_us = 0, balance_us = 0, inter_us = 0, exposed_intra_us = 0;
   double lower_bound_us = 0;   // busiest port (or busiest server NIC set) at full rate

@@ -75,6 +75,7 @@ PYBIND11_MODULE(_sched, m) {
       .def_readwrite("alpha_us", &LinkModel::alpha_us).def_readwrite("beta_us_per_mb", &LinkModel::beta_us_per_mb);
   m.def("nvlink_model", &nvlink_model, py::arg("gbytes_per_s") = 900.0, py::arg("alpha_us") = 2.0);
   m.def("gbps_model", &gbps_model);
+  m.def("hybrid_cube_mesh_links", &hybrid_cube_mesh_links);
 
   m.def("decompose", [](const I64Array& a, MatchPolicy pol, int64_t scale) {
     Decomposition d = decompose(to_matrix(a), pol, scale);
@@ -132,13 +133,20 @@ PYBIND11_MODULE(_sched, m) {
       .def("to_json", &plan_to_json, py::arg("include_ops") = true)
       .def("to_bytes", [](const Plan& p) { auto b = plan_to_bytes(p); return py::bytes(reinterpret_cast<const char*>(b.data()), b.size()); })
       .def_static("from_bytes", [](const py::bytes& s) { std::string t = s; return plan_from_bytes(std::vector<uint8_t>(t.begin(), t.end())); })
-      .def("cost", [](const Plan& p, LinkModel inter, LinkModel intra, double mbpu) {
-        PlanCost c = model_cost(p, CostModel{inter, intra, mbpu});
+      .def("cost", [](const Plan& p, LinkModel inter, LinkModel intra, double mbpu, const std::string& topo, std::vector<int> links) {
+        CostModel cm{inter, intra, mbpu};
+        if (topo == "full_mesh") cm.intra_topology = IntraTopology::kFullMesh;
+        else if (topo == "ring") cm.intra_topology = IntraTopology::kRing;
+        else if (topo == "hybrid_cube_mesh") { cm.intra_topology = IntraTopology::kLinkGraph; cm.links = hybrid_cube_mesh_links(); }
+        else if (topo == "links") { cm.intra_topology = IntraTopology::kLinkGraph; cm.links = std::move(links); }
+        else if (topo != "switch") throw std::invalid_argument("intra_topology: switch | full_mesh | ring | hybrid_cube_mesh | links");
+        PlanCost c = model_cost(p, cm);
         py::dict d;
         d["total_us"] = c.total_us; d["balance_us"] = c.balance_us; d["inter_us"] = c.inter_us; d["exposed_intra_us"] = c.exposed_intra_us;
         d["lower_bound_us"] = c.lower_bound_us; d["spread_out_us"] = c.spread_out_us;
         d["stage_inter_us"] = c.stage_inter_us; d["stage_redistribute_us"] = c.stage_redistribute_us;
-        return d; }, py::arg("inter"), py::arg("intra"), py::arg("mb_per_unit") = 1.0)
+        return d; }, py::arg("inter"), py::arg("intra"), py::arg("mb_per_unit") = 1.0, py::arg("intra_topology") = "switch",
+           py::arg("links") = std::vector<int>())
       .def("lower", [](const Plan& p, int rank, int unit_bytes, int64_t chunk_bytes) {
         LowerOptions lo; lo.unit_bytes = unit_bytes; lo.chunk_bytes = chunk_bytes;
         return program_dict(lower_for_rank(p, rank, lo)); }, py::arg("rank"), py::arg("unit_bytes") = 1, py::arg("chunk_bytes") = 1 << 20)

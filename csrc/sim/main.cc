@@ -63,6 +63,10 @@ CostModel cost_of(const Args& a, int servers) {
     cm.intra = nvlink_model(a.num("nvlink-gbs", 900.0), a.num("intra-alpha-us", 0.1));
   }
   cm.mb_per_unit = a.num("mb-per-unit", 1e-6);  // default unit = 1 byte
+  const std::string topo = a.str("intra-topology", "switch");
+  if (topo == "full_mesh") cm.intra_topology = IntraTopology::kFullMesh;
+  else if (topo == "ring") cm.intra_topology = IntraTopology::kRing;
+  else if (topo == "hybrid_cube_mesh") { cm.intra_topology = IntraTopology::kLinkGraph; cm.links = hybrid_cube_mesh_links(); }
   return cm;
 }
 

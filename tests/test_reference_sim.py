@@ -59,3 +59,16 @@ def test_hierarchical_model_tracks_reference(ref_sim, S, G):
         assert abs(c["spread_out_us"] - ref["spread_out_us"]) / ref["spread_out_us"] < 1e-6
         ratios.append(c["total_us"] / ref["pipeline2_us"])
     assert 0.85 < float(np.mean(ratios)) < 1.1, ratios
+
+
+def test_intra_fabric_models_match_reference_pipeline3(ref_sim):
+    """Full mesh and bidirectional ring reproduce the reference's pipeline3 numbers; the link-graph
+    model of the hybrid cube mesh stays within a few percent of its hand-written formula."""
+    inter, intra = sched.gbps_model(400, 0.7), sched.LinkModel(0.1, 2.3)
+    for seed in range(3):
+        m = sched.workload_uniform(16, 10000, seed)
+        ref = _run_ref(ref_sim, m, 2, 8, inter, intra, 1.0)
+        p = sched.build_plan(m, Topology(2, 8))
+        assert abs(p.cost(inter, intra, 1.0, "full_mesh")["total_us"] - ref["pipeline3_full_mesh_us"]) / ref["pipeline3_full_mesh_us"] < 1e-6
+        assert abs(p.cost(inter, intra, 1.0, "ring")["total_us"] - ref["pipeline3_2ring_us"]) / ref["pipeline3_2ring_us"] < 1e-6
+        assert abs(p.cost(inter, intra, 1.0, "hybrid_cube_mesh")["total_us"] - ref["pipeline3_hybrid_cube_mesh_us"]) / ref["pipeline3_hybrid_cube_mesh_us"] < 0.05

@@ -224,6 +224,19 @@ def test_cost_model_against_reference_figures():
     assert f["total_us"] > c["total_us"]
 
 
+def test_intra_fabric_models_are_ordered():
+    m = sched.workload_uniform(16, 10000, 3)
+    p = sched.build_plan(m, Topology(2, 8))
+    inter, intra = sched.gbps_model(400, 0.7), sched.LinkModel(0.1, 2.3)
+    t = {k: p.cost(inter, intra, 1.0, k)["total_us"] for k in ("switch", "full_mesh", "ring", "hybrid_cube_mesh")}
+    assert t["full_mesh"] < t["hybrid_cube_mesh"] < t["ring"] and t["full_mesh"] < t["switch"]
+    links = sched._S.hybrid_cube_mesh_links()
+    assert len(links) == 64 and all(sum(links[i * 8:(i + 1) * 8]) == 6 for i in range(8))  # six links per GPU
+    assert p.cost(inter, intra, 1.0, "links", links)["total_us"] == t["hybrid_cube_mesh"]
+    with pytest.raises(Exception):
+        p.cost(inter, intra, 1.0, "torus")
+
+
 def test_coarsening_reduces_stages_for_small_messages():
     m = sched.workload_uniform(32, 10000, 3)
     a = sched.build_plan(m, Topology(16, 2))
