@@ -97,7 +97,18 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
         sum += load[i];
       }
       const int64_t target = (sum + G - 1) / G;
-      for (int big = 0; big < G && G > 1; ++big) {
+      bool balance = G > 1;
+      if (balance && opt.balance_alpha_beta) {
+        double alpha = opt.intra.alpha_us;
+        double beta = static_cast<double>(*std::max_element(load.begin(), load.end())) * opt.intra.beta_us_per_mb * opt.mb_per_unit;
+        for (int d = 0; d < G; ++d) {
+          int64_t mx = 0;
+          for (int j = 0; j < G; ++j) mx = std::max(mx, M.at(s * G + j, t * G + (j + d) % G));
+          if (mx) { alpha += opt.intra.alpha_us; beta += static_cast<double>(mx) * opt.intra.beta_us_per_mb * opt.mb_per_unit; }
+        }
+        balance = !(beta / alpha < 2.0);
+      }
+      for (int big = 0; big < G && balance; ++big) {
         for (int small = 0; small < G && load[big] > target; ++small) {
           if (small == big || load[small] >= target) continue;
           auto& src = hold_at(s, t, big);

@@ -66,6 +66,10 @@ struct PlanOptions {
   int64_t scale = 0;        // explicit coarsening divisor; 0 = derive from scale_policy
   int64_t split_align = 1;  // units; pieces are only cut at multiples of this inside a segment
   bool transpose = false;   // plan the reverse collective (combine / backward all-to-all)
+  // Skip the balancing of a (server, server) tile whose transfer is latency-dominated: when the
+  // beta cost of balancing + redistributing it is less than twice its alpha cost (the reference
+  // simulator's check_balance_dispatch, simulation/scheduler/local.cpp:187-216). Uses `intra`.
+  bool balance_alpha_beta = false;
   LinkModel inter{0.7, 22.0};  // used by ScalePolicy::kAlphaBeta only
   LinkModel intra{0.1, 1.2};
   double mb_per_unit = 1.0;

@@ -163,13 +163,14 @@ PYBIND11_MODULE(_sched, m) {
         return execute_on_host(p, unit_bytes, ip, op, drop_op); }, py::arg("unit_bytes"), py::arg("inputs"), py::arg("outputs"), py::arg("drop_op") = -1);
 
   m.def("build_plan", [](const I64Array& a, int servers, int gpus, PlanKind kind, MatchPolicy match, ScalePolicy sp, int64_t scale,
-                         int64_t split_align, bool transpose, LinkModel inter, LinkModel intra, double mbpu) {
+                         int64_t split_align, bool transpose, LinkModel inter, LinkModel intra, double mbpu, bool balance_alpha_beta) {
     PlanOptions o; o.kind = kind; o.match = match; o.scale_policy = sp; o.scale = scale; o.split_align = split_align; o.transpose = transpose;
-    o.inter = inter; o.intra = intra; o.mb_per_unit = mbpu;
+    o.inter = inter; o.intra = intra; o.mb_per_unit = mbpu; o.balance_alpha_beta = balance_alpha_beta;
     return build_plan(to_matrix(a), Topology{servers, gpus}, o);
   }, py::arg("matrix"), py::arg("servers"), py::arg("gpus"), py::arg("kind") = PlanKind::kStaged, py::arg("match") = MatchPolicy::kFirstFit,
      py::arg("scale_policy") = ScalePolicy::kNone, py::arg("scale") = 0, py::arg("split_align") = 1, py::arg("transpose") = false,
-     py::arg("inter") = LinkModel{0.7, 22.0}, py::arg("intra") = LinkModel{0.1, 1.2}, py::arg("mb_per_unit") = 1.0);
+     py::arg("inter") = LinkModel{0.7, 22.0}, py::arg("intra") = LinkModel{0.1, 1.2}, py::arg("mb_per_unit") = 1.0,
+     py::arg("balance_alpha_beta") = false);
   m.def("build_plan_time_us", [](const I64Array& a, int servers, int gpus, int reps) {
     Matrix mm = to_matrix(a);
     auto t0 = std::chrono::steady_clock::now();

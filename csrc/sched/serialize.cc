@@ -85,7 +85,7 @@ std::vector<uint8_t> plan_to_bytes(const Plan& p) {
   w.pod<int32_t>(p.topo.servers); w.pod<int32_t>(p.topo.gpus);
   w.pod<int32_t>(static_cast<int>(p.opt.kind)); w.pod<int32_t>(static_cast<int>(p.opt.match));
   w.pod<int32_t>(static_cast<int>(p.opt.scale_policy)); w.pod<int64_t>(p.opt.scale); w.pod<int64_t>(p.opt.split_align);
-  w.pod<int32_t>(p.opt.transpose ? 1 : 0);
+  w.pod<int32_t>((p.opt.transpose ? 1 : 0) | (p.opt.balance_alpha_beta ? 2 : 0));
   w.mat(p.matrix); w.mat(p.server_matrix);
   w.mat(p.decomp.padded); w.mat(p.decomp.padding); w.pod(p.decomp.line_sum); w.pod(p.decomp.scale);
   w.pod<uint64_t>(p.decomp.stages.size());
@@ -111,7 +111,7 @@ Plan plan_from_bytes(const std::vector<uint8_t>& blob) {
   p.topo.servers = r.pod<int32_t>(); p.topo.gpus = r.pod<int32_t>();
   p.opt.kind = static_cast<PlanKind>(r.pod<int32_t>()); p.opt.match = static_cast<MatchPolicy>(r.pod<int32_t>());
   p.opt.scale_policy = static_cast<ScalePolicy>(r.pod<int32_t>()); p.opt.scale = r.pod<int64_t>(); p.opt.split_align = r.pod<int64_t>();
-  p.opt.transpose = r.pod<int32_t>() != 0;
+  { const int32_t flags = r.pod<int32_t>(); p.opt.transpose = (flags & 1) != 0; p.opt.balance_alpha_beta = (flags & 2) != 0; }
   p.matrix = r.mat(); p.server_matrix = r.mat();
   p.decomp.padded = r.mat(); p.decomp.padding = r.mat(); p.decomp.line_sum = r.pod<int64_t>(); p.decomp.scale = r.pod<int64_t>();
   uint64_t ns = r.pod<uint64_t>();

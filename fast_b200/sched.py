@@ -43,6 +43,24 @@ workload_balanced = _S.workload_balanced
 workload_zipf_rows = _S.workload_zipf_rows
 workload_zipf_entries = _S.workload_zipf_entries
 
+# Link presets: (alpha in us, beta in us per MB). The intra-server and inter-server classes and their
+# figures are those of the reference simulator's tables (simulation/scheduler/config.cpp:8-59), plus
+# the measured NVLink-5 port of a B200 (770 GB/s peer copy, ~2 us per hop).
+INTRA_LINKS = {"DGX2": (0.1, 8.0), "FAST": (0.1, 1.0), "B100": (0.1, 1.2), "H100": (0.1, 2.3), "NDV2": (0.1, 46.0), "MI300X": (0.1, 5.0),
+               "B200_NVLINK5": (2.0, 1e3 / 770.0)}
+INTER_LINKS = {"INFB": (1.7, 106.0), "ETHER100": (0.7, 84.0), "ETHER400": (0.7, 22.0)}
+
+
+def intra_link(name: str) -> "LinkModel":
+    a, b = INTRA_LINKS[name]
+    return LinkModel(a, b)
+
+
+def inter_link(name: str) -> "LinkModel":
+    a, b = INTER_LINKS[name]
+    return LinkModel(a, b)
+
+
 BUF_INPUT, BUF_OUTPUT, BUF_BALANCE, BUF_RAIL = 0, 1, 2, 3
 PHASE_BALANCE, PHASE_INTRINSIC, PHASE_RAIL, PHASE_REDISTRIBUTE = 0, 1, 2, 3
 
@@ -66,7 +84,8 @@ class Topology:
 
 def build_plan(matrix, topo: Topology, kind=PlanKind.STAGED, match=MatchPolicy.FIRST_FIT,
                scale_policy=ScalePolicy.NONE, scale: int = 0, split_align: int = 1, transpose: bool = False,
-               inter: Optional[LinkModel] = None, intra: Optional[LinkModel] = None, mb_per_unit: float = 1.0) -> Plan:
+               inter: Optional[LinkModel] = None, intra: Optional[LinkModel] = None, mb_per_unit: float = 1.0,
+               balance_alpha_beta: bool = False) -> Plan:
     """Plan one all-to-all(v). ``matrix[i, j]`` = units rank i sends to rank j.
 
     ``transpose=True`` plans the reverse collective (MoE combine / backward of dispatch), which
@@ -74,7 +93,7 @@ def build_plan(matrix, topo: Topology, kind=PlanKind.STAGED, match=MatchPolicy.F
     """
     m = np.ascontiguousarray(matrix, dtype=np.int64)
     return _S.build_plan(m, topo.servers, topo.gpus, kind, match, scale_policy, scale, split_align, transpose,
-                         inter or gbps_model(400.0, 0.7), intra or nvlink_model(900.0, 0.1), mb_per_unit)
+                         inter or gbps_model(400.0, 0.7), intra or nvlink_model(900.0, 0.1), mb_per_unit, balance_alpha_beta)
 
 
 class PlanCache:

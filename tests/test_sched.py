@@ -224,6 +224,21 @@ def test_cost_model_against_reference_figures():
     assert f["total_us"] > c["total_us"]
 
 
+def test_alpha_beta_balance_policy_skips_latency_bound_tiles():
+    m = sched.workload_uniform(16, 10000, 3)
+    inter, intra = sched.inter_link("ETHER400"), sched.intra_link("H100")
+    big = sched.build_plan(m, Topology(2, 8), inter=inter, intra=intra, mb_per_unit=1.0, balance_alpha_beta=True)
+    tiny = sched.build_plan(m, Topology(2, 8), inter=inter, intra=intra, mb_per_unit=1e-9, balance_alpha_beta=True)
+    assert (big.ops[:, 0] == sched.PHASE_BALANCE).any()          # bandwidth-bound: balancing pays
+    assert not (tiny.ops[:, 0] == sched.PHASE_BALANCE).any()     # latency-bound: tiles go out as they are
+    for p in (big, tiny):
+        assert p.validate() == "" and (p.delivered_matrix() == m).all()
+    assert tiny.server_matrix[0, 1] == m[:8, 8:].sum(1).max()    # the rail load is then the heaviest GPU's
+    q = sched.Plan.from_bytes(tiny.to_bytes())
+    assert q.validate() == "" and q.num_ops == tiny.num_ops
+    assert set(sched.INTRA_LINKS) >= {"DGX2", "MI300X", "NDV2", "FAST", "H100", "B100"} and set(sched.INTER_LINKS) == {"INFB", "ETHER100", "ETHER400"}
+
+
 def test_intra_fabric_models_are_ordered():
     m = sched.workload_uniform(16, 10000, 3)
     p = sched.build_plan(m, Topology(2, 8))
