@@ -7,6 +7,7 @@
 //   skew      modeled speed-up vs Zipf skew
 //   size      modeled speed-up vs transfer size with and without coarsening
 //   fabric    modeled speed-up and exposed intra-server share vs intra-server link speed
+//   topology  modeled speed-up under each intra-server fabric model
 //   overhead  scheduler time and staging memory relative to the payload, per cluster size
 // Covers the reference simulator's drivers (simulation/test.cpp:15-60 DecompositionTester,
 // :73-116 run, :119-264 grid, :346-498 fabric, :501-592 skew, :595-684 size).
@@ -165,6 +166,29 @@ int cmd_size(const Args& a) {
   }
   return 0;
 }
+// Modeled speed-up over spread-out for each intra-server fabric model (the reference's
+// topology_benchmark, simulation/test.cpp:266-343), 8 GPUs per server.
+int cmd_topology(const Args& a) {
+  const int G = 8;
+  const char* names[] = {"switch", "full_mesh", "ring", "hybrid_cube_mesh"};
+  for (int S : {2, 4, 8, 16}) {
+    Matrix m = workload_uniform(S * G, 10000, 21 + S, false);
+    Plan p = build_plan(m, Topology{S, G}, PlanOptions{});
+    for (int t = 0; t < 4; ++t) {
+      CostModel cm;
+      cm.inter = gbps_model(a.num("inter-gbps", 100.0), 0.7);
+      cm.intra = gbps_model(a.num("intra-gbps", 400.0), 0.1);
+      cm.mb_per_unit = a.num("mb-per-unit", 1.0);
+      cm.intra_topology = static_cast<IntraTopology>(t);
+      if (t == 3) cm.links = hybrid_cube_mesh_links();
+      PlanCost c = model_cost(p, cm);
+      std::printf("{\"cmd\":\"topology\",\"servers\":%d,\"fabric\":\"%s\",\"modeled_us\":%.1f,\"speedup\":%.3f,\"exposed_intra_share\":%.4f}\n", S, names[t], c.total_us,
+                  c.total_us > 0 ? c.spread_out_us / c.total_us : 0.0, c.total_us > 0 ? c.exposed_intra_us / c.total_us : 0.0);
+    }
+  }
+  return 0;
+}
+
 // Scheduler cost and staging memory against the plain send/receive buffers, per cluster size
 // (the reference's overhead test, amd/test_alltoall.cpp:2750-2823).
 int cmd_overhead(const Args& a) {
@@ -199,7 +223,7 @@ int cmd_fabric(const Args& a) {
 
 int main(int argc, char** argv) {
   if (argc < 2) {
-    std::fprintf(stderr, "usage: fastb-sim {plan|verify|grid|skew|size|fabric|overhead} [--key value ...]\n");
+    std::fprintf(stderr, "usage: fastb-sim {plan|verify|grid|skew|size|fabric|topology|overhead} [--key value ...]\n");
     return 2;
   }
   Args a = parse(argc, argv);
@@ -212,6 +236,7 @@ int main(int argc, char** argv) {
     if (c == "size") return cmd_size(a);
     if (c == "fabric") return cmd_fabric(a);
     if (c == "overhead") return cmd_overhead(a);
+    if (c == "topology") return cmd_topology(a);
   } catch (const std::exception& e) {
     std::fprintf(stderr, "fastb-sim: %s\n", e.what());
     return 1;

@@ -287,3 +287,20 @@ def test_native_selfcheck():
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout[-2000:]
     assert json.loads(r.stdout.strip().splitlines()[-1])["failures"] == 0
+
+
+def test_simulator_sweeps_and_plot_parser(tmp_path):
+    from fast_b200 import _build
+    from fast_b200.bench import plot_sim
+
+    exe = _build.build_sim()
+    out = ""
+    for cmd in (["topology"], ["skew", "--servers", "4", "--gpus", "4"], ["overhead", "--max-servers", "3", "--reps", "2"]):
+        out += subprocess.run([str(exe), *cmd], capture_output=True, text=True, check=True).stdout
+    f = tmp_path / "sim.jsonl"
+    f.write_text(out)
+    rows = plot_sim.load(f)
+    assert len(rows["topology"]) == 16 and len(rows["skew"]) == 7 and len(rows["overhead"]) == 2
+    xlabel, ser = plot_sim.series(rows, "topology")
+    assert set(ser) == {"switch", "full_mesh", "ring", "hybrid_cube_mesh"}
+    assert all(j["staging_over_payload"] < 1.0 for j in rows["overhead"])
