@@ -20,7 +20,7 @@ SymmHeap::SymmHeap(int rank, int world, size_t bytes) : rank_(rank), world_(worl
   check(cudaMalloc(&p, bytes), "cudaMalloc slab");
   check(cudaMemset(p, 0, bytes), "cudaMemset slab");
   peer_base_[rank] = p;
-  free_[0] = bytes;
+  ranges_ = RangeAllocator(bytes);
   if (world == 1) { opened_ = true; upload_table(); }
 }
 
@@ -35,7 +35,7 @@ std::vector<SymmHeap*> SymmHeap::create_local_group(int world, size_t bytes) {
     SymmHeap* h = new SymmHeap();
     h->rank_ = r; h->world_ = world; h->bytes_ = bytes;
     h->peer_base_ = slabs;
-    h->free_[0] = bytes;
+    h->ranges_ = RangeAllocator(bytes);
     h->opened_ = true;
     h->upload_table();
     hs.push_back(h);
@@ -79,36 +79,6 @@ void SymmHeap::open_peers(const std::vector<std::string>& handles) {
 void SymmHeap::upload_table() {
   if (!d_table_) check(cudaMalloc(reinterpret_cast<void**>(&d_table_), sizeof(void*) * world_), "cudaMalloc table");
   check(cudaMemcpy(d_table_, peer_base_.data(), sizeof(void*) * world_, cudaMemcpyHostToDevice), "upload table");
-}
-
-size_t SymmHeap::alloc(size_t bytes) {
-  const size_t need = (bytes + 255) / 256 * 256 + (bytes == 0 ? 256 : 0);
-  for (auto it = free_.begin(); it != free_.end(); ++it) {
-    if (it->second < need) continue;
-    const size_t off = it->first, left = it->second - need;
-    free_.erase(it);
-    if (left) free_[off + need] = left;
-    taken_[off] = need;
-    in_use_ += need;
-    return off;
-  }
-  throw std::runtime_error("SymmHeap: out of symmetric memory (asked " + std::to_string(bytes) + " B, in use " +
-                           std::to_string(in_use_) + " of " + std::to_string(bytes_) + ")");
-}
-
-void SymmHeap::free(size_t offset) {
-  auto it = taken_.find(offset);
-  if (it == taken_.end()) throw std::invalid_argument("SymmHeap: free of an unknown offset");
-  size_t off = it->first, sz = it->second;
-  taken_.erase(it);
-  in_use_ -= sz;
-  auto next = free_.lower_bound(off);
-  if (next != free_.end() && off + sz == next->first) { sz += next->second; next = free_.erase(next); }
-  if (next != free_.begin()) {
-    auto prev = std::prev(next);
-    if (prev->first + prev->second == off) { prev->second += sz; return; }
-  }
-  free_[off] = sz;
 }
 
 }  // namespace fastb

@@ -8,9 +8,10 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
-#include <map>
 #include <string>
 #include <vector>
+
+#include "range_allocator.h"
 
 namespace fastb {
 
@@ -35,22 +36,21 @@ class SymmHeap {
   void* peer_base(int r) const { return peer_base_[r]; }
   void* const* device_peer_table() const { return d_table_; }  // device array [world] of slab bases
 
-  // Offsets are multiples of 256 B. Throws std::bad_alloc-like runtime_error when full.
-  size_t alloc(size_t bytes);
-  void free(size_t offset);
-  size_t in_use() const { return in_use_; }
+  // Offsets are multiples of 256 B. Throws std::runtime_error when full.
+  size_t alloc(size_t bytes) { return ranges_.alloc(bytes); }
+  void free(size_t offset) { ranges_.free(offset); }
+  size_t in_use() const { return ranges_.in_use(); }
 
  private:
   SymmHeap() = default;
   void upload_table();
   int rank_ = 0, world_ = 1;
-  size_t bytes_ = 0, in_use_ = 0;
+  size_t bytes_ = 0;
   bool opened_ = false;
   std::vector<char> ipc_opened_;  // peers mapped through an IPC handle (closed in the destructor)
   std::vector<void*> peer_base_;
   void** d_table_ = nullptr;
-  std::map<size_t, size_t> free_;   // offset -> size
-  std::map<size_t, size_t> taken_;  // offset -> size
+  RangeAllocator ranges_;
 };
 
 }  // namespace fastb

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <vector>
 
+#include "../runtime/range_allocator.h"
 #include "plan.h"
 
 using namespace fastb;
@@ -40,7 +41,43 @@ static void replay_check(const Plan& p, int unit_bytes, uint64_t seed) {
     }
 }
 
+// The symmetric-heap allocator: deterministic offsets, alignment, coalescing, exhaustion.
+static void allocator_check() {
+  RangeAllocator a(1 << 20), b(1 << 20);
+  std::vector<size_t> offs;
+  uint64_t x = 12345;
+  for (int i = 0; i < 2000; ++i) {
+    x = x * 6364136223846793005ull + 1442695040888963407ull;
+    if (offs.empty() || (x >> 60) < 10) {
+      const size_t sz = (x >> 20) % 5000;
+      try {
+        const size_t oa = a.alloc(sz), ob = b.alloc(sz);
+        CHECK(oa == ob && oa % 256 == 0, "allocator offsets differ or are unaligned");
+        offs.push_back(oa);
+      } catch (const std::runtime_error&) {
+        bool threw = false;
+        try { b.alloc(sz); } catch (const std::runtime_error&) { threw = true; }
+        CHECK(threw, "exhaustion must be deterministic");
+      }
+    } else {
+      const size_t k = (x >> 30) % offs.size();
+      a.free(offs[k]); b.free(offs[k]);
+      offs.erase(offs.begin() + static_cast<std::ptrdiff_t>(k));
+    }
+    CHECK(a.in_use() == b.in_use() && a.live_blocks() == offs.size(), "allocator bookkeeping");
+  }
+  for (size_t o : offs) { a.free(o); b.free(o); }
+  CHECK(a.pristine() && b.pristine(), "free list must coalesce back to one block");
+  bool threw = false;
+  try { a.free(512); } catch (const std::invalid_argument&) { threw = true; }
+  CHECK(threw, "freeing an unknown offset must be refused");
+  threw = false;
+  try { a.alloc((1 << 20) + 1); } catch (const std::runtime_error&) { threw = true; }
+  CHECK(threw, "over-capacity request must be refused");
+}
+
 int main() {
+  allocator_check();
   const int topo[][2] = {{1, 1}, {1, 4}, {4, 1}, {2, 2}, {2, 4}, {3, 3}, {8, 1}, {4, 2}};
   const PlanKind kinds[] = {PlanKind::kStaged, PlanKind::kSingleBurst, PlanKind::kFanout, PlanKind::kSpreadOut};
   int plans = 0;
