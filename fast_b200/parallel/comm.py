@@ -125,13 +125,19 @@ class Communicator:
 
     # ---- scheduling -----------------------------------------------------------------------------
     def schedule(self, matrix, unit_bytes: int = 1, transpose: bool = False, kind=PlanKind.STAGED, chunk_bytes: Optional[int] = None,
-                 **plan_opts) -> Schedule:
+                 verify: bool = False, **plan_opts) -> Schedule:
         """Plan the collective for ``matrix`` (units; ``matrix[i, j]`` = rank i -> rank j).
 
         Every rank must pass the same matrix. Staged plans are built with pieces cut on 16-byte
-        boundaries whenever the unit size allows it.
+        boundaries whenever the unit size allows it. ``verify=True`` first compares the matrix hash
+        across the ranks (one small all-gather) and raises if they differ - ranks that plan different
+        collectives would wait for bytes that never come.
         """
         m = np.ascontiguousarray(matrix, dtype=np.int64)
+        if verify and self.world > 1:
+            from .host_executor import check_same_plan_inputs
+
+            check_same_plan_inputs(m, self.group)
         if chunk_bytes is None:
             # Work items: about 8 per CTA for the busiest rank (an uneven last round of 1 MiB items costs
             # up to half the bandwidth at 148 CTAs), between 64 KiB and 1 MiB, a power of two.
