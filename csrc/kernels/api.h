@@ -61,7 +61,12 @@ cudaError_t launch_wait_probe(const unsigned long long* flag, unsigned long long
 // grouped_gemm: tcgen05 / TMEM grouped bf16 GEMM (forward, dgrad, wgrad) with optional SwiGLU.
 // ---------------------------------------------------------------------------------------------
 enum class GemmMode : int { kForward = 0, kDgrad = 1, kWgrad = 2 };
-enum class GemmEpilogue : int { kStore = 0, kSwiGLU = 1 };
+enum class GemmEpilogue : int {
+  kStore = 0,
+  kSwiGLU = 1,     // forward: out = silu(gate) * up (+ optional raw gate|up tile)
+  kSwiGLUBwd = 2,  // dgrad of the second projection: the tile is d(act); c2 holds the saved gate|up tiles and c
+                   // receives d(gate|up) in the same layout (CTA-pair kernel only)
+};
 
 struct GemmArgs {
   const int* group_off;    // [num_groups + 1] row offsets of the groups, multiples of 128 (device)

@@ -194,6 +194,7 @@ static cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const 
 cudaError_t launch_grouped_gemm(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
                                 int ctas, cudaStream_t stream) {
   if (ctas < 1) return cudaErrorInvalidValue;
+  if (epi == GemmEpilogue::kSwiGLUBwd) return cudaErrorInvalidValue;  // only the CTA-pair kernel carries this epilogue
   if (epi == GemmEpilogue::kSwiGLU) {
     if (mode != GemmMode::kForward) return cudaErrorInvalidValue;
     return launch_one<GemmMode::kForward, GemmEpilogue::kSwiGLU>(map_a, map_b, args, ctas, stream);

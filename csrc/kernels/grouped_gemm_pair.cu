@@ -166,6 +166,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
       if (EPI == GemmEpilogue::kStore) {
         epilogue_store_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * BN, t_row, empty_reduction);
+      } else if (EPI == GemmEpilogue::kSwiGLUBwd) {
+        epilogue_swiglu_bwd_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (2 * BN),
+                                p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * (2 * BN), t_row);
       } else {
         epilogue_swiglu_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (BN / 2),
                             p.c2 ? p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * BN : nullptr, t_row);
@@ -212,6 +215,10 @@ cudaError_t launch_grouped_gemm_pair(GemmMode mode, GemmEpilogue epi, const CUte
   if (epi == GemmEpilogue::kSwiGLU) {
     if (mode != GemmMode::kForward) return cudaErrorInvalidValue;
     return launch_one<GemmMode::kForward, GemmEpilogue::kSwiGLU>(map_a, map_b, args, ctas, stream);
+  }
+  if (epi == GemmEpilogue::kSwiGLUBwd) {
+    if (mode != GemmMode::kDgrad || args.c2 == nullptr) return cudaErrorInvalidValue;
+    return launch_one<GemmMode::kDgrad, GemmEpilogue::kSwiGLUBwd>(map_a, map_b, args, ctas, stream);
   }
   switch (mode) {
     case GemmMode::kForward: return launch_one<GemmMode::kForward, GemmEpilogue::kStore>(map_a, map_b, args, ctas, stream);

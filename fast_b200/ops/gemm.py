@@ -14,7 +14,7 @@ from .. import runtime
 from ..utils.config import CONFIG
 
 FORWARD, DGRAD, WGRAD = 0, 1, 2
-STORE, SWIGLU = 0, 1
+STORE, SWIGLU, SWIGLU_BWD = 0, 1, 2
 _BM, _BN, _BK = 128, 256, 64
 # CTA-pair kernel (256 x 256 tiles, cta_group::2); set False to fall back to the one-CTA kernel.
 USE_PAIR = CONFIG.gemm != "one"
@@ -88,11 +88,22 @@ def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, 
     return out
 
 
-def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, timeout_s: float = 5.0, gate=None) -> torch.Tensor:
-    """out[rows of g] = dy[rows of g] @ w[g]  (dy [R, N], w [G, N, K], out [R, K])."""
+def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, timeout_s: float = 5.0, gate=None,
+                       swiglu_bwd_of: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[rows of g] = dy[rows of g] @ w[g]  (dy [R, N], w [G, N, K], out [R, K]).
+
+    With ``swiglu_bwd_of`` (the saved gate|up tiles [R, 2K]) the product is taken as d(act) and the
+    epilogue writes d(gate|up) [R, 2K] into ``out`` instead (CTA-pair kernel only): the SwiGLU
+    backward costs no extra pass over memory.
+    """
     G, N, K = w.shape
     assert dy.shape[1] == N and N % _BK == 0 and K % _BN == 0 and dy.shape[0] % _BM == 0
     C = runtime.ext()
+    if swiglu_bwd_of is not None:
+        assert USE_PAIR and out.shape[1] == 2 * K and swiglu_bwd_of.shape == out.shape
+        C.grouped_gemm(DGRAD, SWIGLU_BWD, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, swiglu_bwd_of,
+                       _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
+        return out
     C.grouped_gemm(DGRAD, STORE, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, None, _st().ptr(),
                    int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
     return out

@@ -272,11 +272,15 @@ class ExpertParallel:
                         self._off(self.dy_recv), 0, self.arrive._symm_off + self.El * 8, self._flag_off(2), rs.epoch, self.status, self.timeout_ns,
                         self.comm_ctas, None)
         gate = (self._arrive_ptr(1), self.arrive_target[1])
-        gemm.grouped_gemm_dgrad(self.dy_recv, w2, rs.group_off, self.dact, gate=gate)
+        if gemm.USE_PAIR:  # d(act) never leaves the tensor memory: the dgrad epilogue applies the SwiGLU backward
+            gemm.grouped_gemm_dgrad(self.dy_recv, w2, rs.group_off, self.dgu, gate=gate, swiglu_bwd_of=self.gu)
+        else:
+            gemm.grouped_gemm_dgrad(self.dy_recv, w2, rs.group_off, self.dact, gate=gate)
         gemm.grouped_gemm_wgrad(self.dy_recv, self.act, rs.group_off, dw2)
         if after_dw2 is not None:
             after_dw2()
-        C.swiglu_bwd(self.gu, self.dact, self.dgu, rs.group_off.data_ptr() + 4 * self.El)
+        if not gemm.USE_PAIR:
+            C.swiglu_bwd(self.gu, self.dact, self.dgu, rs.group_off.data_ptr() + 4 * self.El)
         gemm.grouped_gemm_dgrad(self.dgu, w13, rs.group_off, self.dx_recv)
         gemm.grouped_gemm_wgrad(self.dgu, self.x_recv, rs.group_off, dw13)
         C.peer_signal(self.comm.heap, self._flag_off(3), rs.epoch, 0)

@@ -112,3 +112,29 @@ def test_large_shape_matches():
     for i in range(G):
         s, e = int(off[i]), int(off[i + 1])
         _close(out[s:e], a[s:e].float() @ w[i].float().T)
+
+
+def test_dgrad_with_fused_swiglu_backward(kernel_variant):
+    """dgrad of the second projection with the SwiGLU backward applied in its epilogue."""
+    if kernel_variant != "cta_pair":
+        pytest.skip("only the CTA-pair kernel carries this epilogue")
+    from fast_b200.models.moe import split_gate_up
+    from fast_b200.ops import gemm
+
+    G, H, I = 2, 256, 512
+    counts, off, R, dy, _ = _setup(G, 256, H, [300, 200], seed=13)  # dy [R, H]
+    g = torch.Generator(device="cuda").manual_seed(17)
+    w2 = (torch.randn(G, H, I, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    gu = torch.randn(R, 2 * I, generator=g, device="cuda").to(torch.bfloat16)
+    dgu = torch.full((R, 2 * I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_dgrad(dy, w2, off, dgu, swiglu_bwd_of=gu)
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        dact = (dy[s:e].float() @ w2[i].float()).to(torch.bfloat16).float()
+        t = gu[s:e].float().view(e - s, I // 128, 2, 128)
+        gt, ut = t[:, :, 0].reshape(e - s, I).requires_grad_(), t[:, :, 1].reshape(e - s, I).requires_grad_()
+        (torch.nn.functional.silu(gt) * ut).backward(dact)
+        got = dgu[s:e].float().view(e - s, I // 128, 2, 128)
+        _close(got[:, :, 0].reshape(e - s, I), gt.grad)
+        _close(got[:, :, 1].reshape(e - s, I), ut.grad)
