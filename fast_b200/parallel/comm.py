@@ -169,7 +169,7 @@ class Communicator:
         return s
 
     # ---- execution --------------------------------------------------------------------------------
-    def _launch_args(self, s: Schedule, output: torch.Tensor, input: torch.Tensor):
+    def _launch_args(self, s: Schedule, output: torch.Tensor, input: torch.Tensor, staging: Optional[dict] = None):
         if self.broken:
             raise RuntimeError("communicator saw a failed collective; call reset() on every rank first")
         if input.numel() * input.element_size() < s.input_bytes:
@@ -181,8 +181,16 @@ class Communicator:
         if out_off is None:  # library-owned receive staging, copied out afterwards
             out_off = self._stage("recv", s.max_bytes["output"])
             copy_back = self.heap.tensor(out_off, [s.output_bytes], torch.uint8)
-        bal_off = self._stage("balance", s.max_bytes["balance"])
-        rail_off = self._stage("rail", s.max_bytes["rail"])
+        def staged(name):
+            t = (staging or {}).get(name)
+            if t is None:
+                return self._stage(name, s.max_bytes[name])
+            off = self.offset_of(t)
+            if off is None or t.numel() * t.element_size() < s.max_bytes[name]:
+                raise ValueError(f"caller-owned {name} staging must be a symmetric-heap tensor of at least {s.max_bytes[name]} bytes")
+            return off
+
+        bal_off, rail_off = staged("balance"), staged("rail")
         base = self.heap.base_ptr(self.rank)
         src = [input.data_ptr(), 0, base + bal_off, base + rail_off]
         dst = [0, out_off, bal_off, rail_off]
@@ -199,12 +207,15 @@ class Communicator:
     def free_buffers(self, recv: torch.Tensor) -> None:
         self.free(recv)
 
-    def all_to_all_v(self, output: torch.Tensor, input: torch.Tensor, s: Schedule) -> torch.Tensor:
+    def all_to_all_v(self, output: torch.Tensor, input: torch.Tensor, s: Schedule, staging: Optional[dict] = None) -> torch.Tensor:
         """Run a scheduled all-to-all(v) on the current stream. ``input`` holds the segments for
         rank 0..n-1 back to back; ``output`` receives the segments from rank 0..n-1 back to back.
         ``output`` in the symmetric heap (``alloc``) is written in place by the peers; any other
-        tensor goes through a library-owned receive buffer and one extra local copy."""
-        src, dst, copy_back = self._launch_args(s, output, input)
+        tensor goes through a library-owned receive buffer and one extra local copy. ``staging``
+        may name caller-owned symmetric tensors for the two-tier plans' ``"balance"`` and ``"rail"``
+        areas (sizes from ``Schedule.max_bytes``; same allocation order on every rank), as the
+        reference's all_to_all_2 takes them (amd/flash.cpp:570-629); by default the library keeps its own."""
+        src, dst, copy_back = self._launch_args(s, output, input, staging)
         self.epoch += 1
         ctas = max(1, min(self.ctas, s.program.n_items))  # a handful of work items needs a handful of CTAs
         self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, ctas, self.threads)
