@@ -95,6 +95,10 @@ class Communicator:
         self.plan_cache = sched.PlanCache()
         self._staging = {}  # name -> (offset, bytes)
         self._sched_cache = {}
+        # Optional liveness.Heartbeat: consulted before every launch so that a lost peer raises
+        # PeerLost on the host instead of making a kernel wait for its timeout.
+        self.liveness = None
+        self.liveness_max_age_s = 2.0
 
     # ---- symmetric memory ---------------------------------------------------------------------
     def alloc(self, shape, dtype=torch.uint8) -> torch.Tensor:
@@ -172,6 +176,8 @@ class Communicator:
     def _launch_args(self, s: Schedule, output: torch.Tensor, input: torch.Tensor, staging: Optional[dict] = None):
         if self.broken:
             raise RuntimeError("communicator saw a failed collective; call reset() on every rank first")
+        if self.liveness is not None:
+            self.liveness.require_alive(self.liveness_max_age_s)
         if input.numel() * input.element_size() < s.input_bytes:
             raise ValueError("input smaller than the schedule needs")
         if output.numel() * output.element_size() < s.output_bytes:
