@@ -19,6 +19,7 @@ import torch.distributed as dist
 from .. import sched
 from ..parallel import Communicator
 from ..sched import PlanKind, Topology
+from ..utils.results import ResultLog
 
 
 def _time_ms(fn, iters, warmup):
@@ -118,6 +119,7 @@ def run(args):
     inp = torch.randn(max(max_row, need) // 2, generator=g, device="cuda", dtype=torch.bfloat16).view(torch.uint8)
     nccl_out = torch.empty(need, dtype=torch.uint8, device="cuda")
     results = []
+    log = ResultLog(getattr(args, "out", "") or None, "a2a", world=world)
     for size in args.sizes:
         skews = args.skews if args.mode == "skewed" else [None]
         for skew in skews:
@@ -168,6 +170,7 @@ def run(args):
             results.append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)
+                log.add(row)
     dist.barrier()
     dist.destroy_process_group()
     return results
@@ -188,6 +191,7 @@ def main():
     ap.add_argument("--p2p-baseline", action="store_true", help="also run the staged plan over NCCL send/recv groups (the reference's executor style)")
     ap.add_argument("--servers", type=int, default=0, help="treat the ranks as this many virtual servers (hierarchical FAST plan + single-burst ablation)")
     ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--out", default="", help="append every result row to this file (JSON lines)")
     run(ap.parse_args())
 
 

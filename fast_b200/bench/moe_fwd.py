@@ -21,6 +21,7 @@ import torch.distributed as dist
 from .. import runtime
 from ..parallel import Communicator
 from ..parallel.ep import ExpertParallel
+from ..utils.results import ResultLog
 
 
 def _max_over_ranks(vals, world):
@@ -215,6 +216,7 @@ def main():
     ap.add_argument("--skip-nccl", action="store_true")
     ap.add_argument("--graph", action="store_true", help="time the whole forward layer eagerly and as one CUDA graph replay")
     ap.add_argument("--overlap", action="store_true", help="send rows expert by expert on a side stream while the gated GEMM runs (dispatch_us then only times the launch)")
+    ap.add_argument("--out", default="", help="append the result row to this file (JSON lines)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -228,6 +230,7 @@ def main():
         res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap)
     if rank == 0:
         print(json.dumps(res), flush=True)
+        ResultLog(a.out or None, "moe_fwd").add(res)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

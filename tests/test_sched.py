@@ -304,3 +304,16 @@ def test_simulator_sweeps_and_plot_parser(tmp_path):
     xlabel, ser = plot_sim.series(rows, "topology")
     assert set(ser) == {"switch", "full_mesh", "ring", "hybrid_cube_mesh"}
     assert all(j["staging_over_payload"] < 1.0 for j in rows["overhead"])
+
+
+def test_result_log_appends_json_rows(tmp_path):
+    from fast_b200.utils.results import ResultLog
+
+    path = str(tmp_path / "sub" / "rows.jsonl")
+    log = ResultLog(path, "a2a", world=8)
+    log.add({"row_bytes": 1 << 20, "ms": 0.5})
+    ResultLog(path, "moe_fwd").add({"layer_us": 5000.0})
+    rows = list(ResultLog.read(path))
+    assert [r["bench"] for r in rows] == ["a2a", "moe_fwd"] and rows[0]["world"] == 8 and rows[0]["ms"] == 0.5
+    assert [r["layer_us"] for r in ResultLog.read(path, "moe_fwd")] == [5000.0]
+    assert ResultLog(None, "x").add({"a": 1})["a"] == 1   # without a path: nothing written, row returned
