@@ -47,7 +47,10 @@ workload_zipf_entries = _S.workload_zipf_entries
 # figures are those of the reference simulator's tables (simulation/scheduler/config.cpp:8-59), plus
 # the measured NVLink-5 port of a B200 (770 GB/s peer copy, ~2 us per hop).
 INTRA_LINKS = {"DGX2": (0.1, 8.0), "FAST": (0.1, 1.0), "B100": (0.1, 1.2), "H100": (0.1, 2.3), "NDV2": (0.1, 46.0), "MI300X": (0.1, 5.0),
-               "B200_NVLINK5": (2.0, 1e3 / 770.0)}
+               "B200_NVLINK5": (2.0, 1e3 / 770.0),
+               # least-squares fit of (launch + handshake latency, effective port rate) to this runtime's
+               # measured 8-GPU skewed all-to-all(v) completion times (64 MiB - 1 GiB rows, Zipf 0 - 1.5)
+               "B200_MEASURED": (44.0, 1e3 / 644.0)}
 INTER_LINKS = {"INFB": (1.7, 106.0), "ETHER100": (0.7, 84.0), "ETHER400": (0.7, 22.0)}
 
 

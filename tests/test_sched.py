@@ -317,3 +317,16 @@ def test_result_log_appends_json_rows(tmp_path):
     assert [r["bench"] for r in rows] == ["a2a", "moe_fwd"] and rows[0]["world"] == 8 and rows[0]["ms"] == 0.5
     assert [r["layer_us"] for r in ResultLog.read(path, "moe_fwd")] == [5000.0]
     assert ResultLog(None, "x").add({"a": 1})["a"] == 1   # without a path: nothing written, row returned
+
+
+def test_fitted_b200_link_model_tracks_the_measured_table():
+    """One-stage (fan-out) cost under the fitted B200 link model vs completion times measured on
+    8 B200s for the same seeded matrices (ms; best of this runtime's plans): within 12 %."""
+    measured = {(64, 0.0): 0.134, (64, 1.0): 0.188, (256, 0.5): 0.563, (256, 1.5): 0.819, (1024, 0.0): 1.828, (1024, 1.5): 3.151}
+    link = sched.intra_link("B200_MEASURED")
+    for (mib, skew), ms in measured.items():
+        preds = []
+        for mi in range(6):
+            m = sched.workload_zipf_rows(8, skew, mib << 20, 1000 * mi + 7, 16)
+            preds.append(sched.build_plan(m, Topology.flat(8), kind=PlanKind.FANOUT, split_align=16).cost(link, link, 1e-6)["total_us"])
+        assert abs(np.mean(preds) * 1e-3 / ms - 1.0) < 0.12, (mib, skew, np.mean(preds) * 1e-3, ms)
