@@ -55,11 +55,13 @@ def main():
     dw2 = torch.empty_like(w2)
     dw13 = torch.empty_like(w13)
     dx = torch.empty(R, H, device=dev, dtype=torch.bfloat16)
+    dgu = torch.empty(R, 2 * I, device=dev, dtype=torch.bfloat16)
     cases = {
         "fwd_w13_swiglu": (lambda: gemm.grouped_gemm_fwd(x, w13, off, act, swiglu=True, gate_up_out=gu), 2 * R * H * 2 * I),
         "fwd_w13_plain": (lambda: gemm.grouped_gemm_fwd(x, w13, off, gu), 2 * R * H * 2 * I),
         "fwd_w2": (lambda: gemm.grouped_gemm_fwd(act, w2, off, y), 2 * R * H * I),
         "dgrad_w2": (lambda: gemm.grouped_gemm_dgrad(y, w2, off, dact), 2 * R * H * I),
+        **({"dgrad_w2_swiglu_bwd": (lambda: gemm.grouped_gemm_dgrad(y, w2, off, dgu, swiglu_bwd_of=gu), 2 * R * H * I)} if gemm.USE_PAIR else {}),
         "wgrad_w2": (lambda: gemm.grouped_gemm_wgrad(y, act, off, dw2), 2 * R * H * I),
         "dgrad_w13": (lambda: gemm.grouped_gemm_dgrad(gu, w13, off, dx), 2 * R * H * 2 * I),
         "wgrad_w13": (lambda: gemm.grouped_gemm_wgrad(gu, x, off, dw13), 2 * R * H * 2 * I),
