@@ -129,3 +129,32 @@ def test_multi_process_bit_exact():
                         "--master-port", "29533", os.path.join(os.path.dirname(__file__), "mp_a2a_worker.py")], capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "A2A_MP_OK" in r.stdout
+
+
+def test_reference_shaped_adapter_on_one_rank():
+    """FlashAllToAll (the reference's flash_t calls) end to end on a world of one: library-owned
+    and caller-owned paths both deliver the self segment."""
+    from fast_b200.compat import FlashAllToAll
+    from fast_b200.parallel import Communicator
+
+    comm = Communicator(heap_bytes=64 << 20, device=0)
+    f = FlashAllToAll(0, 1, 1, 1, 128, 9, comm=comm)
+    tokens = 1000
+    f.schedule(np.array([tokens], dtype=np.int32), 0)
+    assert list(f.get_buffer_szs()) == [tokens, 0, 0, 0, 0, 0]
+    x = torch.randn(tokens, 128, device="cuda").to(torch.bfloat16)
+    y = torch.zeros_like(x)
+    f.init_buffers(x, y)
+    f.all_to_all()
+    comm.check()
+    assert torch.equal(x, y)
+    f.free_buffers()
+    z = comm.alloc((tokens, 128), torch.bfloat16)
+    z.zero_()
+    f.all_to_all_2(x, z, None, None, None, None, None, None)
+    comm.check()
+    assert torch.equal(x, z)
+    w = torch.zeros_like(x)
+    f.all_to_all_v(x.view(-1), w.view(-1), [tokens], [tokens])
+    comm.check()
+    assert torch.equal(x, w)

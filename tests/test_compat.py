@@ -1,0 +1,116 @@
+"""The reference-shaped adapter (FlashAllToAll) on a stand-in communicator: planning, buffer sizes,
+staging choice and dtype codes, all on the CPU."""
+import numpy as np
+import pytest
+import torch
+
+from fast_b200 import sched
+from fast_b200.compat import DTYPE_CODES, FlashAllToAll, code_of, dtype_of
+from fast_b200.parallel.comm import Schedule
+from fast_b200.sched import PlanKind, Topology
+
+
+class _Comm:
+    """Plans for real (host scheduler + lowering), records launches instead of running them."""
+
+    def __init__(self, rank, world, topo):
+        self.rank, self.world, self.topo = rank, world, topo
+        self.calls = []
+        self.symmetric = set()
+
+    def schedule(self, m, unit_bytes=1, transpose=False, kind=PlanKind.STAGED):
+        plan = sched.build_plan(m, self.topo, kind=kind, transpose=transpose, split_align=1)
+        assert plan.validate() == ""
+        return Schedule(plan, unit_bytes, None, plan.lower(self.rank, unit_bytes, 1 << 16), self.rank)
+
+    def offset_of(self, t):
+        return 0 if id(t) in self.symmetric else None
+
+    def alloc(self, n, dtype=torch.uint8):
+        t = torch.zeros(n, dtype=dtype)
+        self.symmetric.add(id(t))
+        return t
+
+    def init_buffers(self, s):
+        return torch.zeros(max(s.max_bytes["input"], 1), dtype=torch.uint8), self.alloc(max(s.max_bytes["output"], 1))
+
+    def free_buffers(self, recv):
+        self.symmetric.discard(id(recv))
+
+    def all_to_all_v(self, output, input, s, staging=None):
+        self.calls.append(("v", output, input, s, staging))
+        return output
+
+    def all_to_all_single(self, output, input, out_splits, in_splits, kind=None):
+        self.calls.append(("single", output, input, out_splits, in_splits, kind))
+        return output
+
+
+def _matrix(world, seed=0):
+    rng = np.random.default_rng(seed)
+    m = rng.integers(0, 50, size=(world, world))
+    np.fill_diagonal(m, 0)
+    return m
+
+
+def test_dtype_codes_follow_the_reference_table():
+    assert dtype_of(9) == torch.bfloat16 and dtype_of(10) == torch.float8_e4m3fn and dtype_of(11) == torch.float8_e5m2
+    assert dtype_of(6) == torch.float16 and dtype_of(7) == torch.float32 and dtype_of(99) == torch.int8
+    for c, d in DTYPE_CODES.items():
+        assert code_of(d) == c
+
+
+def test_schedule_and_buffer_sizes_in_tokens():
+    world, S, G, hidden = 8, 2, 4, 64
+    m = _matrix(world)
+    for rank in (0, 5):
+        f = FlashAllToAll(rank, world, S, G, hidden, 9, b"ignored", comm=_Comm(rank, world, Topology(S, G)))
+        assert (f.get_world_size(), f.get_rank(), f.get_server_n(), f.get_hidden_sz()) == (world, rank, S, hidden)
+        with pytest.raises(RuntimeError):
+            f.get_buffer_szs()
+        f.schedule(m.reshape(-1), 0)
+        szs = f.get_buffer_szs()
+        assert len(szs) == 6 and szs[0] == m[rank].sum() and szs[1] == 0 and szs[4] == 0 and szs[5] == 0
+        assert szs[2] > 0 and szs[3] > 0                        # two-tier plan: balance and rail staging exist
+        assert f.sched.unit_bytes == hidden * 2 and f.sched.output_bytes == m[:, rank].sum() * hidden * 2
+        f.schedule(m.reshape(-1), 1)                            # backward: the transposed collective
+        assert f.get_buffer_szs()[0] == m[:, rank].sum() and f.sched.output_bytes == m[rank].sum() * hidden * 2
+    flat = FlashAllToAll(0, world, S, G, hidden, 9, comm=_Comm(0, world, Topology.flat(world)), flat=True)
+    flat.schedule(m, 0)
+    assert list(flat.get_buffer_szs()[1:]) == [0, 0, 0, 0, 0]   # flat: data lands in place, no staging at all
+    with pytest.raises(ValueError):
+        FlashAllToAll(0, world, 3, 4, hidden, 9, comm=_Comm(0, world, Topology(S, G)))
+
+
+def test_all_to_all_paths_choose_buffers_like_the_reference_calls():
+    world, S, G, hidden = 4, 2, 2, 32
+    comm = _Comm(1, world, Topology(S, G))
+    f = FlashAllToAll(1, world, S, G, hidden, 7, comm=comm)
+    m = _matrix(world, 3)
+    f.schedule(m, 0)
+    s = f.sched
+    inp = torch.zeros(max(s.input_bytes, 1), dtype=torch.uint8)
+    out = torch.zeros(max(s.output_bytes, 1), dtype=torch.uint8)
+    with pytest.raises(RuntimeError):
+        f.all_to_all()
+    f.init_buffers(inp, out)                                    # plain output: goes through a symmetric receive buffer
+    assert f.all_to_all() is out and comm.calls[-1][1] is f._recv
+    f.free_buffers()
+    sym_out = comm.alloc(max(s.output_bytes, 1))
+    f.init_buffers(inp, sym_out)                                # symmetric output: written in place
+    assert f.all_to_all() is sym_out and comm.calls[-1][1] is sym_out
+    f.free_buffers()
+    # caller-owned staging: used when symmetric and large enough, else the library's own
+    lbrecv, cros = comm.alloc(s.max_bytes["balance"]), comm.alloc(s.max_bytes["rail"])
+    f.all_to_all_2(inp, sym_out, None, None, lbrecv, cros, None, None)
+    assert comm.calls[-1][4] == {"balance": lbrecv, "rail": cros}
+    f.all_to_all_2(inp, sym_out, None, None, torch.zeros(8, dtype=torch.uint8), comm.alloc(1), None, None)
+    assert comm.calls[-1][4] is None
+    # fan-out baseline: splits in tokens, rows of hidden_sz elements
+    x = torch.zeros(int(m[1].sum()) * hidden, dtype=torch.float32)
+    y = torch.zeros(int(m[:, 1].sum()) * hidden, dtype=torch.float32)
+    f.all_to_all_v(x, y, list(m[1]), list(m[:, 1]))
+    kind, o, i, osz, isz, k = comm.calls[-1]
+    assert kind == "single" and i.shape == (int(m[1].sum()), hidden) and o.shape == (int(m[:, 1].sum()), hidden) and k == PlanKind.FANOUT
+    with pytest.raises(ValueError):
+        f.all_to_all_v(x, y, [1], [1])
