@@ -146,3 +146,86 @@ class FlashAllToAll:
     @staticmethod
     def print_tensor(t: torch.Tensor) -> None:
         print(t.detach().cpu())
+
+
+def pattern_words(src: int, dst: int, count: int, device) -> torch.Tensor:
+    """Verification words of one (src, dst) segment: ``src << 24 | dst << 16 | index & 0xffff``, the
+    scheme of the reference's buffer checks (nvidia/src/fast_alltoall/flash_alltoall_nvshmem.cu:1445-1473)."""
+    idx = torch.arange(count, device=device, dtype=torch.int32) & 0xFFFF
+    return idx | ((src << 24) | (dst << 16))
+
+
+class FlashComm:
+    """The reference's NVIDIA tester class (``flash_comm_t(rank, dev_n, world_size, uid)`` with
+    ``test_basic_alltoall()`` and ``test_flash_alltoall()``, nvidia/alltoall_nvshmem.cpp:390-601) on
+    this runtime: rank 0 draws a uniform random workload, every rank gets it, the collective is
+    timed on the device after warm-up and the output is checked word for word. ``uid`` is accepted
+    and ignored (no NVSHMEM bootstrap exists here). Both tests return
+    ``{"time_ms", "algbw_GBps", "per_gpu_MB", "verified"}``; rank 0 also prints them."""
+
+    def __init__(self, rank: int, dev_n: int, world_size: int, uid=None, *, comm=None, mean_units: int = 1 << 23,
+                 heap_bytes: Optional[int] = None, seed: int = 1):
+        self.rank, self.dev_n, self.world = int(rank), int(dev_n), int(world_size)
+        self.mean_units, self.seed = int(mean_units), int(seed)
+        if comm is None:
+            from .parallel import Communicator
+
+            torch.cuda.set_device(self.rank % self.dev_n)
+            need = 3 * 8 * self.mean_units * self.world * 2 + (64 << 20)   # output + staging, worst column twice the mean
+            comm = Communicator(heap_bytes=heap_bytes or need)
+        self.comm = comm
+
+    def _workload(self) -> np.ndarray:
+        import torch.distributed as dist
+
+        from . import sched
+
+        m = torch.from_numpy(np.ascontiguousarray(sched.workload_uniform(self.world, 2 * self.mean_units, self.seed, False)))
+        if self.world > 1:
+            dev = self.comm.device if dist.get_backend() == "nccl" else torch.device("cpu")
+            t = m.to(dev)
+            dist.broadcast(t, 0)
+            m = t.cpu()
+        return m.numpy()
+
+    def _run(self, kind, data_size: int, warmup: int, iters: int, name: str) -> dict:
+        m = self._workload()
+        r, dev, wpu = self.rank, self.comm.device, data_size // 4
+        s = self.comm.schedule(m, unit_bytes=data_size, kind=kind)
+        inp = torch.cat([pattern_words(r, d, int(m[r, d]) * wpu, dev) for d in range(self.world)] + [torch.zeros(4, dtype=torch.int32, device=dev)])
+        want = torch.cat([pattern_words(src, r, int(m[src, r]) * wpu, dev) for src in range(self.world)])
+        out = self.comm.alloc(max(s.max_bytes["output"], 16) // 4, torch.int32)
+        out.zero_()
+        for _ in range(warmup):
+            self.comm.all_to_all_v(out, inp, s)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            self.comm.all_to_all_v(out, inp, s)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        self.comm.check()
+        ms = torch.tensor([e0.elapsed_time(e1) / max(iters, 1)], device=dev)
+        ok = torch.tensor([1 if torch.equal(out[: want.numel()], want) else 0], device=dev)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        self.comm.free(out)
+        total = int(m.sum()) * data_size
+        res = {"time_ms": float(ms.item()), "algbw_GBps": total / self.world / (float(ms.item()) * 1e-3) / 1e9 if ms.item() > 0 else 0.0,
+               "per_gpu_MB": total / self.world / 1e6, "verified": bool(ok.item())}
+        if self.rank == 0:
+            print(f"per-GPU size: {res['per_gpu_MB']:.1f} MB, {name} algbw: {res['algbw_GBps']:.1f} GBps, total time: {res['time_ms']:.3f} ms, "
+                  f"verified: {res['verified']}", flush=True)
+        return res
+
+    def test_basic_alltoall(self, warmup: int = 20, iters: int = 20) -> dict:
+        """Every pair at once (the reference's spread-out / fan-out baseline run), 4-byte units."""
+        return self._run(PlanKind.FANOUT, 4, warmup, iters, "fanout")
+
+    def test_flash_alltoall(self, warmup: int = 50, iters: int = 50) -> dict:
+        """The scheduled collective (balance, BvN stages, redistribute), 8-byte units as in the reference."""
+        return self._run(PlanKind.STAGED, 8, warmup, iters, "flash")

@@ -158,3 +158,13 @@ def test_reference_shaped_adapter_on_one_rank():
     f.all_to_all_v(x.view(-1), w.view(-1), [tokens], [tokens])
     comm.check()
     assert torch.equal(x, w)
+
+
+def test_reference_tester_class_on_one_rank():
+    """FlashComm (the reference's NVIDIA tester class): both self-tests verify their buffers."""
+    from fast_b200.compat import FlashComm
+    from fast_b200.parallel import Communicator
+
+    t = FlashComm(0, 1, 1, None, comm=Communicator(heap_bytes=64 << 20, device=0), mean_units=1 << 16)
+    for res in (t.test_basic_alltoall(warmup=2, iters=2), t.test_flash_alltoall(warmup=2, iters=2)):
+        assert res["verified"] and res["time_ms"] > 0 and res["per_gpu_MB"] > 0

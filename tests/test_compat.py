@@ -114,3 +114,12 @@ def test_all_to_all_paths_choose_buffers_like_the_reference_calls():
     assert kind == "single" and i.shape == (int(m[1].sum()), hidden) and o.shape == (int(m[:, 1].sum()), hidden) and k == PlanKind.FANOUT
     with pytest.raises(ValueError):
         f.all_to_all_v(x, y, [1], [1])
+
+
+def test_pattern_words_match_the_reference_scheme():
+    from fast_b200.compat import pattern_words
+
+    w = pattern_words(3, 5, 70000, "cpu")
+    assert w.dtype == torch.int32 and w.numel() == 70000
+    assert int(w[0]) == (3 << 24) | (5 << 16) and int(w[65535]) == (3 << 24) | (5 << 16) | 0xFFFF and int(w[65536]) == int(w[0])
+    assert pattern_words(0, 0, 0, "cpu").numel() == 0
