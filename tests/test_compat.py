@@ -123,3 +123,33 @@ def test_pattern_words_match_the_reference_scheme():
     assert w.dtype == torch.int32 and w.numel() == 70000
     assert int(w[0]) == (3 << 24) | (5 << 16) and int(w[65535]) == (3 << 24) | (5 << 16) | 0xFFFF and int(w[65536]) == int(w[0])
     assert pattern_words(0, 0, 0, "cpu").numel() == 0
+
+
+def test_named_configs_and_memory_plan():
+    from fast_b200.models.configs import (CONFIGS, DEEPSEEK_V3_MOE_LAYER, HBM_BYTES, MIXTRAL_8X7B_BLOCK, flops_per_step, max_tokens_per_rank,
+                                          memory_plan)
+
+    assert set(CONFIGS) == {"mixtral-8x7b-block", "deepseek-v3-moe-layer"}
+    mx, ds = MIXTRAL_8X7B_BLOCK, DEEPSEEK_V3_MOE_LAYER
+    assert (mx.hidden, mx.inter, mx.num_experts, mx.top_k, mx.tokens_per_rank, mx.vocab) == (4096, 14336, 8, 2, 32768, 32000)
+    assert (ds.hidden, ds.inter, ds.num_experts, ds.top_k, ds.tokens_per_rank, ds.fp8_dispatch) == (7168, 2048, 256, 8, 4096, True)
+    # capacity: the engine's formula (worst case, padded to 256 rows)
+    assert mx.capacity_rows(1) == 67584 and mx.capacity_rows(8) == (8 * 32768 * 1 + 256 + 255) // 256 * 256
+    assert mx.capacity_rows(8, capacity_factor=1.0) == (32768 * 2 + 256 + 255) // 256 * 256
+    with pytest.raises(ValueError):
+        mx.experts_per_rank(3)
+    for cfg in (mx, ds):
+        for world in (1, 2, 4, 8):
+            p = memory_plan(cfg, world)
+            assert p["total"] == sum(p[k] for k in ("symmetric_heap", "workspace", "weights", "grads", "optimizer", "tokens"))
+            assert p["fits_b200"] and p["total"] < HBM_BYTES
+    # expert weights shard over ranks, AdamW state is 6x the bf16 weights, forward-only layers carry none
+    p1, p8 = memory_plan(mx, 1), memory_plan(mx, 8)
+    assert p1["optimizer"] == 6 * p1["weights"] and p8["weights"] < p1["weights"] / 4 and memory_plan(ds, 8)["optimizer"] == 0
+    assert memory_plan(mx, 8, capacity_factor=1.0)["total"] < p8["total"] / 2
+    # the largest batch that fits is far above the benchmark's, and one step more does not fit
+    t = max_tokens_per_rank(mx, 8)
+    assert t > mx.tokens_per_rank and memory_plan(mx.with_(tokens_per_rank=t), 8)["fits_b200"]
+    assert not memory_plan(mx.with_(tokens_per_rank=t + 1024), 8)["fits_b200"]
+    f = flops_per_step(mx, 8)
+    assert f["expert_gemm_total"] == 3 * f["expert_gemm_fwd"] == 3 * 2.0 * 65536 * 4096 * 14336 * 3
