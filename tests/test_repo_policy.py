@@ -68,3 +68,33 @@ def test_graft_entry_has_build_and_smoke():
 
     assert os.path.exists(os.path.join(ROOT, "build", "fastb-sim"))
     assert any(f.startswith("_C.") and f.endswith(".so") for f in os.listdir(os.path.dirname(fast_b200.__file__)))
+
+
+def test_bench_clock_sampler_parses_samples_inside_the_window():
+    import importlib.util
+    import time
+
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class _Proc:
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+    s = bench.ClockSampler(0)
+    s.proc = _Proc()
+    t0 = time.monotonic()
+    s.t_begin, s.t_end = t0 + 1.0, t0 + 2.0
+    row = lambda mhz, cap: [str(mhz), "1965", "640.5", "Not Active", "Not Active", "Not Active", cap]
+    s.rows = [(t0 + 0.5, row(1900, "Not Active")),           # before the window: ignored
+              (t0 + 1.2, row(1200, "Active")), (t0 + 1.5, row(1300, "Active")), (t0 + 1.9, row(1250, "Not Active")),
+              (t0 + 1.6, ["garbage"]), (t0 + 3.0, row(1950, "Not Active"))]
+    out = s.stop()
+    assert out["sm_mhz"] == 1250 and out["sm_max_mhz"] == 1965 and out["samples"] == 3 and out["reasons"] == ["sw_power_cap"]
+    assert out["power_w_max"] == 640.5
+    s2 = bench.ClockSampler(0)                                # nvidia-smi missing: says so instead of failing
+    assert s2.stop()["reasons"] == ["nvidia-smi unavailable"]
