@@ -221,4 +221,26 @@ PlanCost model_cost(const Plan& p, const CostModel& cm) {
   return c;
 }
 
+PlanChoice select_plan(const Matrix& traffic, Topology topo, const PlanOptions& base, const CostModel& cm,
+                       const std::vector<PlanKind>& candidates) {
+  if (candidates.empty()) throw std::invalid_argument("select_plan: no candidate kinds");
+  PlanChoice best;
+  bool have = false;
+  std::vector<std::pair<PlanKind, double>> table;
+  for (PlanKind k : candidates) {
+    PlanOptions o = base;
+    o.kind = k;
+    Plan p = build_plan(traffic, topo, o);
+    PlanCost c = model_cost(p, cm);
+    table.emplace_back(k, c.total_us);
+    if (!have || c.total_us < best.cost.total_us) {
+      best.plan = std::move(p);
+      best.cost = std::move(c);
+      have = true;
+    }
+  }
+  best.modeled_us = std::move(table);
+  return best;
+}
+
 }  // namespace fastb

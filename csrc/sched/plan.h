@@ -141,6 +141,17 @@ struct PlanCost {
 // redistribution (simulation/scheduler/global.cpp:237-402 pipeline2). For one server per GPU
 // (flat NVSwitch domain) every stage is charged to the `inter` link.
 PlanCost model_cost(const Plan& p, const CostModel& cm);
+// Builds one plan per candidate kind and keeps the one the cost model says finishes first (ties go
+// to the earlier candidate). This is the staged-versus-fan-out switch: permutation stages pay one
+// alpha each and win when the slow tier is bandwidth-bound and skewed; a single fan-out wins for
+// small messages. With the kAlphaBeta scale policy in `base`, staged candidates are coarsened first.
+struct PlanChoice {
+  Plan plan;
+  PlanCost cost;
+  std::vector<std::pair<PlanKind, double>> modeled_us;  // every candidate, in the order given
+};
+PlanChoice select_plan(const Matrix& traffic, Topology topo, const PlanOptions& base, const CostModel& cm,
+                       const std::vector<PlanKind>& candidates);
 // Link model for one NVLink-5 port: alpha in us, bandwidth in GB/s.
 LinkModel nvlink_model(double gbytes_per_s = 900.0, double alpha_us = 2.0);
 LinkModel gbps_model(double gbit_per_s, double alpha_us);

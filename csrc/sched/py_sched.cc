@@ -171,6 +171,17 @@ PYBIND11_MODULE(_sched, m) {
      py::arg("scale_policy") = ScalePolicy::kNone, py::arg("scale") = 0, py::arg("split_align") = 1, py::arg("transpose") = false,
      py::arg("inter") = LinkModel{0.7, 22.0}, py::arg("intra") = LinkModel{0.1, 1.2}, py::arg("mb_per_unit") = 1.0,
      py::arg("balance_alpha_beta") = false);
+  m.def("select_plan", [](const I64Array& a, int servers, int gpus, std::vector<PlanKind> kinds, LinkModel inter, LinkModel intra, double mbpu,
+                          MatchPolicy match, ScalePolicy sp, int64_t split_align, bool transpose, bool balance_alpha_beta) {
+    PlanOptions o; o.match = match; o.scale_policy = sp; o.split_align = split_align; o.transpose = transpose;
+    o.inter = inter; o.intra = intra; o.mb_per_unit = mbpu; o.balance_alpha_beta = balance_alpha_beta;
+    PlanChoice c = select_plan(to_matrix(a), Topology{servers, gpus}, o, CostModel{inter, intra, mbpu}, kinds);
+    py::list table;
+    for (auto& kv : c.modeled_us) table.append(py::make_tuple(kv.first, kv.second));
+    return py::make_tuple(std::move(c.plan), table);
+  }, py::arg("matrix"), py::arg("servers"), py::arg("gpus"), py::arg("kinds"), py::arg("inter"), py::arg("intra"), py::arg("mb_per_unit") = 1.0,
+     py::arg("match") = MatchPolicy::kFirstFit, py::arg("scale_policy") = ScalePolicy::kNone, py::arg("split_align") = 1,
+     py::arg("transpose") = false, py::arg("balance_alpha_beta") = false);
   m.def("build_plan_time_us", [](const I64Array& a, int servers, int gpus, int reps) {
     Matrix mm = to_matrix(a);
     auto t0 = std::chrono::steady_clock::now();

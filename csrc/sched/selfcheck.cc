@@ -113,6 +113,16 @@ int main() {
         }
     }
   }
+  {  // the selector returns the cheapest candidate under the model and lists all of them
+    Matrix m = workload_zipf_rows(16, 1.2, 1 << 26, 3, 16);
+    CostModel cm; cm.mb_per_unit = 1e-6;
+    PlanChoice ch = select_plan(m, Topology{4, 4}, PlanOptions{}, cm, {PlanKind::kFanout, PlanKind::kStaged, PlanKind::kSingleBurst});
+    CHECK(ch.modeled_us.size() == 3, "selector table size");
+    double best = ch.modeled_us[0].second;
+    for (auto& kv : ch.modeled_us) best = std::min(best, kv.second);
+    CHECK(ch.cost.total_us == best && validate_plan(ch.plan).empty() && delivered_matrix(ch.plan) == ch.plan.matrix, "selector choice");
+    ++plans;
+  }
   std::printf("{\"selfcheck\":\"sched\",\"plans\":%d,\"failures\":%d}\n", plans, failures);
   return failures ? 1 : 0;
 }

@@ -81,8 +81,20 @@ int cmd_plan(const Args& a) {
   o.split_align = a.integer("align", 1);
   o.scale = a.integer("scale", 0);
   o.transpose = a.integer("transpose", 0);
+  const bool pick = a.str("kind", "staged") == "auto";  // let the cost model choose among the kinds
   const double t0 = now_us();
-  Plan p = build_plan(m, Topology{S, G}, o);
+  Plan p;
+  if (pick) {
+    std::vector<PlanKind> cand = {PlanKind::kFanout, PlanKind::kStaged};
+    if (G > 1) cand.push_back(PlanKind::kSingleBurst);
+    PlanChoice ch = select_plan(m, Topology{S, G}, o, cost_of(a, S), cand);
+    for (auto& kv : ch.modeled_us)
+      std::printf("{\"cmd\":\"plan\",\"candidate\":%d,\"modeled_us\":%.3f}\n", static_cast<int>(kv.first), kv.second);
+    p = std::move(ch.plan);
+    o.kind = p.opt.kind;
+  } else {
+    p = build_plan(m, Topology{S, G}, o);
+  }
   const double t1 = now_us();
   const std::string err = validate_plan(p);
   const bool exact = delivered_matrix(p) == p.matrix;
@@ -92,10 +104,10 @@ int cmd_plan(const Args& a) {
     if (q.src_buf == Buf::kInput) acc.at(q.origin, q.final_dst) += q.len;
   const bool stages_sum = acc == p.matrix;
   PlanCost c = model_cost(p, cost_of(a, S));
-  std::printf("{\"cmd\":\"plan\",\"servers\":%d,\"gpus\":%d,\"stages\":%d,\"ops\":%zu,\"valid\":%s,\"error\":\"%s\",\"delivered_exact\":%s,"
+  std::printf("{\"cmd\":\"plan\",\"kind\":%d,\"servers\":%d,\"gpus\":%d,\"stages\":%d,\"ops\":%zu,\"valid\":%s,\"error\":\"%s\",\"delivered_exact\":%s,"
               "\"stages_sum_to_matrix\":%s,\"decomposition_exact\":%s,\"line_sum\":%lld,\"max_line_sum_input\":%lld,\"scheduler_us\":%.2f,"
               "\"modeled_us\":%.3f,\"lower_bound_us\":%.3f,\"spread_out_us\":%.3f,\"speedup_vs_spread_out\":%.4f,\"bound_fraction\":%.4f}\n",
-              S, G, p.num_stages, p.ops.size(), err.empty() ? "true" : "false", err.c_str(), exact ? "true" : "false",
+              static_cast<int>(o.kind), S, G, p.num_stages, p.ops.size(), err.empty() ? "true" : "false", err.c_str(), exact ? "true" : "false",
               stages_sum ? "true" : "false", (o.kind != PlanKind::kStaged || verify_decomposition(p.decomp)) ? "true" : "false",
               static_cast<long long>(p.decomp.line_sum), static_cast<long long>(p.matrix.max_line_sum()), t1 - t0, c.total_us,
               c.lower_bound_us, c.spread_out_us, c.total_us > 0 ? c.spread_out_us / c.total_us : 0.0,

@@ -135,7 +135,9 @@ class Communicator:
         Every rank must pass the same matrix. Staged plans are built with pieces cut on 16-byte
         boundaries whenever the unit size allows it. ``verify=True`` first compares the matrix hash
         across the ranks (one small all-gather) and raises if they differ - ranks that plan different
-        collectives would wait for bytes that never come.
+        collectives would wait for bytes that never come. ``kind="auto"`` lets the cost model choose
+        between the fan-out and the staged plan (and the single-burst plan on a two-tier topology)
+        for this matrix and unit size, under the link model fitted to this fabric.
         """
         m = np.ascontiguousarray(matrix, dtype=np.int64)
         if verify and self.world > 1:
@@ -154,6 +156,8 @@ class Communicator:
         key = (sched.matrix_hash(m), unit_bytes, transpose, str(kind), chunk_bytes, tuple(sorted((k, str(v)) for k, v in plan_opts.items())))
         s = self._sched_cache.get(key)
         if s is None:
+            if kind == "auto":
+                plan_opts.setdefault("mb_per_unit", unit_bytes * 1e-6)
             plan = self.plan_cache.get(m, self.topo, kind=kind, transpose=transpose, **plan_opts)
             err = plan.validate()
             if err:

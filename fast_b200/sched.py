@@ -99,6 +99,24 @@ def build_plan(matrix, topo: Topology, kind=PlanKind.STAGED, match=MatchPolicy.F
                          inter or gbps_model(400.0, 0.7), intra or nvlink_model(900.0, 0.1), mb_per_unit, balance_alpha_beta)
 
 
+def select_plan(matrix, topo: Topology, inter: LinkModel, intra: LinkModel, mb_per_unit: float = 1.0, kinds=None,
+                match=MatchPolicy.FIRST_FIT, scale_policy=ScalePolicy.NONE, split_align: int = 1, transpose: bool = False,
+                balance_alpha_beta: bool = False):
+    """The plan kind the cost model expects to finish first, with the modeled time of every candidate.
+
+    Returns ``(plan, [(kind, modeled_us), ...])``. Default candidates: fan-out and staged on a flat
+    topology; fan-out, staged and the single-burst ablation on a two-tier one (ties go to the earlier
+    entry). Small or uniform traffic picks the fan-out, large skewed traffic over a slow tier the
+    permutation stages - the switch the reference leaves to the caller's choice of entry point.
+    """
+    if kinds is None:
+        kinds = [PlanKind.FANOUT, PlanKind.STAGED] if topo.gpus == 1 else [PlanKind.FANOUT, PlanKind.STAGED, PlanKind.SINGLE_BURST]
+    m = np.ascontiguousarray(matrix, dtype=np.int64)
+    plan, table = _S.select_plan(m, topo.servers, topo.gpus, list(kinds), inter, intra, mb_per_unit, match, scale_policy, split_align,
+                                 transpose, balance_alpha_beta)
+    return plan, list(table)
+
+
 class PlanCache:
     """Plans keyed by (matrix hash, topology, options): repeated traffic patterns skip the scheduler.
 
@@ -118,7 +136,12 @@ class PlanCache:
         p = self._d.get(key)
         if p is None:
             self.misses += 1
-            p = build_plan(m, topo, **opts)
+            if opts.get("kind") == "auto":
+                o = {k: v for k, v in opts.items() if k != "kind"}
+                nv = intra_link("B200_MEASURED")
+                p, _ = select_plan(m, topo, o.pop("inter", nv), o.pop("intra", nv), o.pop("mb_per_unit", 1.0), **o)
+            else:
+                p = build_plan(m, topo, **opts)
             if len(self._d) >= self.capacity:
                 self._d.pop(next(iter(self._d)))
             self._d[key] = p

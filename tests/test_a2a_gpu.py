@@ -39,7 +39,7 @@ def _expected_outputs(m, ins, unit_words):
 
 
 @pytest.mark.parametrize("servers,gpus", [(1, 1), (2, 1), (4, 1), (8, 1), (2, 2), (2, 4), (1, 4)])
-@pytest.mark.parametrize("kind", [PlanKind.STAGED, PlanKind.FANOUT, PlanKind.SPREAD_OUT, PlanKind.SINGLE_BURST])
+@pytest.mark.parametrize("kind", [PlanKind.STAGED, PlanKind.FANOUT, PlanKind.SPREAD_OUT, PlanKind.SINGLE_BURST, "auto"])
 def test_local_group_bit_exact(servers, gpus, kind):
     from fast_b200.parallel import LocalGroup
 

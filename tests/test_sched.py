@@ -330,3 +330,29 @@ def test_fitted_b200_link_model_tracks_the_measured_table():
             m = sched.workload_zipf_rows(8, skew, mib << 20, 1000 * mi + 7, 16)
             preds.append(sched.build_plan(m, Topology.flat(8), kind=PlanKind.FANOUT, split_align=16).cost(link, link, 1e-6)["total_us"])
         assert abs(np.mean(preds) * 1e-3 / ms - 1.0) < 0.12, (mib, skew, np.mean(preds) * 1e-3, ms)
+
+
+def test_select_plan_switches_between_fanout_and_stages():
+    """The cost-model selector: fan-out for small messages, permutation stages for large skewed
+    traffic over a slow tier; every chosen plan is sound and the table lists every candidate."""
+    inter, intra = sched.inter_link("ETHER400"), sched.intra_link("B100")
+    topo = Topology(4, 8)
+    small = sched.workload_zipf_rows(32, 1.2, 1 << 16, 7, 16)
+    big = sched.workload_zipf_rows(32, 1.2, 1 << 28, 7, 16)
+    p, table = sched.select_plan(small, topo, inter, intra, 1e-6)
+    assert p.kind == PlanKind.FANOUT and [k for k, _ in table] == [PlanKind.FANOUT, PlanKind.STAGED, PlanKind.SINGLE_BURST]
+    assert p.validate() == "" and (p.delivered_matrix() == small).all()
+    p, table = sched.select_plan(big, topo, inter, intra, 1e-6)
+    cost = dict(table)
+    assert p.kind == PlanKind.STAGED and cost[PlanKind.STAGED] < cost[PlanKind.SINGLE_BURST] < cost[PlanKind.FANOUT]
+    assert p.validate() == "" and (p.delivered_matrix() == big).all()
+    assert abs(p.cost(inter, intra, 1e-6)["total_us"] - cost[PlanKind.STAGED]) < 1e-6
+    # explicit candidates, transposed collective, one NVSwitch domain: the fan-out wins at every size
+    nv = sched.intra_link("B200_MEASURED")
+    p, table = sched.select_plan(big[:8, :8], Topology.flat(8), nv, nv, 1e-6, kinds=[PlanKind.STAGED, PlanKind.FANOUT], transpose=True)
+    assert p.kind == PlanKind.FANOUT and (p.delivered_matrix() == big[:8, :8].T).all()
+    cache = sched.PlanCache()
+    q = cache.get(big[:8, :8], Topology.flat(8), kind="auto", mb_per_unit=1e-6)
+    assert q.kind == PlanKind.FANOUT and cache.get(big[:8, :8], Topology.flat(8), kind="auto", mb_per_unit=1e-6) is q and cache.hits == 1
+    with pytest.raises(Exception):
+        sched.select_plan(small, topo, inter, intra, 1e-6, kinds=[])
