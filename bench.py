@@ -88,8 +88,9 @@ class ClockSampler:
 
 def reference_arm(args):
     """The reference's own build cannot run this metric here; say why in one line and exit 0."""
-    why = ("reference (MangoBoost/FAST) has no setup.py/pyproject at its root, so the offline pip install fails; its NVIDIA tree needs an NVSHMEM "
-           "CMake package and sm_90a, exports only self-tests, is a no-op on one server, and contains no MoE layer, GEMM or training step to time")
+    why = ("reference (MangoBoost/FAST) has no setup.py/pyproject at its root, so the offline pip install fails; its NVIDIA library does build "
+           "for sm_100a with a hand-written nvcc line (baseline/build_ref_nvshmem.sh) but exports only all-to-all self-tests on a self-generated "
+           "workload, is a no-op on one server, and contains no MoE layer, GEMM or training step to time")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
