@@ -57,10 +57,11 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
     for (size_t k = 0; k < ops.size(); ++k) {
       const int64_t total = ops[k]->len * ub;
       const int64_t c = chunk_of(total);
-      const int64_t n = (total + c - 1) / c;
-      for (int64_t j = 0; j < n; ++j) slices.push_back(Slice{(static_cast<double>(j) + 0.5) / static_cast<double>(n), k, j * c, std::min(c, total - j * c)});
+      const int64_t pieces = (total + c - 1) / c;
+      for (int64_t j = 0; j < pieces; ++j)
+        slices.push_back(Slice{(static_cast<double>(j) + 0.5) / static_cast<double>(pieces), k, j * c, std::min(c, total - j * c)});
     }
-    std::stable_sort(slices.begin(), slices.end(), [](const Slice& a, const Slice& b) { return a.key < b.key; });
+    std::stable_sort(slices.begin(), slices.end(), [](const Slice& x, const Slice& y) { return x.key < y.key; });
     for (const Slice& sl : slices) {
       const Op& o = *ops[sl.op];
       WorkItem w{};

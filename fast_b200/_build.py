@@ -5,7 +5,6 @@ Everything is compiled with explicit commands into the source tree (``fast_b200/
 """
 from __future__ import annotations
 
-import hashlib
 import os
 import subprocess
 import sys

@@ -8,7 +8,7 @@ exposes self-tests (nvidia/alltoall_nvshmem.cpp:508-601); this one is a general 
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import numpy as np

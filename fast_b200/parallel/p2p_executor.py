@@ -9,7 +9,7 @@ executor that runs on CPU-only machines.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import numpy as np
 import torch

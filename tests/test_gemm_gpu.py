@@ -118,7 +118,6 @@ def test_dgrad_with_fused_swiglu_backward(kernel_variant):
     """dgrad of the second projection with the SwiGLU backward applied in its epilogue."""
     if kernel_variant != "cta_pair":
         pytest.skip("only the CTA-pair kernel carries this epilogue")
-    from fast_b200.models.moe import split_gate_up
     from fast_b200.ops import gemm
 
     G, H, I = 2, 256, 512
