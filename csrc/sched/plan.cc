@@ -161,22 +161,29 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
 
   std::vector<int> last_stage_of_pair(static_cast<size_t>(S) * S, -1);
   
+  const int K = static_cast<int>(stages.size());
+  // Rail and redistribution ops are collected per stage and concatenated at the end, so that the
+  // final list is [balance][intrinsic][rail 0][redis 0][rail 1][redis 1]...
+  std::vector<std::vector<Op>> rail_of_stage(K), redis_of_stage(K);
+
   auto emit_rail = [&](int k, int s, int t, int i, int64_t budget) {
     auto& q = hold_at(s, t, i);
+    if (q.empty()) return;
     const int src_rank = s * G + i, dst_rank = t * G + i;
-    std::vector<Op> redis;
+    std::vector<Op>& rail = rail_of_stage[k];
+    std::vector<Op>& redis = redis_of_stage[k];
     while (!q.empty() && budget != 0) {
       Piece& pc = q.front();
       const int64_t take = budget < 0 ? pc.len : aligned_cut(pc, budget, opt.split_align);
       if (take == 0) break;
       const int origin = s * G + pc.origin_local, fin = t * G + pc.final_local;
       if (pc.final_local == i) {
-        p.ops.push_back(Op{Phase::kRail, pc.buf, Buf::kOutput, k, src_rank, dst_rank, origin, fin, pc.off,
-                           out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
+        rail.push_back(Op{Phase::kRail, pc.buf, Buf::kOutput, k, src_rank, dst_rank, origin, fin, pc.off,
+                          out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
       } else {
         int64_t& cursor = p.buffers[dst_rank].rail_units;
-        p.ops.push_back(Op{Phase::kRail, pc.buf, Buf::kRail, k, src_rank, dst_rank, origin, fin, pc.off, cursor,
-                           take, pc.pair_off});
+        rail.push_back(Op{Phase::kRail, pc.buf, Buf::kRail, k, src_rank, dst_rank, origin, fin, pc.off, cursor,
+                          take, pc.pair_off});
         redis.push_back(Op{Phase::kRedistribute, Buf::kRail, Buf::kOutput, k, dst_rank, fin, origin, fin, cursor,
                            out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
         cursor += take;
@@ -185,37 +192,22 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
       if (take == pc.len) q.pop_front();
       else { pc.pair_off += take; pc.off += take; pc.len -= take; }
     }
-    return redis;
   };
 
-  const int K = static_cast<int>(stages.size());
-  std::vector<std::vector<Op>> redis_of_stage(K);
-  // Rail ops are appended stage by stage; redistribution ops are kept aside and merged after,
-  // so that the final list is [balance][intrinsic][rail 0][redis 0][rail 1][redis 1]...
-  std::vector<std::vector<Op>> rail_of_stage(K);
   for (int k = 0; k < K; ++k) {
-    const size_t mark = p.ops.size();
     for (int s = 0; s < S; ++s) {
       if (opt.kind == PlanKind::kStaged) {
         const int t = stages[k].to[s];
         if (t == s) continue;
         last_stage_of_pair[static_cast<size_t>(s) * S + t] = k;
-        for (int i = 0; i < G; ++i) {
-          auto r = emit_rail(k, s, t, i, stages[k].weight);
-          redis_of_stage[k].insert(redis_of_stage[k].end(), r.begin(), r.end());
-        }
+        for (int i = 0; i < G; ++i) emit_rail(k, s, t, i, stages[k].weight);
       } else {
         for (int step = 1; step < S; ++step) {
           const int t = (s + step) % S;
-          for (int i = 0; i < G; ++i) {
-            auto r = emit_rail(k, s, t, i, -1);
-            redis_of_stage[k].insert(redis_of_stage[k].end(), r.begin(), r.end());
-          }
+          for (int i = 0; i < G; ++i) emit_rail(k, s, t, i, -1);
         }
       }
     }
-    rail_of_stage[k].assign(p.ops.begin() + static_cast<std::ptrdiff_t>(mark), p.ops.end());
-    p.ops.resize(mark);
   }
   // Alignment can leave a few units behind a stage budget; ship them with the pair's last stage.
   if (opt.kind == PlanKind::kStaged) {
@@ -226,17 +218,18 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
           if (hold_at(s, t, i).empty()) continue;
           const int k = last_stage_of_pair[static_cast<size_t>(s) * S + t];
           if (k < 0) throw std::logic_error("build_plan: traffic left without a stage");
-          const size_t mark = p.ops.size();
-          auto r = emit_rail(k, s, t, i, -1);
-          rail_of_stage[k].insert(rail_of_stage[k].end(), p.ops.begin() + static_cast<std::ptrdiff_t>(mark), p.ops.end());
-          p.ops.resize(mark);
-          redis_of_stage[k].insert(redis_of_stage[k].end(), r.begin(), r.end());
+          emit_rail(k, s, t, i, -1);
         }
       }
   }
+  size_t total = p.ops.size();
+  for (int k = 0; k < K; ++k) total += rail_of_stage[k].size() + redis_of_stage[k].size();
+  p.ops.reserve(total);
   for (int k = 0; k < K; ++k) {
     p.ops.insert(p.ops.end(), rail_of_stage[k].begin(), rail_of_stage[k].end());
     p.ops.insert(p.ops.end(), redis_of_stage[k].begin(), redis_of_stage[k].end());
+    std::vector<Op>().swap(rail_of_stage[k]);
+    std::vector<Op>().swap(redis_of_stage[k]);
   }
   p.num_stages = K;
   return p;
