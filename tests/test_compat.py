@@ -153,3 +153,10 @@ def test_named_configs_and_memory_plan():
     assert not memory_plan(mx.with_(tokens_per_rank=t + 1024), 8)["fits_b200"]
     f = flops_per_step(mx, 8)
     assert f["expert_gemm_total"] == 3 * f["expert_gemm_fwd"] == 3 * 2.0 * 65536 * 4096 * 14336 * 3
+
+
+def test_init_id_stand_in_has_the_reference_shape():
+    from fast_b200.compat import get_nvshmem_init_id
+
+    uid = get_nvshmem_init_id()
+    assert uid.dtype == torch.uint8 and uid.numel() == 128 and uid.device.type == "cpu"
