@@ -1,9 +1,7 @@
 // Plan validation and host replay (the CPU oracle for every executor).
 #include <algorithm>
 #include <cstring>
-#include <map>
 #include <sstream>
-#include <tuple>
 
 #include "plan.h"
 
@@ -36,9 +34,12 @@ std::string validate_plan(const Plan& p) {
   const int n = p.matrix.n, G = p.topo.gpus, S = p.topo.servers;
   std::ostringstream err;
   if (static_cast<int>(p.buffers.size()) != n) return "buffers: wrong rank count";
-  std::map<std::pair<int, int>, std::vector<Interval>> delivered;           // (origin, final) -> segment intervals
-  std::map<std::tuple<int, int>, std::vector<Interval>> staged_w, staged_r;  // (rank, buf) -> intervals
-  std::map<int, std::map<int, int>> stage_map, stage_rev;                    // stage -> src server -> dst server
+  // Flat tables instead of maps: validation runs on every new plan, and a 512-rank plan has millions of ops.
+  std::vector<std::vector<Interval>> delivered(static_cast<size_t>(n) * n);  // origin * n + final -> segment intervals
+  std::vector<std::vector<Interval>> staged_w(static_cast<size_t>(n) * 2), staged_r(static_cast<size_t>(n) * 2);  // rank * 2 + (rail ? 1 : 0)
+  const size_t stage_cells = p.opt.kind == PlanKind::kStaged ? static_cast<size_t>(std::max(p.num_stages, 0)) * S : 0;
+  std::vector<int> stage_to(stage_cells, -1), stage_from(stage_cells, -1);   // stage * S + server -> peer server
+  auto staging_slot = [](int rank, Buf b) { return static_cast<size_t>(rank) * 2 + (b == Buf::kRail ? 1 : 0); };
 
   for (size_t k = 0; k < p.ops.size(); ++k) {
     const Op& o = p.ops[k];
@@ -58,45 +59,41 @@ std::string validate_plan(const Plan& p) {
       if (o.src_rank % G != o.dst_rank % G) return bad("rail op is not rail-aligned");
       if (o.stage < 0 || o.stage >= p.num_stages) return bad("stage out of range");
       if (p.opt.kind == PlanKind::kStaged) {
-        auto& fwd = stage_map[o.stage];
-        auto& rev = stage_rev[o.stage];
-        if (fwd.count(ss) && fwd[ss] != ds) return bad("server sends to two servers in one stage");
-        if (rev.count(ds) && rev[ds] != ss) return bad("server receives from two servers in one stage");
-        fwd[ss] = ds; rev[ds] = ss;
+        int& to = stage_to[static_cast<size_t>(o.stage) * S + ss];
+        int& from = stage_from[static_cast<size_t>(o.stage) * S + ds];
+        if (to >= 0 && to != ds) return bad("server sends to two servers in one stage");
+        if (from >= 0 && from != ss) return bad("server receives from two servers in one stage");
+        to = ds; from = ss;
       }
     }
     if (o.src_buf == Buf::kInput) {
       if (o.src_rank != o.origin) return bad("input read on a rank that is not the origin");
       if (o.src_off != p.in_disp[static_cast<size_t>(o.origin) * n + o.final_dst] + o.pair_off) return bad("input offset does not match the pair segment");
     } else {
-      staged_r[{o.src_rank, static_cast<int>(o.src_buf)}].push_back({o.src_off, o.src_off + o.len});
+      staged_r[staging_slot(o.src_rank, o.src_buf)].push_back({o.src_off, o.src_off + o.len});
     }
     if (o.dst_buf == Buf::kOutput) {
       if (o.dst_rank != o.final_dst) return bad("output written on a rank that is not the final destination");
       if (o.dst_off != p.out_disp[static_cast<size_t>(o.final_dst) * n + o.origin] + o.pair_off) return bad("output offset does not match the pair segment");
-      delivered[{o.origin, o.final_dst}].push_back({o.pair_off, o.pair_off + o.len});
+      delivered[static_cast<size_t>(o.origin) * n + o.final_dst].push_back({o.pair_off, o.pair_off + o.len});
     } else {
-      staged_w[{o.dst_rank, static_cast<int>(o.dst_buf)}].push_back({o.dst_off, o.dst_off + o.len});
+      staged_w[staging_slot(o.dst_rank, o.dst_buf)].push_back({o.dst_off, o.dst_off + o.len});
     }
   }
   for (int i = 0; i < n; ++i)
     for (int j = 0; j < n; ++j) {
-      auto it = delivered.find({i, j});
-      std::vector<Interval> none;
-      std::string r = tiles_exactly(it == delivered.end() ? none : it->second, p.matrix.at(i, j));
+      std::string r = tiles_exactly(delivered[static_cast<size_t>(i) * n + j], p.matrix.at(i, j));
       if (!r.empty()) { err << "pair " << i << "->" << j << ": delivery has a " << r; return err.str(); }
     }
   for (int r = 0; r < n; ++r)
     for (Buf b : {Buf::kBalance, Buf::kRail}) {
-      auto key = std::make_tuple(r, static_cast<int>(b));
-      std::vector<Interval> w = staged_w[key], rd = staged_r[key];
+      std::vector<Interval>&w = staged_w[staging_slot(r, b)], &rd = staged_r[staging_slot(r, b)];
       std::string a = tiles_exactly(w, buf_units(p.buffers[r], b));
       if (!a.empty()) { err << "rank " << r << " staging " << static_cast<int>(b) << ": writes have a " << a; return err.str(); }
       // Reads may split a written piece, but together they must cover the same bytes once.
       a = tiles_exactly(rd, buf_units(p.buffers[r], b));
       if (!a.empty()) { err << "rank " << r << " staging " << static_cast<int>(b) << ": forwards have a " << a; return err.str(); }
     }
-  (void)S;
   return "";
 }
 
