@@ -128,6 +128,22 @@ PYBIND11_MODULE(_sched, m) {
         }
         return a; })
       .def("validate", &validate_plan)
+      .def("tampered", [](const Plan& p, int64_t op, const std::string& field, int64_t value) {
+        // A copy with one op damaged, for tests of the validator and of the executors' checks.
+        Plan q = p;
+        if (op < 0 || op >= static_cast<int64_t>(q.ops.size())) throw std::out_of_range("tampered: op index");
+        Op& o = q.ops[static_cast<size_t>(op)];
+        if (field == "drop") q.ops.erase(q.ops.begin() + op);
+        else if (field == "duplicate") q.ops.push_back(o);
+        else if (field == "len") o.len = value;
+        else if (field == "src_off") o.src_off = value;
+        else if (field == "dst_off") o.dst_off = value;
+        else if (field == "pair_off") o.pair_off = value;
+        else if (field == "src_rank") o.src_rank = static_cast<int32_t>(value);
+        else if (field == "dst_rank") o.dst_rank = static_cast<int32_t>(value);
+        else if (field == "stage") o.stage = static_cast<int32_t>(value);
+        else throw std::invalid_argument("tampered: field");
+        return q; }, py::arg("op"), py::arg("field"), py::arg("value") = 0)
       .def("delivered_matrix", [](const Plan& p) { return from_matrix(delivered_matrix(p)); })
       .def("stage_matrix", [](const Plan& p, int k) { return from_matrix(stage_matrix(p, k)); })
       .def("to_json", &plan_to_json, py::arg("include_ops") = true)

@@ -356,3 +356,45 @@ def test_select_plan_switches_between_fanout_and_stages():
     assert q.kind == PlanKind.FANOUT and cache.get(big[:8, :8], Topology.flat(8), kind="auto", mb_per_unit=1e-6) is q and cache.hits == 1
     with pytest.raises(Exception):
         sched.select_plan(small, topo, inter, intra, 1e-6, kinds=[])
+
+
+def test_validator_rejects_damaged_plans():
+    """Every kind of damage to a sound plan is named by the validator (it is the gate in front of
+    every upload to a GPU): lost, duplicated, shifted, oversized, misrouted and mis-staged ops."""
+    m = sched.workload_zipf_rows(8, 1.0, 4096, 5, 1)
+    p = sched.build_plan(m, Topology(2, 4))
+    assert p.validate() == ""
+    ops = p.ops
+    rail = int(np.flatnonzero(ops[:, 0] == sched.PHASE_RAIL)[0])
+    staged = int(np.flatnonzero((ops[:, 0] == sched.PHASE_RAIL) & (ops[:, 5] == sched.BUF_RAIL))[0])
+    bal = int(np.flatnonzero(ops[:, 0] == sched.PHASE_BALANCE)[0])
+    out = int(np.flatnonzero(ops[:, 5] == sched.BUF_OUTPUT)[0])
+    cases = [
+        (out, "drop", 0, "delivery has a"),                       # a lost message
+        (out, "duplicate", 0, "overlap"),                         # delivered twice
+        (out, "len", 0, "non-positive length"),
+        (out, "len", int(ops[out, 8]) + 1, "outside"),           # longer than its pair segment / buffer
+        (out, "dst_off", int(ops[out, 7]) + 1, "output offset does not match"),
+        (out, "src_off", 1 << 40, "source range outside its buffer"),
+        (out, "dst_rank", 99, "rank out of range"),
+        (out, "pair_off", -1, "piece outside its pair segment"),
+        (staged, "dst_off", int(ops[staged, 7]) + 1, "staging"),  # staged bytes no longer tile the staging area
+        (staged, "drop", 0, "a gap"),                             # staged piece never arrives: its forward reads a hole
+        (bal, "dst_rank", (int(ops[bal, 3]) + 4) % 8, "crosses servers"),
+        (rail, "stage", p.num_stages + 3, "stage out of range"),
+        (rail, "dst_rank", int(ops[rail, 3]) ^ 1, "rail"),        # no longer rail-aligned / wrong final rank
+    ]
+    for op, field, value, needle in cases:
+        err = p.tampered(op, field, value).validate()
+        assert err != "" and needle in err, (op, field, value, err)
+    # a server that talks to two servers in one stage (needs three servers)
+    m3 = sched.workload_uniform(6, 500, 11, True)
+    p3 = sched.build_plan(m3, Topology(3, 2))
+    o3 = p3.ops
+    rails = [int(i) for i in np.flatnonzero(o3[:, 0] == sched.PHASE_RAIL)]
+    a = rails[0]
+    b = next(i for i in rails if o3[i, 2] // 2 == o3[a, 2] // 2 and o3[i, 3] // 2 != o3[a, 3] // 2)
+    assert p3.validate() == "" and "in one stage" in p3.tampered(b, "stage", int(o3[a, 1])).validate()
+    with pytest.raises(Exception):
+        p.tampered(10**9, "len", 1)
+    assert p.validate() == ""                                      # the original is untouched
