@@ -33,7 +33,12 @@ std::string tiles_exactly(std::vector<Interval>& iv, int64_t total) {
 std::string validate_plan(const Plan& p) {
   const int n = p.matrix.n, G = p.topo.gpus, S = p.topo.servers;
   std::ostringstream err;
+  // Structure first (a plan may come from a file): everything below indexes by these sizes.
+  if (n < 0 || G < 1 || S < 1 || static_cast<int64_t>(S) * G != n) return "topology does not match the matrix";
   if (static_cast<int>(p.buffers.size()) != n) return "buffers: wrong rank count";
+  if (p.in_disp.size() != static_cast<size_t>(n) * n || p.out_disp.size() != static_cast<size_t>(n) * n) return "displacement tables: wrong size";
+  if (p.matrix.v.size() != static_cast<size_t>(n) * n) return "matrix: wrong size";
+  if (p.num_stages < 0) return "negative stage count";
   // Flat tables instead of maps: validation runs on every new plan, and a 512-rank plan has millions of ops.
   std::vector<std::vector<Interval>> delivered(static_cast<size_t>(n) * n);  // origin * n + final -> segment intervals
   std::vector<std::vector<Interval>> staged_w(static_cast<size_t>(n) * 2), staged_r(static_cast<size_t>(n) * 2);  // rank * 2 + (rail ? 1 : 0)
@@ -45,6 +50,7 @@ std::string validate_plan(const Plan& p) {
     const Op& o = p.ops[k];
     auto bad = [&](const char* what) { err << "op " << k << ": " << what; return err.str(); };
     if (o.len <= 0) return bad("non-positive length");
+    if (static_cast<unsigned>(o.phase) > 3u || static_cast<unsigned>(o.src_buf) > 3u || static_cast<unsigned>(o.dst_buf) > 3u) return bad("unknown phase or buffer");
     if (o.src_rank < 0 || o.src_rank >= n || o.dst_rank < 0 || o.dst_rank >= n) return bad("rank out of range");
     if (o.origin < 0 || o.origin >= n || o.final_dst < 0 || o.final_dst >= n) return bad("pair out of range");
     if (o.src_off < 0 || o.src_off + o.len > buf_units(p.buffers[o.src_rank], o.src_buf)) return bad("source range outside its buffer");

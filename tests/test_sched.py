@@ -398,3 +398,39 @@ def test_validator_rejects_damaged_plans():
     with pytest.raises(Exception):
         p.tampered(10**9, "len", 1)
     assert p.validate() == ""                                      # the original is untouched
+
+
+def test_damaged_plan_files_are_rejected_not_trusted():
+    """A plan read back from bytes that were cut or altered either fails to parse, fails validation
+    or is still a sound plan for its matrix; it never reaches an executor in a broken state."""
+    import struct
+
+    m = sched.workload_uniform(8, 100, 1, True)
+    p = sched.build_plan(m, Topology(2, 4))
+    blob = p.to_bytes()
+    for cut in (0, 3, 8, 100, len(blob) // 2, len(blob) - 1):
+        with pytest.raises(ValueError):
+            sched.Plan.from_bytes(blob[:cut])
+    rng = np.random.default_rng(0)
+    outcomes = {"raised": 0, "invalid": 0, "sound": 0}
+    for trial in range(300):
+        b = bytearray(blob)
+        pos = int(rng.integers(0, len(b) - 8))
+        if trial % 3 == 0:
+            b[pos:pos + 8] = struct.pack("<q", int(rng.integers(-(1 << 62), 1 << 62)))
+        elif trial % 3 == 1:
+            b[pos] ^= 1 << int(rng.integers(0, 8))
+        else:
+            b[pos:pos + 4] = struct.pack("<i", int(rng.integers(-5, 5)))
+        try:
+            q = sched.Plan.from_bytes(bytes(b))
+        except ValueError:
+            outcomes["raised"] += 1
+            continue
+        err = q.validate()
+        if err:
+            outcomes["invalid"] += 1
+        else:
+            outcomes["sound"] += 1
+            assert (q.delivered_matrix() == q.matrix).all()
+    assert outcomes["invalid"] > 50 and outcomes["raised"] + outcomes["invalid"] + outcomes["sound"] == 300
