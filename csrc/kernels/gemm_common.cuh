@@ -2,47 +2,14 @@
 #pragma once
 #include "api.h"
 #include "sm100_ptx.cuh"
+#include "tile_walker.h"
 
 namespace fastb {
 namespace gemm {
 
 constexpr int BN = 256, BK = 64, UMMA_K = 16;
 
-struct TileCoord {
-  int g, m_idx, n_idx;   // group, tile row inside the group (of the fixed dim for wgrad), tile column
-  int row0;              // first row of the group in the grouped matrix
-  int red_blocks;        // BK steps of the reduction
-};
-
-// Walks the tile space group by group; inside a group, in bands of kBandRows rows: all column tiles
-// of a band are visited (m fastest inside the band) before the next band starts. The tiles that
-// run at the same time then form a roughly square patch of the output, which minimises the
-// operand bytes a wave pulls from DRAM (a wave of p x q tiles reads p A-panels and q B-panels).
-// TILE_M is 128 (one CTA) or 256 (CTA pair).
-constexpr int kDefaultBandRows = 4096;
-template <int TILE_M>
-struct TileWalker {
-  const int* off; int G, tiles_n, fixed_m, red_len; GemmMode mode; int band_rows;
-  int g = 0, base = 0;
-  __device__ bool locate(int tile, TileCoord& c) {
-    while (g < G) {
-      const int r0 = off[g], r1 = off[g + 1];
-      const int mt = mode == GemmMode::kWgrad ? fixed_m : (r1 - r0) / TILE_M;
-      const int cnt = mt * tiles_n;
-      if (tile < base + cnt) {
-        const int local = tile - base;
-        const int kBand = max(1, (band_rows > 0 ? band_rows : kDefaultBandRows) / TILE_M);
-        const int band = local / (kBand * tiles_n), rem = local % (kBand * tiles_n);
-        const int m0 = band * kBand, cur = min(kBand, mt - m0);
-        c.g = g; c.n_idx = rem / cur; c.m_idx = m0 + rem % cur; c.row0 = r0;
-        c.red_blocks = mode == GemmMode::kWgrad ? (r1 - r0) / BK : red_len / BK;
-        return true;
-      }
-      base += cnt; ++g;
-    }
-    return false;
-  }
-};
+static_assert(BK == kWalkBK, "the tile walker counts reduction steps of BK");
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);

@@ -65,7 +65,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
 
-  TileWalker<BM> walk{p.group_off, p.num_groups, p.tiles_n, p.fixed_m_tiles, p.red_len, MODE, p.band_rows};
+  TileWalker<BM> walk{p.group_off, p.num_groups, p.tiles_n, p.fixed_m_tiles, p.red_len, MODE == GemmMode::kWgrad, p.band_rows};
   TileCoord tc;
 
   if (warp == 0) {

@@ -71,7 +71,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   volatile int* abort_flag = &ctl->abort_flag;
 
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-  TileWalker<TILE_M> walk{p.group_off, p.num_groups, p.tiles_n, p.fixed_m_tiles, p.red_len, MODE, p.band_rows};
+  TileWalker<TILE_M> walk{p.group_off, p.num_groups, p.tiles_n, p.fixed_m_tiles, p.red_len, MODE == GemmMode::kWgrad, p.band_rows};
   TileCoord tc;
 
   if (warp == 0) {

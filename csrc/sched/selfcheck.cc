@@ -6,6 +6,7 @@
 #include <cstring>
 #include <vector>
 
+#include "../kernels/tile_walker.h"
 #include "../runtime/range_allocator.h"
 #include "plan.h"
 
@@ -76,8 +77,53 @@ static void allocator_check() {
   CHECK(threw, "over-capacity request must be refused");
 }
 
+// The grouped GEMMs' tile enumeration: every role of every CTA steps its own walker by the grid
+// stride; together they must visit every tile of every group exactly once, in bands, with the
+// right reduction length, and stop after the last tile.
+template <int TILE_M>
+static void walker_check() {
+  using fastb::gemm::TileCoord;
+  using fastb::gemm::TileWalker;
+  uint64_t x = 0x9e3779b97f4a7c15ull + TILE_M;
+  auto rnd = [&](int m) { x ^= x << 13; x ^= x >> 7; x ^= x << 17; return static_cast<int>(x % static_cast<uint64_t>(m)); };
+  for (int trial = 0; trial < 400; ++trial) {
+    const int G = 1 + rnd(9), tiles_n = 1 + rnd(7), fixed_m = 1 + rnd(5), stride = 1 + rnd(40);
+    const bool wgrad = trial % 3 == 2;
+    const int band_rows = trial % 4 == 0 ? 0 : TILE_M * (1 + rnd(6));
+    std::vector<int> off(G + 1, 0);
+    for (int g = 0; g < G; ++g) off[g + 1] = off[g] + (rnd(4) == 0 ? 0 : TILE_M * (1 + rnd(40)));  // empty groups included
+    const int red_len = 64 * (1 + rnd(8));
+    long long want = 0;
+    std::vector<long long> first(G + 1, 0);
+    for (int g = 0; g < G; ++g) { first[g] = want; want += static_cast<long long>(wgrad ? fixed_m : (off[g + 1] - off[g]) / TILE_M) * tiles_n; }
+    std::vector<int> seen(static_cast<size_t>(want), 0);
+    for (int cta = 0; cta < stride; ++cta) {
+      TileWalker<TILE_M> w{off.data(), G, tiles_n, fixed_m, red_len, wgrad, band_rows};
+      TileCoord c{};
+      int tile = cta;
+      for (; w.locate(tile, c); tile += stride) {
+        const int mt = wgrad ? fixed_m : (off[c.g + 1] - off[c.g]) / TILE_M;
+        CHECK(c.g >= 0 && c.g < G && c.m_idx >= 0 && c.m_idx < mt && c.n_idx >= 0 && c.n_idx < tiles_n, "walker: coordinate out of range");
+        CHECK(c.row0 == off[c.g], "walker: row0");
+        CHECK(c.red_blocks == (wgrad ? (off[c.g + 1] - off[c.g]) / 64 : red_len / 64), "walker: reduction length");
+        const long long id = first[c.g] + static_cast<long long>(c.m_idx) * tiles_n + c.n_idx;
+        CHECK(id >= 0 && id < want, "walker: tile id");
+        if (id >= 0 && id < want) ++seen[static_cast<size_t>(id)];
+        // Band order: tiles of a band come before tiles of the next band of the same group.
+        const int kb = (band_rows > 0 ? band_rows : fastb::gemm::kDefaultBandRows) / TILE_M > 1 ? (band_rows > 0 ? band_rows : fastb::gemm::kDefaultBandRows) / TILE_M : 1;
+        const long long local = tile - first[c.g];
+        CHECK(c.m_idx / kb == local / (static_cast<long long>(kb) * tiles_n), "walker: band order");
+      }
+      CHECK(tile >= want, "walker: stopped early");
+    }
+    for (long long i = 0; i < want; ++i) CHECK(seen[static_cast<size_t>(i)] == 1, "walker: tile %lld visited %d times", i, seen[static_cast<size_t>(i)]);
+  }
+}
+
 int main() {
   allocator_check();
+  walker_check<128>();
+  walker_check<256>();
   const int topo[][2] = {{1, 1}, {1, 4}, {4, 1}, {2, 2}, {2, 4}, {3, 3}, {8, 1}, {4, 2}};
   const PlanKind kinds[] = {PlanKind::kStaged, PlanKind::kSingleBurst, PlanKind::kFanout, PlanKind::kSpreadOut};
   int plans = 0;

@@ -65,7 +65,7 @@ def build_selfcheck(force=False):
     out = ROOT / "build" / "fastb-selfcheck"
     out.parent.mkdir(exist_ok=True)
     srcs = [CSRC / "sched" / "selfcheck.cc"] + [CSRC / "sched" / f"{s}.cc" for s in SCHED_SRCS]
-    if force or _stale(out, srcs + _headers("sched") + _headers("runtime")):
+    if force or _stale(out, srcs + _headers("sched") + _headers("runtime") + [CSRC / "kernels" / "tile_walker.h"]):
         _run(["g++", "-std=c++17", "-O2", "-Wall", *srcs, "-o", out])
     return out
 
