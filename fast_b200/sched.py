@@ -161,3 +161,92 @@ class PlanCache:
         with open(path, "rb") as f:
             for k, b in pickle.load(f).items():
                 self._d[k] = Plan.from_bytes(b)
+
+
+@dataclass(frozen=True)
+class TrafficMatrix:
+    """An ``n x n`` demand matrix with its unit size: ``units[i, j]`` = units rank ``i`` sends to
+    rank ``j`` (the reference's ``workload`` argument, in tokens; amd/flash.cpp:400-420), and what
+    the planner and the benchmarks want to know about it before anything runs."""
+
+    units: np.ndarray
+    unit_bytes: int = 1
+
+    def __post_init__(self):
+        m = np.ascontiguousarray(self.units, dtype=np.int64)
+        if m.ndim != 2 or m.shape[0] != m.shape[1] or (m < 0).any() or self.unit_bytes < 1:
+            raise ValueError("TrafficMatrix: square non-negative matrix and a positive unit size")
+        object.__setattr__(self, "units", m)
+
+    # ---- constructors ---------------------------------------------------------------------------
+    @staticmethod
+    def from_splits(rows, unit_bytes: int = 1) -> "TrafficMatrix":
+        """``rows[i]`` = the ``input_split_sizes`` of rank ``i`` (what an all-gather of every rank's
+        splits yields)."""
+        return TrafficMatrix(np.stack([np.asarray(r, dtype=np.int64) for r in rows]), unit_bytes)
+
+    @staticmethod
+    def from_tokens(tokens, hidden: int, element_bytes: int) -> "TrafficMatrix":
+        return TrafficMatrix(tokens, hidden * element_bytes)
+
+    @staticmethod
+    def zipf(n: int, skew: float, row_bytes: int, seed: int, quantum: int = 16) -> "TrafficMatrix":
+        return TrafficMatrix(workload_zipf_rows(n, skew, row_bytes, seed, quantum), 1)
+
+    @staticmethod
+    def uniform(n: int, bytes_per_pair: int, zero_diag: bool = False) -> "TrafficMatrix":
+        return TrafficMatrix(workload_balanced(n, bytes_per_pair, zero_diag), 1)
+
+    # ---- views ----------------------------------------------------------------------------------
+    @property
+    def n(self) -> int:
+        return int(self.units.shape[0])
+
+    @property
+    def bytes(self) -> np.ndarray:
+        return self.units * self.unit_bytes
+
+    def transposed(self) -> "TrafficMatrix":
+        """The reverse collective (combine / backward of dispatch)."""
+        return TrafficMatrix(self.units.T.copy(), self.unit_bytes)
+
+    def input_splits(self, rank: int):
+        return [int(x) for x in self.units[rank]]
+
+    def output_splits(self, rank: int):
+        return [int(x) for x in self.units[:, rank]]
+
+    def hash(self) -> int:
+        return matrix_hash(self.units)
+
+    # ---- bounds and shape -------------------------------------------------------------------------
+    def port_bound_bytes(self) -> int:
+        """Bytes through the busiest port: max over ranks of what leaves and what enters a GPU,
+        self traffic excluded. Completion time can not be below this over the port bandwidth."""
+        b = self.bytes
+        off = b - np.diag(np.diag(b))
+        return int(max(off.sum(1).max(initial=0), off.sum(0).max(initial=0)))
+
+    def lower_bound_us(self, gbytes_per_s: float = 770.0) -> float:
+        return self.port_bound_bytes() / (gbytes_per_s * 1e3)
+
+    def imbalance(self) -> float:
+        """Busiest port over the mean port load (1.0 = perfectly even)."""
+        b = self.bytes
+        off = b - np.diag(np.diag(b))
+        mean = off.sum() / max(self.n, 1)
+        return float(self.port_bound_bytes() / mean) if mean > 0 else 1.0
+
+    def server_view(self, topo: "Topology") -> np.ndarray:
+        """``S x S`` bytes between servers (diagonal = traffic that stays inside a server)."""
+        if topo.ranks != self.n:
+            raise ValueError("topology does not match the matrix")
+        S, G = topo.servers, topo.gpus
+        return self.bytes.reshape(S, G, S, G).sum(axis=(1, 3))
+
+    def plan(self, topo: "Topology", kind=None, **opts) -> "Plan":
+        """Plan this matrix (``kind=None`` lets the cost model choose, see ``select_plan``)."""
+        if kind is None:
+            nv = intra_link("B200_MEASURED")
+            return select_plan(self.units, topo, opts.pop("inter", nv), opts.pop("intra", nv), self.unit_bytes * 1e-6, **opts)[0]
+        return build_plan(self.units, topo, kind=kind, **opts)

@@ -434,3 +434,28 @@ def test_damaged_plan_files_are_rejected_not_trusted():
             outcomes["sound"] += 1
             assert (q.delivered_matrix() == q.matrix).all()
     assert outcomes["invalid"] > 50 and outcomes["raised"] + outcomes["invalid"] + outcomes["sound"] == 300
+
+
+def test_traffic_matrix_views_and_bounds():
+    from fast_b200.sched import TrafficMatrix
+
+    tm = TrafficMatrix.from_splits([[0, 3, 1], [2, 5, 0], [4, 0, 0]], unit_bytes=8)
+    assert tm.n == 3 and tm.input_splits(1) == [2, 5, 0] and tm.output_splits(0) == [0, 2, 4]
+    assert (tm.bytes == tm.units * 8).all() and (tm.transposed().units == tm.units.T).all()
+    # busiest port: rank 0 receives 2 + 4 = 6 units (self traffic of rank 1 does not count)
+    assert tm.port_bound_bytes() == 6 * 8 and tm.lower_bound_us(1.0) == pytest.approx(48 / 1e3)
+    assert tm.imbalance() == pytest.approx(6 / (10 / 3))
+    assert tm.hash() == sched.matrix_hash(tm.units) and tm.hash() != tm.transposed().hash()
+    tok = TrafficMatrix.from_tokens(np.full((4, 4), 10), hidden=7168, element_bytes=1)
+    assert tok.unit_bytes == 7168 and (tok.server_view(Topology(2, 2)) == 4 * 10 * 7168).all()
+    z = TrafficMatrix.zipf(8, 1.2, 1 << 20, seed=3)
+    assert (z.units.sum(1) == 1 << 20).all() and z.imbalance() > 1.0 and TrafficMatrix.uniform(8, 1024, True).imbalance() == pytest.approx(1.0)
+    p = z.plan(Topology.flat(8))
+    assert p.validate() == "" and (p.delivered_matrix() == z.units).all()
+    p = tm.plan(Topology.flat(3), kind=PlanKind.STAGED)
+    assert p.kind == PlanKind.STAGED and p.validate() == ""
+    for bad in ([[1, 2]], [[1, -1], [0, 0]]):
+        with pytest.raises(ValueError):
+            TrafficMatrix(np.array(bad))
+    with pytest.raises(ValueError):
+        tm.server_view(Topology(2, 2))
