@@ -182,6 +182,33 @@ struct LowerOptions {
 };
 RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo);
 
+// ---- threaded host twin of the device executor ----------------------------------------------------
+// Runs the lowered work lists of all ranks with `workers` threads per rank (the kernel's CTAs) for
+// `epochs` consecutive collectives over the same signal words, with the device protocol's ready
+// epochs, byte counters, bounded waits and counter clearing (host_threads.cc). Faults are made on
+// the host: a rank that never enters, or one work item whose arrival is never counted.
+struct HostRunOptions {
+  int unit_bytes = 1;
+  int64_t chunk_bytes = 4096;
+  int workers = 3;
+  int epochs = 2;
+  double timeout_s = 2.0;
+  int absent_rank = -1;
+  int withhold_rank = -1;
+  int64_t withhold_item = -1;
+};
+struct HostRunFailure {
+  int rank = -1, site = 0;       // site: 1 entry-ready, 2 balance arrivals, 3 rail arrivals, 4 output arrivals
+  int64_t detail = 0;
+  uint64_t seen = 0, want = 0;
+};
+struct HostRunResult {
+  bool ok = false;
+  HostRunFailure failure;
+  std::vector<std::vector<uint8_t>> outputs;  // of the last collective
+};
+HostRunResult run_on_host_threads(const Plan& p, const HostRunOptions& o, const std::vector<const uint8_t*>& inputs);
+
 // ---- serialisation ------------------------------------------------------------------------------
 std::string plan_to_json(const Plan& p, bool include_ops = true);
 std::vector<uint8_t> plan_to_bytes(const Plan& p);

@@ -18,7 +18,7 @@ CSRC = ROOT / "csrc"
 OBJ = ROOT / "build" / "obj"
 EXT = sysconfig.get_config_var("EXT_SUFFIX")
 
-SCHED_SRCS = ["decompose", "plan", "validate", "cost_model", "lower", "workload", "serialize"]
+SCHED_SRCS = ["decompose", "plan", "validate", "cost_model", "lower", "workload", "serialize", "host_threads"]
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -47,7 +47,7 @@ def build_sched(force=False):
     srcs = [CSRC / "sched" / f"{s}.cc" for s in SCHED_SRCS] + [CSRC / "sched" / "py_sched.cc"]
     if force or _stale(out, srcs + _headers("sched")):
         inc = [f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}"]
-        _run(["g++", "-std=c++17", "-O2", "-Wall", "-shared", "-fPIC", *inc, *srcs, "-o", out])
+        _run(["g++", "-std=c++17", "-O2", "-Wall", "-shared", "-fPIC", "-pthread", *inc, *srcs, "-o", out])
     return out
 
 
@@ -56,7 +56,23 @@ def build_sim(force=False):
     out.parent.mkdir(exist_ok=True)
     srcs = [CSRC / "sim" / "main.cc"] + [CSRC / "sched" / f"{s}.cc" for s in SCHED_SRCS]
     if force or _stale(out, srcs + _headers("sched")):
-        _run(["g++", "-std=c++17", "-O2", "-Wall", *srcs, "-o", out])
+        _run(["g++", "-std=c++17", "-O2", "-Wall", "-pthread", *srcs, "-o", out])
+    return out
+
+
+def build_twin_check(force=False, tsan=True, relaxed=False):
+    """Threaded host twin of the executor protocol as an executable; with ``tsan`` it is built with
+    ThreadSanitizer (build/fastb-twin-tsan), which makes it the protocol's race detector.
+    ``relaxed`` builds the deliberately broken variant (signals without release / acquire) that the
+    detector must report."""
+    out = ROOT / "build" / (("fastb-twin-tsan" if tsan else "fastb-twin") + ("-relaxed" if relaxed else ""))
+    out.parent.mkdir(exist_ok=True)
+    srcs = [CSRC / "sched" / "twin_check.cc"] + [CSRC / "sched" / f"{s}.cc" for s in SCHED_SRCS]
+    if force or _stale(out, srcs + _headers("sched")):
+        flags = ["-O1", "-g", "-fsanitize=thread"] if tsan else ["-O2"]
+        if relaxed:
+            flags.append("-DFASTB_TWIN_RELAXED")
+        _run(["g++", "-std=c++17", *flags, "-Wall", "-pthread", *srcs, "-o", out])
     return out
 
 
@@ -66,7 +82,7 @@ def build_selfcheck(force=False):
     out.parent.mkdir(exist_ok=True)
     srcs = [CSRC / "sched" / "selfcheck.cc"] + [CSRC / "sched" / f"{s}.cc" for s in SCHED_SRCS]
     if force or _stale(out, srcs + _headers("sched") + _headers("runtime") + [CSRC / "kernels" / "tile_walker.h"]):
-        _run(["g++", "-std=c++17", "-O2", "-Wall", *srcs, "-o", out])
+        _run(["g++", "-std=c++17", "-O2", "-Wall", "-pthread", *srcs, "-o", out])
     return out
 
 

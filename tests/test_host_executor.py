@@ -3,6 +3,7 @@ failures (absent rank, withheld signal, mismatched matrices over gloo)."""
 import os
 import subprocess
 import sys
+import time
 
 import numpy as np
 import pytest
@@ -92,3 +93,59 @@ def test_p2p_executor_gloo(world):
                         "--master-port", str(29580 + world), worker], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
     assert "P2P_OK" in r.stdout
+
+
+# ---- native threaded twin of the device executor (csrc/sched/host_threads.cc) -----------------------
+
+def _byte_inputs(m, unit, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, 256, size=int(m[r].sum()) * unit, dtype=np.uint8) for r in range(m.shape[0])]
+
+
+@pytest.mark.parametrize("servers,gpus", [(4, 1), (2, 2), (2, 4), (3, 2)])
+@pytest.mark.parametrize("kind", [PlanKind.STAGED, PlanKind.FANOUT, PlanKind.SINGLE_BURST, PlanKind.SPREAD_OUT])
+def test_native_twin_matches_sequential_replay(servers, gpus, kind):
+    """Several worker threads per rank, three collectives in a row over the same signal words:
+    the outputs equal the sequential replay of the plan, bit for bit."""
+    n = servers * gpus
+    m = sched.workload_uniform(n, 200, 3 + n, False)
+    p = sched.build_plan(m, Topology(servers, gpus), kind=kind)
+    ins = _byte_inputs(m, 3, seed=n)
+    want = [np.zeros(int(m[:, r].sum()) * 3, np.uint8) for r in range(n)]
+    p.execute_on_host(3, ins, want)
+    res = p.run_threads(ins, unit_bytes=3, chunk_bytes=128, workers=4, epochs=3, timeout_s=20.0)
+    assert res["ok"], res["failure"]
+    for r in range(n):
+        assert np.array_equal(res["outputs"][r], want[r]), f"rank {r}"
+
+
+def test_native_twin_reports_host_made_failures():
+    m = sched.workload_uniform(4, 100, 1, True)
+    p = sched.build_plan(m, Topology(2, 2))
+    ins = _byte_inputs(m, 1)
+    t0 = time.monotonic()
+    res = p.run_threads(ins, timeout_s=0.3, absent_rank=2)           # a rank that never enters
+    rank, site, detail, seen, want = res["failure"]                   # whichever wait ran out first is the one reported
+    assert not res["ok"] and rank != 2 and site in (1, 2, 3, 4) and seen < want and (site != 1 or detail == 2)
+    res = p.run_threads(ins, timeout_s=0.3, withhold_rank=0, withhold_item=0)    # a copy whose arrival is never counted
+    assert not res["ok"] and res["failure"][1] in (2, 3, 4) and res["failure"][3] < res["failure"][4]
+    assert time.monotonic() - t0 < 10.0
+    with pytest.raises(Exception):
+        p.tampered(0, "len", 0).run_threads(ins)                       # invalid plans are refused before anything runs
+
+
+def test_protocol_is_race_free_under_thread_sanitizer():
+    """The twin built with ThreadSanitizer is the protocol's race detector: clean as written,
+    and reported as soon as the arrival signals lose their release / acquire order."""
+    from fast_b200 import _build
+
+    try:
+        good = _build.build_twin_check(tsan=True)
+        broken = _build.build_twin_check(tsan=True, relaxed=True)
+    except Exception as e:  # no sanitizer runtime on this host
+        pytest.skip(f"ThreadSanitizer build unavailable: {e}")
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66")
+    r = subprocess.run([str(good), "1"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and '"failures":0' in r.stdout, r.stdout[-500:] + r.stderr[-2000:]
+    r = subprocess.run([str(broken), "1"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 66 and "data race" in r.stderr
