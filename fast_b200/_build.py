@@ -76,6 +76,21 @@ def build_twin_check(force=False, tsan=True, relaxed=False):
     return out
 
 
+def build_moe_twin(force=False, tsan=True, broken=False):
+    """Threaded host twin of the expert-parallel step's synchronisation (csrc/sched/moe_twin.cc);
+    with ``tsan`` built with ThreadSanitizer (build/fastb-moe-twin-tsan). ``broken`` drops the wait
+    for the owners' ready flags before combine, which the detector must report."""
+    out = ROOT / "build" / (("fastb-moe-twin-tsan" if tsan else "fastb-moe-twin") + ("-broken" if broken else ""))
+    out.parent.mkdir(exist_ok=True)
+    srcs = [CSRC / "sched" / "moe_twin.cc"]
+    if force or _stale(out, srcs):
+        flags = ["-O1", "-g", "-fsanitize=thread"] if tsan else ["-O2"]
+        if broken:
+            flags.append("-DFASTB_MOE_TWIN_NO_READY_WAIT")
+        _run(["g++", "-std=c++17", *flags, "-Wall", "-pthread", *srcs, "-o", out])
+    return out
+
+
 def build_selfcheck(force=False):
     """Native self-check executable of the scheduler library (build/fastb-selfcheck)."""
     out = ROOT / "build" / "fastb-selfcheck"

@@ -149,3 +149,24 @@ def test_protocol_is_race_free_under_thread_sanitizer():
     assert r.returncode == 0 and '"failures":0' in r.stdout, r.stdout[-500:] + r.stderr[-2000:]
     r = subprocess.run([str(broken), "1"], capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 66 and "data race" in r.stderr
+
+
+def test_moe_step_protocol_is_race_free_under_thread_sanitizer():
+    """The expert-parallel step's flags and counters order every reuse of the receive buffers
+    across steps (forward-only and forward + backward, 1 to 4 ranks); dropping the wait for the
+    owners' ready flags before combine is reported."""
+    from fast_b200 import _build
+
+    try:
+        good = _build.build_moe_twin(tsan=True)
+        broken = _build.build_moe_twin(tsan=True, broken=True)
+    except Exception as e:
+        pytest.skip(f"ThreadSanitizer build unavailable: {e}")
+    env = dict(os.environ, TSAN_OPTIONS="halt_on_error=1 exitcode=66")
+    r = subprocess.run([str(good), "4"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and '"failures":0' in r.stdout, r.stdout[-500:] + r.stderr[-2000:]
+    # the backward pass' entry handshake is belt and braces: the count exchange already orders the reuse
+    r = subprocess.run([str(good), "4", "0"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and '"failures":0' in r.stdout, r.stdout[-500:] + r.stderr[-2000:]
+    r = subprocess.run([str(broken), "3"], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 66 and "data race" in r.stderr
