@@ -32,8 +32,11 @@ def main():
                 want = [np.zeros(int(plan.buffers[r, 1]) * ub, dtype=np.uint8) for r in range(world)]
                 plan.execute_on_host(ub, ins, want)
                 out = torch.zeros(int(plan.buffers[rank, 1]) * ub, dtype=torch.uint8)
-                ex.run(plan, ub, torch.from_numpy(ins[rank]), out)
-                assert np.array_equal(out.numpy(), want[rank]), f"rank {rank} {kind} {topo}"
+                prepared = ex.prepare(plan, ub, torch.from_numpy(ins[rank]), out)
+                for _ in range(2):  # a prepared plan can be issued again (descriptors are bound to the buffers)
+                    out.zero_()
+                    prepared.run()
+                    assert np.array_equal(out.numpy(), want[rank]), f"rank {rank} {kind} {topo}"
                 # transposed plan = the reverse collective
                 back = sched.build_plan(m, topo, kind=kind, transpose=True)
                 ret = torch.zeros(int(back.buffers[rank, 1]) * ub, dtype=torch.uint8)
