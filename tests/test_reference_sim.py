@@ -72,3 +72,20 @@ def test_intra_fabric_models_match_reference_pipeline3(ref_sim):
         assert abs(p.cost(inter, intra, 1.0, "full_mesh")["total_us"] - ref["pipeline3_full_mesh_us"]) / ref["pipeline3_full_mesh_us"] < 1e-6
         assert abs(p.cost(inter, intra, 1.0, "ring")["total_us"] - ref["pipeline3_2ring_us"]) / ref["pipeline3_2ring_us"] < 1e-6
         assert abs(p.cost(inter, intra, 1.0, "hybrid_cube_mesh")["total_us"] - ref["pipeline3_hybrid_cube_mesh_us"]) / ref["pipeline3_hybrid_cube_mesh_us"] < 0.05
+
+
+def test_large_topology_tracks_reference(ref_sim):
+    """16 servers x 8 GPUs (beyond the reference runtime's 10-server structs, within its simulator):
+    same line sum, stage counts within 3 %, and this decomposition is faster on the same CPU."""
+    S, G = 16, 8
+    inter, intra = sched.gbps_model(400, 0.7), sched.LinkModel(0.1, 2.3)
+    m = sched.workload_uniform(S * G, 10000, 3)
+    ref = _run_ref(ref_sim, m, S, G, inter, intra, 1e-3)
+    p = sched.build_plan(m, Topology(S, G))
+    assert ref["exact"] and p.validate() == "" and (p.delivered_matrix() == m).all()
+    sm = np.ascontiguousarray(p.server_matrix)
+    d = sched.decompose(sm)
+    assert d["exact"] and d["line_sum"] == ref["freq_sum"]
+    assert abs(len(d["stages"]) - ref["stages"]) <= 0.03 * ref["stages"] and len(d["stages"]) <= S * S - 2 * S + 2
+    ours_us = min(sched.decompose_time_us(sm, reps=3) for _ in range(3))
+    assert ours_us < ref["decompose_us"], (ours_us, ref["decompose_us"])
