@@ -178,6 +178,8 @@ class Communicator:
 
     # ---- execution --------------------------------------------------------------------------------
     def _launch_args(self, s: Schedule, output: torch.Tensor, input: torch.Tensor, staging: Optional[dict] = None):
+        if self.heap is None:
+            raise RuntimeError("communicator is closed")
         if self.broken:
             raise RuntimeError("communicator saw a failed collective; call reset() on every rank first")
         if self.liveness is not None:
@@ -279,6 +281,32 @@ class Communicator:
         if self.group is not None or (dist.is_initialized() and self.world > 1):
             dist.barrier(group=self.group)
         self.broken = False
+
+    def close(self) -> None:
+        """Collective: every rank calls it after its last collective. Synchronises the device,
+        waits for the peers (nobody unmaps memory a peer may still write), stops an attached
+        heartbeat and lets go of the symmetric heap; the slab and the peer mappings are released
+        when the last tensor carved from the heap is gone. The communicator is unusable afterwards."""
+        import torch.distributed as dist
+
+        if self.heap is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.group is not None or (dist.is_initialized() and self.world > 1):
+            dist.barrier(group=self.group)
+        if self.liveness is not None:
+            self.liveness.leave()
+            self.liveness = None
+        self._staging.clear()
+        self._sched_cache.clear()
+        self.heap = None
+        self.broken = True  # any further launch is refused
+
+    def __enter__(self) -> "Communicator":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
 
 
 class LocalGroup:

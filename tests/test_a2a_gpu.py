@@ -168,3 +168,21 @@ def test_reference_tester_class_on_one_rank():
     t = FlashComm(0, 1, 1, None, comm=Communicator(heap_bytes=64 << 20, device=0), mean_units=1 << 16)
     for res in (t.test_basic_alltoall(warmup=2, iters=2), t.test_flash_alltoall(warmup=2, iters=2)):
         assert res["verified"] and res["time_ms"] > 0 and res["per_gpu_MB"] > 0
+
+
+def test_close_refuses_further_launches_and_keeps_live_tensors_valid():
+    from fast_b200.parallel import Communicator
+
+    with Communicator(heap_bytes=16 << 20, device=0) as comm:
+        s = comm.schedule(np.array([[256]], dtype=np.int64), unit_bytes=4)
+        out = comm.alloc(256, torch.int32)
+        x = torch.arange(256, dtype=torch.int32, device="cuda")
+        comm.all_to_all_v(out, x, s)
+        comm.check()
+        assert torch.equal(out, x)
+    with pytest.raises(RuntimeError, match="closed"):
+        comm.all_to_all_v(out, x, s)
+    out.add_(1)                      # the slab lives as long as a tensor carved from it
+    torch.cuda.synchronize()
+    assert torch.equal(out, x + 1)
+    comm.close()                     # idempotent
