@@ -459,3 +459,22 @@ def test_traffic_matrix_views_and_bounds():
             TrafficMatrix(np.array(bad))
     with pytest.raises(ValueError):
         tm.server_view(Topology(2, 2))
+
+
+def test_cmake_project_builds_and_its_tests_pass(tmp_path):
+    """The stand-alone native build (library, simulator, self-check, protocol twins) for C++ users."""
+    import shutil
+
+    cmake, ctest, gxx = shutil.which("cmake"), shutil.which("ctest"), shutil.which("g++")
+    if not (cmake and ctest and gxx):
+        pytest.skip("cmake / ctest / g++ not available")
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    bdir = str(tmp_path / "b")
+    r = subprocess.run([cmake, "-S", root, "-B", bdir, f"-DCMAKE_CXX_COMPILER={gxx}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r = subprocess.run([cmake, "--build", bdir, "-j", "8"], capture_output=True, text=True)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    r = subprocess.run([ctest, "--test-dir", bdir, "--output-on-failure"], capture_output=True, text=True)
+    assert r.returncode == 0 and "100% tests passed" in r.stdout, (r.stdout + r.stderr)[-3000:]
