@@ -73,7 +73,7 @@ bool wait_ge(Shared& sh, const std::atomic<uint64_t>& flag, uint64_t want, int r
 }
 
 // One "CTA" of rank `r` for collective `epoch`; mirrors run_rank() of the kernel.
-void run_worker(Shared& sh, const RankProgram& prog, int n, int stages, int r, int worker, int workers, uint64_t epoch, const HostRunOptions& o) {
+void run_worker(Shared& sh, const RankProgram& prog, int n, int r, int worker, int workers, uint64_t epoch, const HostRunOptions& o) {
   RankState& me = *sh.ranks[r];
   std::vector<uint64_t> pending(n, 0);  // output bytes stored per peer and not yet announced
   if (worker == 0)
@@ -108,7 +108,7 @@ void run_worker(Shared& sh, const RankProgram& prog, int n, int stages, int r, i
     if (ok) {
       me.counters[0].store(0, std::memory_order_relaxed);
       me.counters[1].store(0, std::memory_order_relaxed);
-      for (int k = 0; k < stages; ++k) me.counters[2 + k].store(0, std::memory_order_relaxed);
+      for (size_t k = 0; k < prog.expect_rail_bytes.size(); ++k) me.counters[2 + k].store(0, std::memory_order_relaxed);
     }
     me.ticket.store(0, std::memory_order_release);
   }
@@ -117,19 +117,20 @@ void run_worker(Shared& sh, const RankProgram& prog, int n, int stages, int r, i
 }  // namespace
 
 HostRunResult run_on_host_threads(const Plan& p, const HostRunOptions& o, const std::vector<const uint8_t*>& inputs) {
-  const int n = p.matrix.n, K = p.num_stages;
+  const int n = p.matrix.n;
   if (static_cast<int>(inputs.size()) != n) throw std::invalid_argument("run_on_host_threads: one input buffer per rank");
   if (o.workers < 1 || o.epochs < 1 || o.unit_bytes < 1) throw std::invalid_argument("run_on_host_threads: bad options");
   const std::string err = validate_plan(p);
   if (!err.empty()) throw std::invalid_argument("run_on_host_threads: invalid plan: " + err);
   std::vector<RankProgram> progs;
-  LowerOptions lo; lo.unit_bytes = o.unit_bytes; lo.chunk_bytes = o.chunk_bytes;
+  LowerOptions lo; lo.unit_bytes = o.unit_bytes; lo.chunk_bytes = o.chunk_bytes; lo.rail_segment_bytes = o.rail_segment_bytes;
   for (int r = 0; r < n; ++r) progs.push_back(lower_for_rank(p, r, lo));
 
   Shared sh;
   for (int r = 0; r < n; ++r) {
     auto st = std::make_unique<RankState>();
     st->ready.reset(new std::atomic<uint64_t>[n]);
+    const int K = static_cast<int>(progs[r].expect_rail_bytes.size());  // rail counters of this rank (stages, or segments)
     st->counters.reset(new std::atomic<uint64_t>[2 + K]);
     for (int i = 0; i < n; ++i) st->ready[i].store(0);
     for (int i = 0; i < 2 + K; ++i) st->counters[i].store(0);
@@ -151,7 +152,7 @@ HostRunResult run_on_host_threads(const Plan& p, const HostRunOptions& o, const 
         if (e > 1) std::fill(sh.ranks[r]->buf[1].begin(), sh.ranks[r]->buf[1].end(), 0);  // stale output must not pass for new
         std::vector<std::thread> ws;
         for (int w = 0; w < o.workers; ++w)
-          ws.emplace_back(run_worker, std::ref(sh), std::cref(progs[r]), n, K, r, w, o.workers, static_cast<uint64_t>(e), std::cref(o));
+          ws.emplace_back(run_worker, std::ref(sh), std::cref(progs[r]), n, r, w, o.workers, static_cast<uint64_t>(e), std::cref(o));
         for (auto& t : ws) t.join();
       }
     });

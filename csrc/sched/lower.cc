@@ -6,10 +6,78 @@
 // interleaved so that every peer of a slot is in flight at once, and ordering between phases is
 // carried by byte counters (balance / per-stage rail / output) instead of per-block flags.
 #include <algorithm>
+#include <cstdint>
 
 #include "plan.h"
 
 namespace fastb {
+
+namespace {
+
+// Arrival counters of the rail staging. Without segments there is one per stage (slot = stage).
+// With segments every stage's region in a rank's rail staging is cut into pieces of
+// `segment_bytes`, each with a counter of its own, so that a forwarder waits only for the piece it
+// reads (the reference's cumulative chunk_ready_threshold, alltoall_global_scheduler.cc:1152-1178,
+// without its assumption that chunks arrive in order).
+struct RailSlots {
+  int64_t ub = 1, seg = 0;                 // unit bytes; segment bytes (0 = one slot per stage)
+  int K = 0;
+  std::vector<int64_t> lo, hi;             // [rank * K + stage] region of the stage in the rank's rail staging, bytes
+  std::vector<int> base;                   // [rank * K + stage] first slot of the region
+  std::vector<int> count;                  // [rank] slots of the rank
+
+  int slots_in(int64_t bytes) const { return seg > 0 ? static_cast<int>((bytes + seg - 1) / seg) : 1; }
+  int slot(int rank, int stage, int64_t byte_off) const {
+    const size_t i = static_cast<size_t>(rank) * K + stage;
+    return seg > 0 ? base[i] + static_cast<int>((byte_off - lo[i]) / seg) : stage;
+  }
+  // End (bytes, exclusive) of the segment that contains byte_off.
+  int64_t segment_end(int rank, int stage, int64_t byte_off) const {
+    if (seg <= 0) return INT64_MAX;
+    const size_t i = static_cast<size_t>(rank) * K + stage;
+    return lo[i] + ((byte_off - lo[i]) / seg + 1) * seg;
+  }
+};
+
+RailSlots make_slots(const Plan& p, const LowerOptions& lo_opt, int max_slots) {
+  RailSlots rs;
+  const int n = p.matrix.n, K = p.num_stages;
+  rs.ub = lo_opt.unit_bytes; rs.K = K;
+  rs.count.assign(n, K);
+  if (lo_opt.rail_segment_bytes <= 0 || K == 0) return rs;
+  rs.lo.assign(static_cast<size_t>(n) * K, INT64_MAX);
+  rs.hi.assign(static_cast<size_t>(n) * K, 0);
+  for (const Op& o : p.ops) {
+    if (o.dst_buf != Buf::kRail) continue;
+    const size_t i = static_cast<size_t>(o.dst_rank) * K + o.stage;
+    rs.lo[i] = std::min(rs.lo[i], o.dst_off * rs.ub);
+    rs.hi[i] = std::max(rs.hi[i], (o.dst_off + o.len) * rs.ub);
+  }
+  rs.seg = (std::max<int64_t>(lo_opt.rail_segment_bytes, 16) + 15) / 16 * 16;
+  rs.base.assign(static_cast<size_t>(n) * K, 0);
+  int64_t widest = 0;
+  for (size_t i = 0; i < rs.lo.size(); ++i)
+    if (rs.lo[i] != INT64_MAX) widest = std::max(widest, rs.hi[i] - rs.lo[i]);
+  while (true) {  // every rank must fit the signal block: coarsen until the busiest one does
+    int worst = 0;
+    for (int r = 0; r < n; ++r) {
+      int c = 0;
+      for (int k = 0; k < K; ++k) {
+        const size_t i = static_cast<size_t>(r) * K + k;
+        rs.base[i] = c;
+        c += rs.hi[i] > rs.lo[i] && rs.lo[i] != INT64_MAX ? rs.slots_in(rs.hi[i] - rs.lo[i]) : 1;
+      }
+      rs.count[r] = c;
+      worst = std::max(worst, c);
+    }
+    // Never below one counter per stage: once a segment covers the widest region nothing is left to merge.
+    if (worst <= max_slots || rs.seg >= widest) break;
+    rs.seg *= 2;
+  }
+  return rs;
+}
+
+}  // namespace
 
 RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
   const int n = p.matrix.n;
@@ -18,28 +86,58 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
   RankProgram prog;
   prog.rank = rank;
   const int K = p.num_stages;
-  prog.expect_rail_bytes.assign(K, 0);
   const int64_t ub = lo.unit_bytes;
+  const RailSlots slots = make_slots(p, lo, lo.max_rail_slots);
+  prog.expect_rail_bytes.assign(slots.count[rank], 0);
   const RankBuffers& b = p.buffers[rank];
   prog.buffers_bytes = RankBuffers{b.input_units * ub, b.output_units * ub, b.balance_units * ub, b.rail_units * ub};
 
+  // A piece is the part of an op that signals (rail push) or waits for (forward) one rail slot.
+  struct Piece { const Op* op; int64_t begin, bytes; int signal_slot, wait_slot; };
+  auto pieces_of = [&](const Op& o, std::vector<Piece>& out) {
+    const int64_t total = o.len * ub;
+    const bool to_rail = o.dst_buf == Buf::kRail, from_rail = o.src_buf == Buf::kRail;
+    if (slots.seg <= 0 || (!to_rail && !from_rail)) {
+      out.push_back(Piece{&o, 0, total, o.stage, from_rail ? o.stage : -1});
+      return;
+    }
+    // Cut where the rail-side offset crosses a segment boundary (a forward reads rail, a push writes it).
+    const int owner = to_rail ? o.dst_rank : o.src_rank;
+    const int64_t rail0 = (to_rail ? o.dst_off : o.src_off) * ub;
+    int64_t done = 0;
+    while (done < total) {
+      const int64_t at = rail0 + done;
+      const int64_t take = std::min(total - done, slots.segment_end(owner, o.stage, at) - at);
+      const int s = slots.slot(owner, o.stage, at);
+      out.push_back(Piece{&o, done, take, to_rail ? s : o.stage, from_rail ? s : -1});
+      done += take;
+    }
+  };
+
   // slot 0: balance | slot 1: rail 0, intrinsic, un-staged direct ops | slot k+1: rail k (+ staged
   // direct ops of round k) and redistribution of stage k-1 | last slot: final redistribution.
-  std::vector<std::vector<const Op*>> push_slot(K + 3), fwd_slot(K + 3);
+  std::vector<std::vector<Piece>> push_slot(K + 3), fwd_slot(K + 3);
+  std::vector<Piece> tmp;
   for (const Op& o : p.ops) {
     if (o.dst_rank == rank) {
       const int64_t bytes = o.len * ub;
       if (o.dst_buf == Buf::kOutput) prog.expect_output_bytes += bytes;
       else if (o.dst_buf == Buf::kBalance) prog.expect_balance_bytes += bytes;
-      else prog.expect_rail_bytes[o.stage] += bytes;
+      else {
+        tmp.clear();
+        pieces_of(o, tmp);
+        for (const Piece& pc : tmp) prog.expect_rail_bytes[pc.signal_slot] += pc.bytes;
+      }
     }
     if (o.src_rank != rank) continue;
+    std::vector<Piece>* dst = nullptr;
     switch (o.phase) {
-      case Phase::kBalance: push_slot[0].push_back(&o); break;
-      case Phase::kIntrinsic: push_slot[o.stage < 0 ? 1 : 1 + o.stage].push_back(&o); break;
-      case Phase::kRail: push_slot[1 + o.stage].push_back(&o); break;
-      case Phase::kRedistribute: fwd_slot[2 + o.stage].push_back(&o); break;
+      case Phase::kBalance: dst = &push_slot[0]; break;
+      case Phase::kIntrinsic: dst = &push_slot[o.stage < 0 ? 1 : 1 + o.stage]; break;
+      case Phase::kRail: dst = &push_slot[1 + o.stage]; break;
+      case Phase::kRedistribute: dst = &fwd_slot[2 + o.stage]; break;
     }
+    pieces_of(o, *dst);
   }
   auto chunk_of = [&](int64_t bytes) {
     int64_t c = lo.chunk_bytes;
@@ -47,15 +145,15 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
     c = (c + 15) / 16 * 16;
     return c;
   };
-  auto emit_interleaved = [&](const std::vector<const Op*>& ops) {
-    // Proportional interleave: chunk j of an op with c chunks gets key (j + 1/2) / c and chunks are
-    // issued in key order, so every op of the slot advances at a rate proportional to its size
-    // and all of them finish together (equal ops degenerate to plain round-robin). A heavy pair
+  auto emit_interleaved = [&](const std::vector<Piece>& pcs) {
+    // Proportional interleave: chunk j of a piece with c chunks gets key (j + 1/2) / c and chunks are
+    // issued in key order, so every transfer of the slot advances at a rate proportional to its size
+    // and all of them finish together (equal ones degenerate to plain round-robin). A heavy pair
     // is then in flight from the first chunk on instead of trailing alone at the end.
-    struct Slice { double key; size_t op; int64_t begin, bytes; };
+    struct Slice { double key; size_t pc; int64_t begin, bytes; };
     std::vector<Slice> slices;
-    for (size_t k = 0; k < ops.size(); ++k) {
-      const int64_t total = ops[k]->len * ub;
+    for (size_t k = 0; k < pcs.size(); ++k) {
+      const int64_t total = pcs[k].bytes;
       const int64_t c = chunk_of(total);
       const int64_t pieces = (total + c - 1) / c;
       for (int64_t j = 0; j < pieces; ++j)
@@ -63,18 +161,19 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
     }
     std::stable_sort(slices.begin(), slices.end(), [](const Slice& x, const Slice& y) { return x.key < y.key; });
     for (const Slice& sl : slices) {
-      const Op& o = *ops[sl.op];
+      const Piece& pc = pcs[sl.pc];
+      const Op& o = *pc.op;
       WorkItem w{};
-      w.src_off = o.src_off * ub + sl.begin;
-      w.dst_off = o.dst_off * ub + sl.begin;
+      w.src_off = o.src_off * ub + pc.begin + sl.begin;
+      w.dst_off = o.dst_off * ub + pc.begin + sl.begin;
       w.bytes = sl.bytes;
       w.dst_rank = o.dst_rank;
       w.src_buf = static_cast<uint8_t>(o.src_buf);
       w.dst_buf = static_cast<uint8_t>(o.dst_buf);
       w.wait_kind = o.src_buf == Buf::kBalance ? 1 : o.src_buf == Buf::kRail ? 2 : 0;
       w.signal_kind = o.dst_buf == Buf::kBalance ? 1 : o.dst_buf == Buf::kRail ? 2 : 3;
-      w.stage = o.stage;
-      w.wait_stage = o.src_buf == Buf::kRail ? o.stage : -1;
+      w.stage = pc.signal_slot;
+      w.wait_stage = pc.wait_slot;
       prog.items.push_back(w);
     }
   };

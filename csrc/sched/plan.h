@@ -179,6 +179,13 @@ struct LowerOptions {
   int64_t chunk_bytes = 1 << 20;  // upper size of a work item
   int64_t min_chunk_bytes = 64 << 10;
   int max_chunks_per_op = 1 << 16;
+  // > 0: every stage's region of the rail staging gets one arrival counter per this many bytes, and a
+  // forwarder waits only for the piece it reads (chunk-level readiness inside a stage). 0: one
+  // counter per stage. The program then has `expect_rail_bytes.size()` counters instead of one per
+  // stage; work items name them in `stage` / `wait_stage`. Segments are coarsened until no rank
+  // needs more than `max_rail_slots` counters (the size of the device signal block).
+  int64_t rail_segment_bytes = 0;
+  int max_rail_slots = 4096;
 };
 RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo);
 
@@ -190,6 +197,7 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo);
 struct HostRunOptions {
   int unit_bytes = 1;
   int64_t chunk_bytes = 4096;
+  int64_t rail_segment_bytes = 0;  // see LowerOptions
   int workers = 3;
   int epochs = 2;
   double timeout_s = 2.0;

@@ -164,11 +164,13 @@ PYBIND11_MODULE(_sched, m) {
         d["stage_inter_us"] = c.stage_inter_us; d["stage_redistribute_us"] = c.stage_redistribute_us;
         return d; }, py::arg("inter"), py::arg("intra"), py::arg("mb_per_unit") = 1.0, py::arg("intra_topology") = "switch",
            py::arg("links") = std::vector<int>())
-      .def("lower", [](const Plan& p, int rank, int unit_bytes, int64_t chunk_bytes) {
-        LowerOptions lo; lo.unit_bytes = unit_bytes; lo.chunk_bytes = chunk_bytes;
-        return program_dict(lower_for_rank(p, rank, lo)); }, py::arg("rank"), py::arg("unit_bytes") = 1, py::arg("chunk_bytes") = 1 << 20)
+      .def("lower", [](const Plan& p, int rank, int unit_bytes, int64_t chunk_bytes, int64_t rail_segment_bytes, int max_rail_slots) {
+        LowerOptions lo; lo.unit_bytes = unit_bytes; lo.chunk_bytes = chunk_bytes; lo.rail_segment_bytes = rail_segment_bytes; lo.max_rail_slots = max_rail_slots;
+        return program_dict(lower_for_rank(p, rank, lo)); }, py::arg("rank"), py::arg("unit_bytes") = 1, py::arg("chunk_bytes") = 1 << 20,
+           py::arg("rail_segment_bytes") = 0, py::arg("max_rail_slots") = 4096)
       .def("run_threads", [](const Plan& p, std::vector<py::array_t<uint8_t, py::array::c_style>> ins, int unit_bytes, int64_t chunk_bytes,
-                             int workers, int epochs, double timeout_s, int absent_rank, int withhold_rank, int64_t withhold_item) {
+                             int workers, int epochs, double timeout_s, int absent_rank, int withhold_rank, int64_t withhold_item,
+                             int64_t rail_segment_bytes) {
         const int n = p.matrix.n;
         if (static_cast<int>(ins.size()) != n) throw std::invalid_argument("need one input array per rank");
         std::vector<const uint8_t*> ip;
@@ -177,7 +179,7 @@ PYBIND11_MODULE(_sched, m) {
           ip.push_back(ins[r].data());
         }
         HostRunOptions o; o.unit_bytes = unit_bytes; o.chunk_bytes = chunk_bytes; o.workers = workers; o.epochs = epochs; o.timeout_s = timeout_s;
-        o.absent_rank = absent_rank; o.withhold_rank = withhold_rank; o.withhold_item = withhold_item;
+        o.absent_rank = absent_rank; o.withhold_rank = withhold_rank; o.withhold_item = withhold_item; o.rail_segment_bytes = rail_segment_bytes;
         HostRunResult res;
         { py::gil_scoped_release nogil; res = run_on_host_threads(p, o, ip); }
         py::dict d;
@@ -187,7 +189,8 @@ PYBIND11_MODULE(_sched, m) {
         for (auto& v : res.outputs) { py::array_t<uint8_t> a(static_cast<py::ssize_t>(v.size())); std::memcpy(a.mutable_data(), v.data(), v.size()); outs.append(a); }
         d["outputs"] = outs;
         return d; }, py::arg("inputs"), py::arg("unit_bytes") = 1, py::arg("chunk_bytes") = 4096, py::arg("workers") = 3, py::arg("epochs") = 2,
-           py::arg("timeout_s") = 2.0, py::arg("absent_rank") = -1, py::arg("withhold_rank") = -1, py::arg("withhold_item") = -1)
+           py::arg("timeout_s") = 2.0, py::arg("absent_rank") = -1, py::arg("withhold_rank") = -1, py::arg("withhold_item") = -1,
+           py::arg("rail_segment_bytes") = 0)
       .def("execute_on_host", [](const Plan& p, int unit_bytes, std::vector<py::array_t<uint8_t, py::array::c_style>> ins,
                                  std::vector<py::array_t<uint8_t, py::array::c_style>> outs, int64_t drop_op) {
         const int n = p.matrix.n;

@@ -34,6 +34,7 @@ int main(int argc, char** argv) {
         }
         execute_on_host(p, unit, ip, wp);
         HostRunOptions o; o.unit_bytes = unit; o.chunk_bytes = 192; o.workers = 2 + runs % 3; o.epochs = 3; o.timeout_s = 20.0;
+        o.rail_segment_bytes = runs % 2 ? 256 : 0;  // every other run: one arrival counter per 256 bytes of rail staging
         HostRunResult res = run_on_host_threads(p, o, ip);
         ++runs;
         bool same = res.ok;

@@ -19,6 +19,9 @@ from ..sched import PlanKind, Topology
 from ..utils.config import CONFIG
 
 
+MAX_RAIL_COUNTERS = 4096  # rail arrival counters in the device signal block (kSigMaxStages)
+
+
 @dataclass
 class Schedule:
     """A plan lowered for one rank, with its device-resident work list."""
@@ -129,7 +132,7 @@ class Communicator:
 
     # ---- scheduling -----------------------------------------------------------------------------
     def schedule(self, matrix, unit_bytes: int = 1, transpose: bool = False, kind=PlanKind.STAGED, chunk_bytes: Optional[int] = None,
-                 verify: bool = False, **plan_opts) -> Schedule:
+                 verify: bool = False, rail_segment_bytes: int = 0, **plan_opts) -> Schedule:
         """Plan the collective for ``matrix`` (units; ``matrix[i, j]`` = rank i -> rank j).
 
         Every rank must pass the same matrix. Staged plans are built with pieces cut on 16-byte
@@ -138,6 +141,8 @@ class Communicator:
         collectives would wait for bytes that never come. ``kind="auto"`` lets the cost model choose
         between the fan-out and the staged plan (and the single-burst plan on a two-tier topology)
         for this matrix and unit size, under the link model fitted to this fabric.
+        ``rail_segment_bytes > 0`` (two-tier plans) gives every such piece of a stage's rail staging its
+        own arrival counter, so that redistribution starts piece by piece instead of stage by stage.
         """
         m = np.ascontiguousarray(matrix, dtype=np.int64)
         if verify and self.world > 1:
@@ -153,7 +158,7 @@ class Communicator:
                 chunk_bytes *= 2
         if "split_align" not in plan_opts:
             plan_opts["split_align"] = max(1, 16 // np.gcd(16, unit_bytes))
-        key = (sched.matrix_hash(m), unit_bytes, transpose, str(kind), chunk_bytes, tuple(sorted((k, str(v)) for k, v in plan_opts.items())))
+        key = (sched.matrix_hash(m), unit_bytes, transpose, str(kind), chunk_bytes, rail_segment_bytes, tuple(sorted((k, str(v)) for k, v in plan_opts.items())))
         s = self._sched_cache.get(key)
         if s is None:
             if kind == "auto":
@@ -162,7 +167,7 @@ class Communicator:
             err = plan.validate()
             if err:
                 raise RuntimeError(f"scheduler produced an invalid plan: {err}")
-            low = plan.lower(self.rank, unit_bytes, chunk_bytes)
+            low = plan.lower(self.rank, unit_bytes, chunk_bytes, rail_segment_bytes, MAX_RAIL_COUNTERS)
             prog = self._C.A2AProgram(torch.from_numpy(low["items"]), [int(x) for x in low["expect_rail_bytes"]],
                                       int(low["expect_output_bytes"]), int(low["expect_balance_bytes"]), self.device.index)
             s = Schedule(plan, unit_bytes, prog, low, self.rank)

@@ -38,10 +38,11 @@ class HostExecutor:
     enters the collective) or ``{"drop_signal": (src_rank, item_index)}`` (the copy happens but its
     arrival is never counted)."""
 
-    def __init__(self, plan: "sched.Plan", unit_bytes: int = 1, chunk_bytes: int = 4096, timeout_s: float = 1.0, faults: Optional[dict] = None):
+    def __init__(self, plan: "sched.Plan", unit_bytes: int = 1, chunk_bytes: int = 4096, timeout_s: float = 1.0, faults: Optional[dict] = None,
+                 rail_segment_bytes: int = 0):
         self.plan, self.unit_bytes, self.timeout_s = plan, unit_bytes, timeout_s
         self.n = plan.matrix.shape[0]
-        self.programs = [plan.lower(r, unit_bytes, chunk_bytes) for r in range(self.n)]
+        self.programs = [plan.lower(r, unit_bytes, chunk_bytes, rail_segment_bytes) for r in range(self.n)]
         self.faults = faults or {}
         self.errors: List[Optional[HostTimeout]] = [None] * self.n
 

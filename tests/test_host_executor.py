@@ -170,3 +170,18 @@ def test_moe_step_protocol_is_race_free_under_thread_sanitizer():
     assert r.returncode == 0 and '"failures":0' in r.stdout, r.stdout[-500:] + r.stderr[-2000:]
     r = subprocess.run([str(broken), "3"], capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 66 and "data race" in r.stderr
+
+
+@pytest.mark.parametrize("servers,gpus", [(2, 2), (2, 4), (3, 2)])
+def test_rail_segments_run_bit_exact_in_both_host_models(servers, gpus):
+    n = servers * gpus
+    m = sched.workload_uniform(n, 300, 9 + n, False)
+    p = sched.build_plan(m, Topology(servers, gpus))
+    ins = _byte_inputs(m, 3, seed=n)
+    want = [np.zeros(int(m[:, r].sum()) * 3, np.uint8) for r in range(n)]
+    p.execute_on_host(3, ins, want)
+    res = p.run_threads(ins, unit_bytes=3, chunk_bytes=128, workers=4, epochs=3, timeout_s=20.0, rail_segment_bytes=192)
+    assert res["ok"], res["failure"]
+    outs = HostExecutor(p, unit_bytes=3, chunk_bytes=128, timeout_s=10.0, rail_segment_bytes=192).run(ins)
+    for r in range(n):
+        assert np.array_equal(res["outputs"][r], want[r]) and np.array_equal(outs[r], want[r]), f"rank {r}"

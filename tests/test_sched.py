@@ -478,3 +478,38 @@ def test_cmake_project_builds_and_its_tests_pass(tmp_path):
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
     r = subprocess.run([ctest, "--test-dir", bdir, "--output-on-failure"], capture_output=True, text=True)
     assert r.returncode == 0 and "100% tests passed" in r.stdout, (r.stdout + r.stderr)[-3000:]
+
+
+def test_lowering_with_rail_segments_gives_each_piece_its_own_counter():
+    """Chunk-level readiness inside a stage: with ``rail_segment_bytes`` the rail staging of every
+    stage is cut into pieces with one arrival counter each; pushes signal the piece they land in,
+    forwards wait only for the piece they read, and the byte accounting still closes."""
+    m = sched.workload_uniform(16, 400, 23, False)
+    p = sched.build_plan(m, Topology(4, 4))
+    ub, seg = 3, 256
+    base = [p.lower(r, ub, 128) for r in range(16)]
+    segd = [p.lower(r, ub, 128, seg) for r in range(16)]
+    for r in range(16):
+        b, s = base[r], segd[r]
+        assert len(b["expect_rail_bytes"]) == p.num_stages and len(s["expect_rail_bytes"]) > p.num_stages
+        assert sum(s["expect_rail_bytes"]) == sum(b["expect_rail_bytes"]) and max(s["expect_rail_bytes"]) <= seg + 15
+        assert s["items"][:, 2].sum() == b["items"][:, 2].sum()            # same bytes sent
+        assert s["expect_output_bytes"] == b["expect_output_bytes"]
+    # what is signalled into a counter of rank d by all senders equals what d expects there
+    for d in range(16):
+        got = np.zeros(len(segd[d]["expect_rail_bytes"]), dtype=np.int64)
+        for r in range(16):
+            it = segd[r]["items"]
+            sel = (it[:, 3] == d) & (it[:, 7] == 2)                         # dst_rank == d, signals a rail counter
+            np.add.at(got, it[sel, 8], it[sel, 2])
+        assert (got == np.array(segd[d]["expect_rail_bytes"])).all()
+        it = segd[d]["items"]
+        waits = it[it[:, 6] == 2]
+        assert (waits[:, 9] >= 0).all() and (waits[:, 9] < len(got)).all()
+        assert (waits[:, 2] <= seg + 15).all()                              # a forward reads at most one piece
+    capped = p.lower(0, ub, 128, 16, 12)                                    # coarsened until the counters fit
+    assert p.num_stages <= len(capped["expect_rail_bytes"]) <= 12 and sum(capped["expect_rail_bytes"]) == sum(base[0]["expect_rail_bytes"])
+    floor = p.lower(0, ub, 128, 16, 2)                                      # never below one counter per stage
+    assert len(floor["expect_rail_bytes"]) == p.num_stages
+    flat = sched.build_plan(m, Topology.flat(16))
+    assert flat.lower(0, ub, 128, seg)["expect_rail_bytes"] == flat.lower(0, ub, 128)["expect_rail_bytes"]   # no rail staging: nothing changes
