@@ -151,6 +151,7 @@ PlanCost model_cost(const Plan& p, const CostModel& cm) {
       c.total_us = l.alpha_us + static_cast<double>(worst) * l.beta_us_per_mb * mb;
     }
     c.inter_us = c.total_us;
+    c.chunked_total_us = c.total_us;
     return c;
   }
 
@@ -218,6 +219,20 @@ PlanCost model_cost(const Plan& p, const CostModel& cm) {
   }
   c.total_us = t;
   c.exposed_intra_us = t - c.inter_us;
+  {
+    // Two resources, pieces of fraction f of a stage: the NIC runs the stages back to back (stage k
+    // ends at A_k); the intra-server fabric forwards stage k from the moment its first piece has
+    // landed and the previous forward is done, and ends no earlier than one piece after A_k.
+    const double f = std::min(1.0, std::max(cm.rail_segment_fraction, 1e-6));
+    double a_prev = c.balance_us, fwd = c.balance_us + intrinsic_us, a = c.balance_us;
+    for (int k = 0; k < K; ++k) {
+      a = a_prev + c.stage_inter_us[k];
+      const double r = c.stage_redistribute_us[k];
+      if (r > 0) fwd = std::max(std::max(fwd, a_prev + f * c.stage_inter_us[k]) + r, a + f * r);
+      a_prev = a;
+    }
+    c.chunked_total_us = std::max(a, fwd);
+  }
   return c;
 }
 

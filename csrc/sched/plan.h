@@ -127,6 +127,7 @@ struct CostModel {
   double mb_per_unit = 1.0;
   IntraTopology intra_topology = IntraTopology::kSwitch;
   std::vector<int> links;      // kLinkGraph: gpus x gpus link multiplicities (0 = no direct link)
+  double rail_segment_fraction = 1.0 / 16;  // piece size over stage size for PlanCost::chunked_total_us
 };
 // Link multiplicities of the 8-GPU hybrid cube mesh (6 links per GPU, the fabric the reference's
 // intra_transfer_hybrid_cude_mesh hard-codes).
@@ -136,6 +137,10 @@ struct PlanCost {
   double lower_bound_us = 0;   // busiest port (or busiest server NIC set) at full rate
   double spread_out_us = 0;    // ring-offset baseline on the same matrix
   std::vector<double> stage_inter_us, stage_redistribute_us;
+  // The same plan executed with chunk-level readiness (LowerOptions::rail_segment_bytes): the
+  // redistribution of a stage follows its inter-server transfer piece by piece instead of waiting
+  // for the whole stage. Equal to total_us for plans without redistribution.
+  double chunked_total_us = 0;
 };
 // Pipeline model: balance, then stage k's inter-server transfer overlaps stage k-1's
 // redistribution (simulation/scheduler/global.cpp:237-402 pipeline2). For one server per GPU

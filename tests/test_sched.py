@@ -513,3 +513,18 @@ def test_lowering_with_rail_segments_gives_each_piece_its_own_counter():
     assert len(floor["expect_rail_bytes"]) == p.num_stages
     flat = sched.build_plan(m, Topology.flat(16))
     assert flat.lower(0, ub, 128, seg)["expect_rail_bytes"] == flat.lower(0, ub, 128)["expect_rail_bytes"]   # no rail staging: nothing changes
+
+
+def test_cost_model_values_chunk_level_readiness():
+    """chunked_total_us: redistribution follows the inter-server transfer piece by piece. Never slower
+    than stage-level readiness, never below the port bound, equal when nothing is redistributed."""
+    inter, slow_intra = sched.inter_link("ETHER400"), sched.intra_link("DGX2")
+    m = sched.workload_zipf_rows(32, 0.0, 1 << 26, 3, 16)
+    c = sched.build_plan(m, Topology(4, 8)).cost(inter, slow_intra, 1e-6)
+    assert c["lower_bound_us"] <= c["chunked_total_us"] < c["total_us"]
+    assert (c["total_us"] - c["chunked_total_us"]) > 0.5 * (c["total_us"] - c["lower_bound_us"])   # most of the exposed forward time is hidden
+    nv = sched.intra_link("B200_MEASURED")
+    flat = sched.build_plan(m[:8, :8], Topology.flat(8)).cost(nv, nv, 1e-6)
+    assert flat["chunked_total_us"] == flat["total_us"]
+    fan = sched.build_plan(m, Topology(4, 8), kind=PlanKind.FANOUT).cost(inter, slow_intra, 1e-6)
+    assert fan["chunked_total_us"] == fan["total_us"]
