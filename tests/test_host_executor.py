@@ -185,3 +185,36 @@ def test_rail_segments_run_bit_exact_in_both_host_models(servers, gpus):
     outs = HostExecutor(p, unit_bytes=3, chunk_bytes=128, timeout_s=10.0, rail_segment_bytes=192).run(ins)
     for r in range(n):
         assert np.array_equal(res["outputs"][r], want[r]) and np.array_equal(outs[r], want[r]), f"rank {r}"
+
+
+def test_random_plans_and_lowering_options_through_the_native_twin():
+    """Random topologies, sparse / skewed / single-entry matrices, plan kinds, alignments, unit and
+    chunk sizes, rail segments and worker counts: the threaded twin always equals the replay."""
+    from fast_b200.sched import MatchPolicy
+
+    rng = np.random.default_rng(2024)
+    kinds = [PlanKind.STAGED, PlanKind.SINGLE_BURST, PlanKind.FANOUT, PlanKind.SPREAD_OUT]
+    for trial in range(120):
+        S, G = int(rng.integers(1, 5)), int(rng.integers(1, 5))
+        n = S * G
+        if trial % 3 == 0:
+            m = sched.workload_uniform(n, int(rng.integers(1, 500)), trial, bool(trial % 2))
+        elif trial % 3 == 1:
+            m = rng.integers(0, 50, size=(n, n))
+            m[rng.random((n, n)) < 0.6] = 0
+        else:
+            m = np.zeros((n, n), dtype=np.int64)
+            m[rng.integers(0, n), rng.integers(0, n)] = int(rng.integers(1, 1000))
+        p = sched.build_plan(np.ascontiguousarray(m, dtype=np.int64), Topology(S, G), kind=kinds[int(rng.integers(0, 4))],
+                             split_align=int(rng.choice([1, 2, 4, 16])), transpose=bool(rng.integers(0, 2)),
+                             match=MatchPolicy.BOTTLENECK if trial % 5 == 0 else MatchPolicy.FIRST_FIT)
+        assert p.validate() == ""
+        ub, pm = int(rng.choice([1, 3, 8, 16])), p.matrix
+        ins = [rng.integers(0, 256, size=int(pm[r].sum()) * ub, dtype=np.uint8) for r in range(n)]
+        want = [np.zeros(int(pm[:, r].sum()) * ub, np.uint8) for r in range(n)]
+        p.execute_on_host(ub, ins, want)
+        res = p.run_threads(ins, unit_bytes=ub, chunk_bytes=int(rng.choice([16, 64, 256, 4096])), workers=int(rng.integers(1, 5)), epochs=2,
+                            timeout_s=20.0, rail_segment_bytes=int(rng.choice([0, 16, 48, 256, 1000])))
+        assert res["ok"], (trial, res["failure"])
+        for r in range(n):
+            assert np.array_equal(res["outputs"][r], want[r]), (trial, r)
