@@ -41,6 +41,11 @@ struct __align__(8) SmemCtl {
   int abort_flag;
 };
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(SmemCtl);
+static_assert(kSmemBytes <= 227 * 1024, "dynamic shared memory of one CTA on sm_100a");
+static_assert(kABytes % 1024 == 0 && kBBytes % 1024 == 0, "operand tiles start on 1024-byte boundaries (128-byte swizzle atoms)");
+static_assert(kAccStages * BN <= kTmemCols && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tensor memory columns: power of two, at most 512");
+static_assert(BK * 2 == 128, "one k block is one 128-byte swizzle row of bf16");
+static_assert(kThreads == 32 * (2 + kEpiWarps) && kEpiWarps == 4, "warp roles: producer, MMA issuer, four epilogue warps (one per TMEM lane quarter)");
 
 template <GemmMode MODE, GemmEpilogue EPI>
 __global__ void __launch_bounds__(kThreads, 1)
