@@ -160,3 +160,26 @@ def test_init_id_stand_in_has_the_reference_shape():
 
     uid = get_nvshmem_init_id()
     assert uid.dtype == torch.uint8 and uid.numel() == 128 and uid.device.type == "cpu"
+
+
+def test_torch_custom_ops_are_registered_with_schemas_and_trace_with_fake_tensors():
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    from fast_b200.ops import registry  # noqa: F401  (registers torch.ops.fast_b200.*)
+
+    schema = str(torch.ops.fast_b200.grouped_gemm_fwd.default._schema)
+    assert "Tensor(a3!) out" in schema and "Tensor(a5!)? gate_up_out" in schema      # outputs are declared as mutated
+    assert "-> (Tensor, Tensor)" in str(torch.ops.fast_b200.route_topk.default._schema)
+    for name in ("grouped_gemm_dgrad", "grouped_gemm_wgrad"):
+        assert hasattr(torch.ops.fast_b200, name)
+    with FakeTensorMode():                                                               # shapes propagate, no kernel runs
+        logits = torch.empty(100, 8, dtype=torch.float32, device="cuda")
+        idx, w = torch.ops.fast_b200.route_topk(logits, None, 2)
+        assert idx.shape == (100, 2) and idx.dtype == torch.int32 and w.dtype == torch.float32 and w.device.type == "cuda"
+        a = torch.empty(512, 256, dtype=torch.bfloat16, device="cuda")
+        wt = torch.empty(2, 512, 256, dtype=torch.bfloat16, device="cuda")
+        off = torch.empty(3, dtype=torch.int32, device="cuda")
+        out = torch.empty(512, 512, dtype=torch.bfloat16, device="cuda")
+        assert torch.ops.fast_b200.grouped_gemm_fwd(a, wt, off, out, False, None) is None
+        assert torch.ops.fast_b200.grouped_gemm_dgrad(out, wt, off, a, None) is None
+        assert torch.ops.fast_b200.grouped_gemm_wgrad(out, a, off, torch.empty_like(wt)) is None
