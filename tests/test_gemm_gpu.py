@@ -137,3 +137,29 @@ def test_dgrad_with_fused_swiglu_backward(kernel_variant):
         got = dgu[s:e].float().view(e - s, I // 128, 2, 128)
         _close(got[:, :, 0].reshape(e - s, I), gt.grad)
         _close(got[:, :, 1].reshape(e - s, I), ut.grad)
+
+
+def test_custom_operators_run_the_same_kernels():
+    """torch.ops.fast_b200.* (schemas, mutation annotations) give the same bits as the direct calls."""
+    from fast_b200.ops import gemm, registry  # noqa: F401
+
+    G, N, K = 2, 512, 256
+    counts, off, R, a, w = _setup(G, N, K, [200, 77], seed=5)
+    direct = torch.zeros(R, N, device="cuda", dtype=torch.bfloat16)
+    via_op = torch.zeros(R, N, device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_fwd(a, w, off, direct)
+    torch.ops.fast_b200.grouped_gemm_fwd(a, w, off, via_op, False, None)
+    gemm.check()
+    assert torch.equal(direct, via_op)
+    dx1, dx2 = torch.zeros_like(a), torch.zeros_like(a)
+    gemm.grouped_gemm_dgrad(direct, w, off, dx1)
+    torch.ops.fast_b200.grouped_gemm_dgrad(direct, w, off, dx2, None)
+    dw1, dw2 = torch.zeros_like(w), torch.zeros_like(w)
+    gemm.grouped_gemm_wgrad(direct, a, off, dw1)
+    torch.ops.fast_b200.grouped_gemm_wgrad(direct, a, off, dw2)
+    gemm.check()
+    assert torch.equal(dx1, dx2) and torch.equal(dw1, dw2)
+    logits = torch.randn(300, 16, device="cuda")
+    idx, wts = torch.ops.fast_b200.route_topk(logits, None, 2)
+    ref = torch.softmax(logits, -1).topk(2, dim=-1)
+    assert torch.equal(idx.long(), ref.indices) and torch.allclose(wts, ref.values / ref.values.sum(-1, keepdim=True), atol=1e-5)
