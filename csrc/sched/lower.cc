@@ -15,65 +15,51 @@ namespace fastb {
 namespace {
 
 // Arrival counters of the rail staging. Without segments there is one per stage (slot = stage).
-// With segments every stage's region in a rank's rail staging is cut into pieces of
-// `segment_bytes`, each with a counter of its own, so that a forwarder waits only for the piece it
-// reads (the reference's cumulative chunk_ready_threshold, alltoall_global_scheduler.cc:1152-1178,
-// without its assumption that chunks arrive in order).
+// With segments a rank's rail staging is cut into pieces of `seg` bytes by absolute offset and a
+// piece of stage k gets the counter `offset / seg + k`, so that a forwarder waits only for the
+// pieces it reads (the reference's cumulative chunk_ready_threshold,
+// alltoall_global_scheduler.cc:1152-1178, without its assumption that chunks arrive in order).
+// Adding the stage index keeps the counters of neighbouring stages apart even where their regions
+// share a `seg`-sized window: a forward of stage k must never wait for bytes of a later stage,
+// whose pushes come after it in the work lists (that would be a cycle between ranks). This relies
+// on the regions lying in stage order, which holds up to Plan::rail_tail_start; what is staged
+// behind it (remainders of aligned cuts, a few units per pair) gets one counter per stage instead.
+// The numbering needs nothing but per-rank sizes, so a one-rank view of the plan lowers exactly
+// like the full plan.
 struct RailSlots {
-  int64_t ub = 1, seg = 0;                 // unit bytes; segment bytes (0 = one slot per stage)
+  int64_t seg = 0, ub = 1;    // segment bytes (0 = one slot per stage); unit bytes
   int K = 0;
-  std::vector<int64_t> lo, hi;             // [rank * K + stage] region of the stage in the rank's rail staging, bytes
-  std::vector<int> base;                   // [rank * K + stage] first slot of the region
-  std::vector<int> count;                  // [rank] slots of the rank
+  const Plan* plan = nullptr;
+  std::vector<int> count;     // [rank] counters of the rank
 
-  int slots_in(int64_t bytes) const { return seg > 0 ? static_cast<int>((bytes + seg - 1) / seg) : 1; }
-  int slot(int rank, int stage, int64_t byte_off) const {
-    const size_t i = static_cast<size_t>(rank) * K + stage;
-    return seg > 0 ? base[i] + static_cast<int>((byte_off - lo[i]) / seg) : stage;
+  bool in_tail(int owner, int64_t byte_off) const { return seg > 0 && byte_off >= plan->rail_tail_start[owner] * ub; }
+  int ordered_slots(int owner) const { return static_cast<int>((plan->buffers[owner].rail_units * ub + seg - 1) / seg) + K; }
+  int slot(int owner, int stage, int64_t byte_off) const {
+    if (seg <= 0) return stage;
+    return in_tail(owner, byte_off) ? ordered_slots(owner) + stage : static_cast<int>(byte_off / seg) + stage;
   }
-  // End (bytes, exclusive) of the segment that contains byte_off.
-  int64_t segment_end(int rank, int stage, int64_t byte_off) const {
-    if (seg <= 0) return INT64_MAX;
-    const size_t i = static_cast<size_t>(rank) * K + stage;
-    return lo[i] + ((byte_off - lo[i]) / seg + 1) * seg;
+  // End (bytes, exclusive) of the piece that contains byte_off; tail pieces are not cut.
+  int64_t piece_end(int owner, int64_t byte_off) const {
+    if (seg <= 0 || in_tail(owner, byte_off)) return INT64_MAX;
+    return std::min((byte_off / seg + 1) * seg, plan->rail_tail_start[owner] * ub);
   }
 };
 
-RailSlots make_slots(const Plan& p, const LowerOptions& lo_opt, int max_slots) {
+RailSlots make_slots(const Plan& p, const LowerOptions& lo_opt) {
   RailSlots rs;
   const int n = p.matrix.n, K = p.num_stages;
-  rs.ub = lo_opt.unit_bytes; rs.K = K;
+  rs.plan = &p; rs.K = K; rs.ub = lo_opt.unit_bytes;
   rs.count.assign(n, K);
   if (lo_opt.rail_segment_bytes <= 0 || K == 0) return rs;
-  rs.lo.assign(static_cast<size_t>(n) * K, INT64_MAX);
-  rs.hi.assign(static_cast<size_t>(n) * K, 0);
-  for (const Op& o : p.ops) {
-    if (o.dst_buf != Buf::kRail) continue;
-    const size_t i = static_cast<size_t>(o.dst_rank) * K + o.stage;
-    rs.lo[i] = std::min(rs.lo[i], o.dst_off * rs.ub);
-    rs.hi[i] = std::max(rs.hi[i], (o.dst_off + o.len) * rs.ub);
-  }
-  rs.seg = (std::max<int64_t>(lo_opt.rail_segment_bytes, 16) + 15) / 16 * 16;
-  rs.base.assign(static_cast<size_t>(n) * K, 0);
   int64_t widest = 0;
-  for (size_t i = 0; i < rs.lo.size(); ++i)
-    if (rs.lo[i] != INT64_MAX) widest = std::max(widest, rs.hi[i] - rs.lo[i]);
-  while (true) {  // every rank must fit the signal block: coarsen until the busiest one does
-    int worst = 0;
-    for (int r = 0; r < n; ++r) {
-      int c = 0;
-      for (int k = 0; k < K; ++k) {
-        const size_t i = static_cast<size_t>(r) * K + k;
-        rs.base[i] = c;
-        c += rs.hi[i] > rs.lo[i] && rs.lo[i] != INT64_MAX ? rs.slots_in(rs.hi[i] - rs.lo[i]) : 1;
-      }
-      rs.count[r] = c;
-      worst = std::max(worst, c);
-    }
-    // Never below one counter per stage: once a segment covers the widest region nothing is left to merge.
-    if (worst <= max_slots || rs.seg >= widest) break;
-    rs.seg *= 2;
-  }
+  for (int r = 0; r < n; ++r) widest = std::max(widest, p.buffers[r].rail_units * lo_opt.unit_bytes);
+  if (widest == 0) return rs;  // nothing is staged (flat plans): nothing to segment
+  rs.seg = (std::max<int64_t>(lo_opt.rail_segment_bytes, 16) + 15) / 16 * 16;
+  // Every rank must fit the signal block: coarsen until the largest staging area does (never
+  // below one counter per stage, plus one per stage for the tail).
+  const int64_t room = std::max<int64_t>(lo_opt.max_rail_slots - 2 * K, 1);
+  while ((widest + rs.seg - 1) / rs.seg > room && rs.seg < widest) rs.seg *= 2;
+  for (int r = 0; r < n; ++r) rs.count[r] = rs.ordered_slots(r) + K;
   return rs;
 }
 
@@ -87,7 +73,7 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
   prog.rank = rank;
   const int K = p.num_stages;
   const int64_t ub = lo.unit_bytes;
-  const RailSlots slots = make_slots(p, lo, lo.max_rail_slots);
+  const RailSlots slots = make_slots(p, lo);
   prog.expect_rail_bytes.assign(slots.count[rank], 0);
   const RankBuffers& b = p.buffers[rank];
   prog.buffers_bytes = RankBuffers{b.input_units * ub, b.output_units * ub, b.balance_units * ub, b.rail_units * ub};
@@ -101,13 +87,13 @@ RankProgram lower_for_rank(const Plan& p, int rank, const LowerOptions& lo) {
       out.push_back(Piece{&o, 0, total, o.stage, from_rail ? o.stage : -1});
       return;
     }
-    // Cut where the rail-side offset crosses a segment boundary (a forward reads rail, a push writes it).
+    // Cut where the rail-side offset crosses a piece boundary (a forward reads rail, a push writes it).
     const int owner = to_rail ? o.dst_rank : o.src_rank;
     const int64_t rail0 = (to_rail ? o.dst_off : o.src_off) * ub;
     int64_t done = 0;
     while (done < total) {
       const int64_t at = rail0 + done;
-      const int64_t take = std::min(total - done, slots.segment_end(owner, o.stage, at) - at);
+      const int64_t take = std::min(total - done, slots.piece_end(owner, at) - at);
       const int s = slots.slot(owner, o.stage, at);
       out.push_back(Piece{&o, done, take, to_rail ? s : o.stage, from_rail ? s : -1});
       done += take;

@@ -56,8 +56,11 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
   }
   auto in_at = [&](int r, int d) { return p.in_disp[static_cast<size_t>(r) * n + d]; };
   auto out_at = [&](int r, int s) { return p.out_disp[static_cast<size_t>(r) * n + s]; };
+  const int only = opt.only_rank;
+  if (only >= n) throw std::invalid_argument("build_plan: only_rank out of range");
+  auto keep = [only](int src, int dst) { return only < 0 || src == only || dst == only; };
   auto direct = [&](int r, int d, int stage) {
-    if (M.at(r, d) == 0) return;
+    if (M.at(r, d) == 0 || !keep(r, d)) return;
     p.ops.push_back(Op{Phase::kIntrinsic, Buf::kInput, Buf::kOutput, stage, r, d, r, d, in_at(r, d),
                        out_at(d, r), M.at(r, d), 0});
   };
@@ -68,12 +71,14 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
     for (int step = 0; step < n; ++step)
       for (int r = 0; r < n; ++r) direct(r, (r + step) % n, -1);
     p.num_stages = 0;
+    p.rail_tail_start.assign(n, 0);
     return p;
   }
   if (opt.kind == PlanKind::kSpreadOut) {
     for (int step = 0; step < n; ++step)
       for (int r = 0; r < n; ++r) direct(r, (r + step) % n, step);
     p.num_stages = n;
+    p.rail_tail_start.assign(n, 0);
     return p;
   }
 
@@ -121,8 +126,9 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
             if (mv == 0) { ++k; continue; }
             const int dst_rank = s * G + small, src_rank = s * G + big;
             int64_t& cursor = p.buffers[dst_rank].balance_units;
-            p.ops.push_back(Op{Phase::kBalance, Buf::kInput, Buf::kBalance, -1, src_rank, dst_rank,
-                               src_rank, t * G + pc.final_local, pc.off, cursor, mv, pc.pair_off});
+            if (keep(src_rank, dst_rank))
+              p.ops.push_back(Op{Phase::kBalance, Buf::kInput, Buf::kBalance, -1, src_rank, dst_rank,
+                                 src_rank, t * G + pc.final_local, pc.off, cursor, mv, pc.pair_off});
             hold_at(s, t, small).push_back(Piece{pc.origin_local, pc.final_local, pc.pair_off, mv, Buf::kBalance, cursor});
             cursor += mv;
             load[big] -= mv;
@@ -178,14 +184,17 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
       if (take == 0) break;
       const int origin = s * G + pc.origin_local, fin = t * G + pc.final_local;
       if (pc.final_local == i) {
-        rail.push_back(Op{Phase::kRail, pc.buf, Buf::kOutput, k, src_rank, dst_rank, origin, fin, pc.off,
-                          out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
+        if (keep(src_rank, dst_rank))
+          rail.push_back(Op{Phase::kRail, pc.buf, Buf::kOutput, k, src_rank, dst_rank, origin, fin, pc.off,
+                            out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
       } else {
         int64_t& cursor = p.buffers[dst_rank].rail_units;
-        rail.push_back(Op{Phase::kRail, pc.buf, Buf::kRail, k, src_rank, dst_rank, origin, fin, pc.off, cursor,
-                          take, pc.pair_off});
-        redis.push_back(Op{Phase::kRedistribute, Buf::kRail, Buf::kOutput, k, dst_rank, fin, origin, fin, cursor,
-                           out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
+        if (keep(src_rank, dst_rank))
+          rail.push_back(Op{Phase::kRail, pc.buf, Buf::kRail, k, src_rank, dst_rank, origin, fin, pc.off, cursor,
+                            take, pc.pair_off});
+        if (keep(dst_rank, fin))
+          redis.push_back(Op{Phase::kRedistribute, Buf::kRail, Buf::kOutput, k, dst_rank, fin, origin, fin, cursor,
+                             out_at(fin, origin) + pc.pair_off, take, pc.pair_off});
         cursor += take;
       }
       if (budget > 0) budget -= take;
@@ -209,6 +218,8 @@ Plan build_plan(const Matrix& traffic, Topology topo, const PlanOptions& opt) {
       }
     }
   }
+  p.rail_tail_start.resize(n);
+  for (int r = 0; r < n; ++r) p.rail_tail_start[r] = p.buffers[r].rail_units;  // up to here regions follow the stage order
   // Alignment can leave a few units behind a stage budget; ship them with the pair's last stage.
   if (opt.kind == PlanKind::kStaged) {
     for (int s = 0; s < S; ++s)

@@ -66,6 +66,11 @@ struct PlanOptions {
   int64_t scale = 0;        // explicit coarsening divisor; 0 = derive from scale_policy
   int64_t split_align = 1;  // units; pieces are only cut at multiples of this inside a segment
   bool transpose = false;   // plan the reverse collective (combine / backward all-to-all)
+  // >= 0: keep only the ops this rank sends or receives (buffer sizes, offsets and stages are those
+  // of the full plan). What one rank needs to lower and run its part; the op list of a full plan
+  // grows with the cube of the server count (the reference's per-GPU view is schedule_this_gpu,
+  // alltoall_global_scheduler.cc:1512-1821).
+  int only_rank = -1;
   // Skip the balancing of a (server, server) tile whose transfer is latency-dominated: when the
   // beta cost of balancing + redistributing it is less than twice its alpha cost (the reference
   // simulator's check_balance_dispatch, simulation/scheduler/local.cpp:187-216). Uses `intra`.
@@ -88,6 +93,10 @@ struct Plan {
   int32_t num_stages = 0;  // number of distinct stage indices used by ops
   std::vector<int64_t> in_disp, out_disp;  // n x n: offset of segment [r][peer] in r's input / output
   std::vector<RankBuffers> buffers;        // per rank
+  // Per rank: offset (units) in the rail staging from which the regions are no longer laid out in
+  // stage order. Alignment can leave a few units behind a stage budget; they are shipped with the
+  // pair's last stage but staged after everything else. Equal to rail_units when there is no such tail.
+  std::vector<int64_t> rail_tail_start;
   std::vector<Op> ops;                     // global list, grouped by phase then stage
   uint64_t matrix_hash = 0;
 };
@@ -184,11 +193,11 @@ struct LowerOptions {
   int64_t chunk_bytes = 1 << 20;  // upper size of a work item
   int64_t min_chunk_bytes = 64 << 10;
   int max_chunks_per_op = 1 << 16;
-  // > 0: every stage's region of the rail staging gets one arrival counter per this many bytes, and a
-  // forwarder waits only for the piece it reads (chunk-level readiness inside a stage). 0: one
-  // counter per stage. The program then has `expect_rail_bytes.size()` counters instead of one per
-  // stage; work items name them in `stage` / `wait_stage`. Segments are coarsened until no rank
-  // needs more than `max_rail_slots` counters (the size of the device signal block).
+  // > 0: the rail staging gets one arrival counter per this many bytes, and a forwarder waits only
+  // for the pieces it reads (chunk-level readiness inside a stage). 0: one counter per stage. The
+  // program then has `expect_rail_bytes.size()` counters instead of one per stage; work items name
+  // them in `stage` / `wait_stage`. Pieces are coarsened until no rank needs more than
+  // `max_rail_slots` counters (the size of the device signal block).
   int64_t rail_segment_bytes = 0;
   int max_rail_slots = 4096;
 };

@@ -102,6 +102,8 @@ PYBIND11_MODULE(_sched, m) {
       .def_property_readonly("servers", [](const Plan& p) { return p.topo.servers; })
       .def_property_readonly("gpus", [](const Plan& p) { return p.topo.gpus; })
       .def_property_readonly("kind", [](const Plan& p) { return p.opt.kind; })
+      .def_property_readonly("only_rank", [](const Plan& p) { return p.opt.only_rank; })
+      .def_property_readonly("rail_tail_start", [](const Plan& p) { return p.rail_tail_start; })
       .def_property_readonly("transpose", [](const Plan& p) { return p.opt.transpose; })
       .def_property_readonly("num_stages", [](const Plan& p) { return p.num_stages; })
       .def_property_readonly("num_ops", [](const Plan& p) { return p.ops.size(); })
@@ -204,14 +206,14 @@ PYBIND11_MODULE(_sched, m) {
         return execute_on_host(p, unit_bytes, ip, op, drop_op); }, py::arg("unit_bytes"), py::arg("inputs"), py::arg("outputs"), py::arg("drop_op") = -1);
 
   m.def("build_plan", [](const I64Array& a, int servers, int gpus, PlanKind kind, MatchPolicy match, ScalePolicy sp, int64_t scale,
-                         int64_t split_align, bool transpose, LinkModel inter, LinkModel intra, double mbpu, bool balance_alpha_beta) {
+                         int64_t split_align, bool transpose, LinkModel inter, LinkModel intra, double mbpu, bool balance_alpha_beta, int only_rank) {
     PlanOptions o; o.kind = kind; o.match = match; o.scale_policy = sp; o.scale = scale; o.split_align = split_align; o.transpose = transpose;
-    o.inter = inter; o.intra = intra; o.mb_per_unit = mbpu; o.balance_alpha_beta = balance_alpha_beta;
+    o.inter = inter; o.intra = intra; o.mb_per_unit = mbpu; o.balance_alpha_beta = balance_alpha_beta; o.only_rank = only_rank;
     return build_plan(to_matrix(a), Topology{servers, gpus}, o);
   }, py::arg("matrix"), py::arg("servers"), py::arg("gpus"), py::arg("kind") = PlanKind::kStaged, py::arg("match") = MatchPolicy::kFirstFit,
      py::arg("scale_policy") = ScalePolicy::kNone, py::arg("scale") = 0, py::arg("split_align") = 1, py::arg("transpose") = false,
      py::arg("inter") = LinkModel{0.7, 22.0}, py::arg("intra") = LinkModel{0.1, 1.2}, py::arg("mb_per_unit") = 1.0,
-     py::arg("balance_alpha_beta") = false);
+     py::arg("balance_alpha_beta") = false, py::arg("only_rank") = -1);
   m.def("select_plan", [](const I64Array& a, int servers, int gpus, std::vector<PlanKind> kinds, LinkModel inter, LinkModel intra, double mbpu,
                           MatchPolicy match, ScalePolicy sp, int64_t split_align, bool transpose, bool balance_alpha_beta) {
     PlanOptions o; o.match = match; o.scale_policy = sp; o.split_align = split_align; o.transpose = transpose;

@@ -85,7 +85,7 @@ std::vector<uint8_t> plan_to_bytes(const Plan& p) {
   w.pod<int32_t>(p.topo.servers); w.pod<int32_t>(p.topo.gpus);
   w.pod<int32_t>(static_cast<int>(p.opt.kind)); w.pod<int32_t>(static_cast<int>(p.opt.match));
   w.pod<int32_t>(static_cast<int>(p.opt.scale_policy)); w.pod<int64_t>(p.opt.scale); w.pod<int64_t>(p.opt.split_align);
-  w.pod<int32_t>((p.opt.transpose ? 1 : 0) | (p.opt.balance_alpha_beta ? 2 : 0));
+  w.pod<int32_t>((p.opt.transpose ? 1 : 0) | (p.opt.balance_alpha_beta ? 2 : 0) | ((p.opt.only_rank + 1) << 8));
   w.mat(p.matrix); w.mat(p.server_matrix);
   w.mat(p.decomp.padded); w.mat(p.decomp.padding); w.pod(p.decomp.line_sum); w.pod(p.decomp.scale);
   w.pod<uint64_t>(p.decomp.stages.size());
@@ -100,6 +100,7 @@ std::vector<uint8_t> plan_to_bytes(const Plan& p) {
     w.pod(o.src_off); w.pod(o.dst_off); w.pod(o.len); w.pod(o.pair_off);
   }
   w.pod(p.matrix_hash);
+  w.vec(p.rail_tail_start);  // appended after the first release of the format: absent in older blobs
   return w.b;
 }
 
@@ -111,7 +112,7 @@ Plan plan_from_bytes(const std::vector<uint8_t>& blob) {
   p.topo.servers = r.pod<int32_t>(); p.topo.gpus = r.pod<int32_t>();
   p.opt.kind = static_cast<PlanKind>(r.pod<int32_t>()); p.opt.match = static_cast<MatchPolicy>(r.pod<int32_t>());
   p.opt.scale_policy = static_cast<ScalePolicy>(r.pod<int32_t>()); p.opt.scale = r.pod<int64_t>(); p.opt.split_align = r.pod<int64_t>();
-  { const int32_t flags = r.pod<int32_t>(); p.opt.transpose = (flags & 1) != 0; p.opt.balance_alpha_beta = (flags & 2) != 0; }
+  { const int32_t flags = r.pod<int32_t>(); p.opt.transpose = (flags & 1) != 0; p.opt.balance_alpha_beta = (flags & 2) != 0; p.opt.only_rank = (flags >> 8) - 1; }
   p.matrix = r.mat(); p.server_matrix = r.mat();
   p.decomp.padded = r.mat(); p.decomp.padding = r.mat(); p.decomp.line_sum = r.pod<int64_t>(); p.decomp.scale = r.pod<int64_t>();
   uint64_t ns = r.pod<uint64_t>();
@@ -132,6 +133,11 @@ Plan plan_from_bytes(const std::vector<uint8_t>& blob) {
     o.src_off = r.pod<int64_t>(); o.dst_off = r.pod<int64_t>(); o.len = r.pod<int64_t>(); o.pair_off = r.pod<int64_t>();
   }
   p.matrix_hash = r.pod<uint64_t>();
+  if (r.pos < blob.size()) {
+    p.rail_tail_start = r.vec<int64_t>();
+  } else {  // older blob: no tail recorded, which is right for every plan built without piece alignment
+    for (const RankBuffers& b : p.buffers) p.rail_tail_start.push_back(b.rail_units);
+  }
   return p;
 }
 

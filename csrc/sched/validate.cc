@@ -39,6 +39,11 @@ std::string validate_plan(const Plan& p) {
   if (p.in_disp.size() != static_cast<size_t>(n) * n || p.out_disp.size() != static_cast<size_t>(n) * n) return "displacement tables: wrong size";
   if (p.matrix.v.size() != static_cast<size_t>(n) * n) return "matrix: wrong size";
   if (p.num_stages < 0) return "negative stage count";
+  if (p.rail_tail_start.size() != static_cast<size_t>(n)) return "rail tail table: wrong size";
+  for (int r = 0; r < n; ++r)
+    if (p.rail_tail_start[r] < 0 || p.rail_tail_start[r] > p.buffers[r].rail_units) return "rail tail outside the staging area";
+  const int only = p.opt.only_rank;  // >= 0: a one-rank view, only that rank's deliveries and staging can be complete
+  if (only >= n) return "only_rank out of range";
   // Flat tables instead of maps: validation runs on every new plan, and a 512-rank plan has millions of ops.
   std::vector<std::vector<Interval>> delivered(static_cast<size_t>(n) * n);  // origin * n + final -> segment intervals
   std::vector<std::vector<Interval>> staged_w(static_cast<size_t>(n) * 2), staged_r(static_cast<size_t>(n) * 2);  // rank * 2 + (rail ? 1 : 0)
@@ -50,6 +55,7 @@ std::string validate_plan(const Plan& p) {
     const Op& o = p.ops[k];
     auto bad = [&](const char* what) { err << "op " << k << ": " << what; return err.str(); };
     if (o.len <= 0) return bad("non-positive length");
+    if (only >= 0 && o.src_rank != only && o.dst_rank != only) return bad("op of another rank in a one-rank view");
     if (static_cast<unsigned>(o.phase) > 3u || static_cast<unsigned>(o.src_buf) > 3u || static_cast<unsigned>(o.dst_buf) > 3u) return bad("unknown phase or buffer");
     if (o.src_rank < 0 || o.src_rank >= n || o.dst_rank < 0 || o.dst_rank >= n) return bad("rank out of range");
     if (o.origin < 0 || o.origin >= n || o.final_dst < 0 || o.final_dst >= n) return bad("pair out of range");
@@ -86,13 +92,25 @@ std::string validate_plan(const Plan& p) {
       staged_w[staging_slot(o.dst_rank, o.dst_buf)].push_back({o.dst_off, o.dst_off + o.len});
     }
   }
+  {  // up to rail_tail_start the regions of a rank's rail staging follow the stage order
+    std::vector<std::vector<std::pair<int64_t, int>>> by_off(n);
+    for (const Op& o : p.ops)
+      if (o.dst_buf == Buf::kRail && o.dst_off < p.rail_tail_start[o.dst_rank]) by_off[o.dst_rank].push_back({o.dst_off, o.stage});
+    for (int r = 0; r < n; ++r) {
+      std::sort(by_off[r].begin(), by_off[r].end());
+      for (size_t k = 1; k < by_off[r].size(); ++k)
+        if (by_off[r][k].second < by_off[r][k - 1].second) { err << "rank " << r << ": rail staging is not in stage order before its tail"; return err.str(); }
+    }
+  }
   for (int i = 0; i < n; ++i)
     for (int j = 0; j < n; ++j) {
+      if (only >= 0 && j != only) continue;
       std::string r = tiles_exactly(delivered[static_cast<size_t>(i) * n + j], p.matrix.at(i, j));
       if (!r.empty()) { err << "pair " << i << "->" << j << ": delivery has a " << r; return err.str(); }
     }
   for (int r = 0; r < n; ++r)
     for (Buf b : {Buf::kBalance, Buf::kRail}) {
+      if (only >= 0 && r != only) continue;
       std::vector<Interval>&w = staged_w[staging_slot(r, b)], &rd = staged_r[staging_slot(r, b)];
       std::string a = tiles_exactly(w, buf_units(p.buffers[r], b));
       if (!a.empty()) { err << "rank " << r << " staging " << static_cast<int>(b) << ": writes have a " << a; return err.str(); }

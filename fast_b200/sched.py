@@ -88,15 +88,18 @@ class Topology:
 def build_plan(matrix, topo: Topology, kind=PlanKind.STAGED, match=MatchPolicy.FIRST_FIT,
                scale_policy=ScalePolicy.NONE, scale: int = 0, split_align: int = 1, transpose: bool = False,
                inter: Optional[LinkModel] = None, intra: Optional[LinkModel] = None, mb_per_unit: float = 1.0,
-               balance_alpha_beta: bool = False) -> Plan:
+               balance_alpha_beta: bool = False, only_rank: int = -1) -> Plan:
     """Plan one all-to-all(v). ``matrix[i, j]`` = units rank i sends to rank j.
+
+    ``only_rank >= 0`` keeps only the ops that rank sends or receives (sizes, offsets and stages
+    are those of the full plan): what one process needs to lower and run its part on a large job.
 
     ``transpose=True`` plans the reverse collective (MoE combine / backward of dispatch), which
     is what the reference's ``schedule(workload, backward=1)`` does (amd/flash.cpp:400-408).
     """
     m = np.ascontiguousarray(matrix, dtype=np.int64)
     return _S.build_plan(m, topo.servers, topo.gpus, kind, match, scale_policy, scale, split_align, transpose,
-                         inter or gbps_model(400.0, 0.7), intra or nvlink_model(900.0, 0.1), mb_per_unit, balance_alpha_beta)
+                         inter or gbps_model(400.0, 0.7), intra or nvlink_model(900.0, 0.1), mb_per_unit, balance_alpha_beta, only_rank)
 
 
 def select_plan(matrix, topo: Topology, inter: LinkModel, intra: LinkModel, mb_per_unit: float = 1.0, kinds=None,

@@ -194,8 +194,8 @@ def test_random_plans_and_lowering_options_through_the_native_twin():
 
     rng = np.random.default_rng(2024)
     kinds = [PlanKind.STAGED, PlanKind.SINGLE_BURST, PlanKind.FANOUT, PlanKind.SPREAD_OUT]
-    for trial in range(120):
-        S, G = int(rng.integers(1, 5)), int(rng.integers(1, 5))
+    for trial in range(240):
+        S, G = int(rng.integers(1, 6)), int(rng.integers(1, 5))  # five servers and aligned cuts: remainders staged out of stage order
         n = S * G
         if trial % 3 == 0:
             m = sched.workload_uniform(n, int(rng.integers(1, 500)), trial, bool(trial % 2))

@@ -507,10 +507,11 @@ def test_lowering_with_rail_segments_gives_each_piece_its_own_counter():
         waits = it[it[:, 6] == 2]
         assert (waits[:, 9] >= 0).all() and (waits[:, 9] < len(got)).all()
         assert (waits[:, 2] <= seg + 15).all()                              # a forward reads at most one piece
-    capped = p.lower(0, ub, 128, 16, 12)                                    # coarsened until the counters fit
-    assert p.num_stages <= len(capped["expect_rail_bytes"]) <= 12 and sum(capped["expect_rail_bytes"]) == sum(base[0]["expect_rail_bytes"])
-    floor = p.lower(0, ub, 128, 16, 2)                                      # never below one counter per stage
-    assert len(floor["expect_rail_bytes"]) == p.num_stages
+    K = p.num_stages                                                        # counters: pieces + one per stage (+ one per stage for the tail)
+    capped = p.lower(0, ub, 128, 16, 2 * K + 6)                             # coarsened until the counters fit
+    assert 2 * K < len(capped["expect_rail_bytes"]) <= 2 * K + 6 and sum(capped["expect_rail_bytes"]) == sum(base[0]["expect_rail_bytes"])
+    floor = p.lower(0, ub, 128, 16, 2)                                      # never below one piece for the whole staging area
+    assert len(floor["expect_rail_bytes"]) == 2 * K + 1 and sum(floor["expect_rail_bytes"]) == sum(base[0]["expect_rail_bytes"])
     flat = sched.build_plan(m, Topology.flat(16))
     assert flat.lower(0, ub, 128, seg)["expect_rail_bytes"] == flat.lower(0, ub, 128)["expect_rail_bytes"]   # no rail staging: nothing changes
 
@@ -528,3 +529,60 @@ def test_cost_model_values_chunk_level_readiness():
     assert flat["chunked_total_us"] == flat["total_us"]
     fan = sched.build_plan(m, Topology(4, 8), kind=PlanKind.FANOUT).cost(inter, slow_intra, 1e-6)
     assert fan["chunked_total_us"] == fan["total_us"]
+
+
+def test_one_rank_views_lower_like_the_full_plan():
+    """``only_rank``: the ops one rank sends or receives, with the full plan's sizes and offsets.
+    The view validates, survives serialisation and lowers to exactly the same work list."""
+    for servers, gpus in [(4, 1), (2, 4), (3, 2)]:
+        n = servers * gpus
+        m = sched.workload_zipf_rows(n, 1.1, 50000, 3, 4)
+        for kind in (PlanKind.STAGED, PlanKind.SINGLE_BURST, PlanKind.FANOUT):
+            full = sched.build_plan(m, Topology(servers, gpus), kind=kind, split_align=4)
+            total = 0
+            for r in range(n):
+                v = sched.build_plan(m, Topology(servers, gpus), kind=kind, split_align=4, only_rank=r)
+                assert v.validate() == "" and v.only_rank == r and (v.buffers == full.buffers).all() and v.num_stages == full.num_stages
+                ops = v.ops
+                assert ((ops[:, 2] == r) | (ops[:, 3] == r)).all()
+                total += v.num_ops
+                for seg in (0, 256):
+                    a, b = full.lower(r, 4, 4096, seg), v.lower(r, 4, 4096, seg)
+                    assert (a["items"] == b["items"]).all() and a["expect_rail_bytes"] == b["expect_rail_bytes"]
+                    assert a["expect_output_bytes"] == b["expect_output_bytes"] and a["expect_balance_bytes"] == b["expect_balance_bytes"]
+                q = sched.Plan.from_bytes(v.to_bytes())
+                assert q.only_rank == r and q.validate() == "" and q.num_ops == v.num_ops
+            assert total == 2 * full.num_ops - int((full.ops[:, 2] == full.ops[:, 3]).sum())   # every op has two ends (one if local)
+    # an op of another rank inside a view is refused
+    v = sched.build_plan(m, Topology(3, 2), only_rank=0)
+    k = int(np.flatnonzero((v.ops[:, 2] == 0) & (v.ops[:, 3] != 0))[0])
+    stranger = next(x for x in range(1, 6) if x != int(v.ops[k, 3]))
+    assert "another rank" in v.tampered(k, "src_rank", stranger).validate()
+    with pytest.raises(Exception):
+        sched.build_plan(m, Topology(3, 2), only_rank=6)
+
+
+def test_rail_tail_is_recorded_and_gets_stage_counters():
+    """Aligned cuts leave remainders that are staged behind everything else, out of stage order;
+    the plan records where that tail starts, the validator checks the order before it, and the
+    segmented lowering gives tail pieces one counter per stage."""
+    rng = np.random.default_rng(3)
+    m = rng.integers(0, 50, size=(15, 15))
+    p = sched.build_plan(np.ascontiguousarray(m, dtype=np.int64), Topology(5, 3), split_align=2)
+    tails = np.array(p.rail_tail_start)
+    assert p.validate() == "" and (tails <= p.buffers[:, 3]).all() and (tails < p.buffers[:, 3]).any()   # some rank has a tail
+    q = sched.Plan.from_bytes(p.to_bytes())
+    assert list(q.rail_tail_start) == list(p.rail_tail_start) and q.validate() == ""
+    plain = sched.build_plan(np.ascontiguousarray(m, dtype=np.int64), Topology(5, 3), split_align=1)
+    assert (np.array(plain.rail_tail_start) == plain.buffers[:, 3]).all()                                # no alignment, no tail
+    r = int(np.flatnonzero(tails < p.buffers[:, 3])[0])
+    g = p.lower(r, 2, 64, 48)
+    K, nseg = p.num_stages, -(-int(p.buffers[r, 3]) * 2 // 48)
+    assert len(g["expect_rail_bytes"]) == nseg + 2 * K
+    tail_bytes = (int(p.buffers[r, 3]) - int(tails[r])) * 2
+    assert sum(g["expect_rail_bytes"][nseg + K:]) == tail_bytes                                           # tail counters hold exactly the tail
+    # stage order before the tail is part of a plan's soundness: moving an early region to the last stage is refused
+    ops = p.ops
+    ordered = [int(i) for i in np.flatnonzero((ops[:, 5] == sched.BUF_RAIL) & (ops[:, 3] == r) & (ops[:, 7] < tails[r]))]
+    first = min(ordered, key=lambda i: ops[i, 7])
+    assert ops[first, 1] < K - 1 and p.tampered(first, "stage", K - 1).validate() != ""
