@@ -20,6 +20,7 @@ from ..utils.config import CONFIG
 
 
 MAX_RAIL_COUNTERS = 4096  # rail arrival counters in the device signal block (kSigMaxStages)
+VIEW_WORLD = 64           # above this many ranks a communicator plans one-rank views instead of full plans
 
 
 @dataclass
@@ -163,6 +164,10 @@ class Communicator:
         if s is None:
             if kind == "auto":
                 plan_opts.setdefault("mb_per_unit", unit_bytes * 1e-6)
+            elif self.world > VIEW_WORLD:
+                # Large jobs: keep only this rank's ops (same sizes, offsets and work list); the op list
+                # of a full plan grows with the cube of the server count.
+                plan_opts.setdefault("only_rank", self.rank)
             plan = self.plan_cache.get(m, self.topo, kind=kind, transpose=transpose, **plan_opts)
             err = plan.validate()
             if err:
@@ -171,7 +176,7 @@ class Communicator:
             prog = self._C.A2AProgram(torch.from_numpy(low["items"]), [int(x) for x in low["expect_rail_bytes"]],
                                       int(low["expect_output_bytes"]), int(low["expect_balance_bytes"]), self.device.index)
             s = Schedule(plan, unit_bytes, prog, low, self.rank)
-            if CONFIG.log and self.rank == 0:
+            if CONFIG.log and self.rank == 0 and plan.only_rank < 0:
                 nv = sched.nvlink_model(900.0, 2.0)
                 c = plan.cost(nv, nv, unit_bytes * 1e-6)
                 print(f"[fast_b200] scheduled {kind}: {plan.num_stages} stages, {plan.num_ops} ops, {prog.n_items} work items on rank 0, "
