@@ -39,6 +39,20 @@ std::string validate_plan(const Plan& p) {
   if (p.in_disp.size() != static_cast<size_t>(n) * n || p.out_disp.size() != static_cast<size_t>(n) * n) return "displacement tables: wrong size";
   if (p.matrix.v.size() != static_cast<size_t>(n) * n) return "matrix: wrong size";
   if (p.num_stages < 0) return "negative stage count";
+  // Every stage moves something except where a plan kind fixes the count (n rounds of the
+  // spread-out kind); a count far beyond the ops is a damaged header and would size tables by it.
+  if (static_cast<size_t>(p.num_stages) > p.ops.size() + static_cast<size_t>(n) + 1) return "stage count beyond the ops";
+  {  // no buffer of any rank can hold more than the whole traffic (sizes feed offset arithmetic later on)
+    int64_t total = 0;
+    for (int64_t x : p.matrix.v) {
+      if (x < 0 || x > (int64_t{1} << 50)) return "matrix entry out of range";
+      total += x;
+      if (total > (int64_t{1} << 56)) return "matrix total out of range";
+    }
+    for (const RankBuffers& b : p.buffers)
+      for (int64_t u : {b.input_units, b.output_units, b.balance_units, b.rail_units})
+        if (u < 0 || u > total) return "buffer size out of range";
+  }
   if (p.rail_tail_start.size() != static_cast<size_t>(n)) return "rail tail table: wrong size";
   for (int r = 0; r < n; ++r)
     if (p.rail_tail_start[r] < 0 || p.rail_tail_start[r] > p.buffers[r].rail_units) return "rail tail outside the staging area";
@@ -63,6 +77,10 @@ std::string validate_plan(const Plan& p) {
     if (o.dst_off < 0 || o.dst_off + o.len > buf_units(p.buffers[o.dst_rank], o.dst_buf)) return bad("destination range outside its buffer");
     if (o.pair_off < 0 || o.pair_off + o.len > p.matrix.at(o.origin, o.final_dst)) return bad("piece outside its pair segment");
     if (o.src_buf == Buf::kOutput || o.dst_buf == Buf::kInput) return bad("reads output or writes input");
+    // The lowering files ops by stage: none outside [-1, num_stages), staged phases never -1.
+    if (o.stage < -1 || o.stage >= p.num_stages) return bad("stage out of range");
+    if (o.stage < 0 && (o.phase == Phase::kRail || o.phase == Phase::kRedistribute)) return bad("stage out of range");
+    if ((o.src_buf == Buf::kRail || o.dst_buf == Buf::kRail) && o.stage < 0) return bad("rail staging used outside a stage");
     const int ss = o.src_rank / G, ds = o.dst_rank / G;
     if (o.phase != Phase::kRail && p.opt.kind != PlanKind::kFanout && p.opt.kind != PlanKind::kSpreadOut && ss != ds)
       return bad("intra-server phase crosses servers");

@@ -382,6 +382,8 @@ def test_validator_rejects_damaged_plans():
         (staged, "drop", 0, "a gap"),                             # staged piece never arrives: its forward reads a hole
         (bal, "dst_rank", (int(ops[bal, 3]) + 4) % 8, "crosses servers"),
         (rail, "stage", p.num_stages + 3, "stage out of range"),
+        (out, "stage", 10 ** 6, "stage out of range"),            # also for ops outside the staged phases (the lowering files ops by stage)
+        (bal, "stage", -7, "stage out of range"),
         (rail, "dst_rank", int(ops[rail, 3]) ^ 1, "rail"),        # no longer rail-aligned / wrong final rank
     ]
     for op, field, value, needle in cases:
