@@ -39,9 +39,9 @@ std::string validate_plan(const Plan& p) {
   if (p.in_disp.size() != static_cast<size_t>(n) * n || p.out_disp.size() != static_cast<size_t>(n) * n) return "displacement tables: wrong size";
   if (p.matrix.v.size() != static_cast<size_t>(n) * n) return "matrix: wrong size";
   if (p.num_stages < 0) return "negative stage count";
-  // Every stage moves something except where a plan kind fixes the count (n rounds of the
-  // spread-out kind); a count far beyond the ops is a damaged header and would size tables by it.
-  if (static_cast<size_t>(p.num_stages) > p.ops.size() + static_cast<size_t>(n) + 1) return "stage count beyond the ops";
+  // A decomposition of an S x S matrix has at most S^2 - 2S + 2 stages, the spread-out kind n rounds;
+  // anything far beyond is a damaged header, and tables are sized by this count later on.
+  if (static_cast<int64_t>(p.num_stages) > static_cast<int64_t>(S) * S + n + 2) return "stage count out of range";
   {  // no buffer of any rank can hold more than the whole traffic (sizes feed offset arithmetic later on)
     int64_t total = 0;
     for (int64_t x : p.matrix.v) {
