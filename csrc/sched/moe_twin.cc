@@ -7,7 +7,9 @@
 // protocol's own flags. Consecutive steps reuse every buffer, which is the point: built with
 // -fsanitize=thread (build/fastb-moe-twin-tsan) any reuse that the count exchange, the arrival
 // counters and the ready flags do not order is reported as a data race. Results are also checked
-// against values computed directly from the routing.
+// against values computed directly from the routing. Forward-only runs are repeated with the fp8
+// receive path (quantised buffer written by peers, converted locally after all experts arrived)
+// and with the dispatch overlapped with the gated GEMMs on a side stream.
 #include <atomic>
 #include <cstdint>
 #include <cstdio>
@@ -23,7 +25,7 @@ constexpr int H = 4;        // words per row
 constexpr int RA = 4;       // group rows are padded to a multiple of this
 constexpr int kWorkers = 3;
 
-struct Cfg { int W, El, K, T, steps; bool training; bool bwd_entry_handshake; };
+struct Cfg { int W, El, K, T, steps; bool training; bool bwd_entry_handshake; bool fp8 = false; bool overlap = false; };
 
 uint64_t mix(uint64_t x) { x += 0x9e3779b97f4a7c15ull; x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull; x = (x ^ (x >> 27)) * 0x94d049bb133111ebull; return x ^ (x >> 31); }
 
@@ -33,6 +35,7 @@ struct Rank {
   std::unique_ptr<std::atomic<uint64_t>[]> flags;         // [4][W]: 0 counts, 1 y ready, 2 bwd entry, 3 dx ready
   std::unique_ptr<std::atomic<uint64_t>[]> arrive;        // [2][El] monotone row counters
   std::vector<uint32_t> x_recv, y, dy_recv, dx_recv;      // [cap][H] plain
+  std::vector<uint32_t> xq_recv;                          // [cap][H] plain: quantised rows (fp8 dispatch); x_recv is then local
   // local
   std::vector<uint64_t> target;                           // [2][El]
   std::vector<int> send_base, group_off, group_rows;      // [E], [El + 1], [El]
@@ -116,24 +119,27 @@ void run_rank(World& w, int me) {
         for (int row = my.group_off[le] + my.group_rows[le]; row < my.group_off[le + 1]; ++row)
           for (int i = 0; i < H; ++i) buf[static_cast<size_t>(row) * H + i] = 0;
     };
-    // ---- dispatch_push (forward): rows straight into the owners' x_recv, then arrival counts -------
-    zero_pad(my.x_recv);
-    parallel(kWorkers, [&](int k, int n) {
+    // ---- dispatch_push (forward): rows straight into the owners' receive buffer, then arrival counts --
+    // fp8 mode: peers write the quantised buffer; the owner waits for all its experts, converts into
+    // its (then purely local) x_recv and runs the GEMMs ungated. overlap mode: the dispatch runs on a
+    // side stream at the same time as the gated GEMMs of the main stream.
+    if (!c.fp8) zero_pad(my.x_recv);
+    auto dispatch = [&](int k, int n) {
       std::vector<int> sent(E, 0);
       for (int t = k; t < T; t += n)
         for (int j = 0; j < K; ++j) {
           const int e = topk[t * K + j];
-          uint32_t* dst = w.r[e / El]->x_recv.data() + static_cast<size_t>(dest_row[t * K + j]) * H;
-          for (int i = 0; i < H; ++i) dst[i] = x_word(me, step, t, i);
+          Rank& owner = *w.r[e / El];
+          uint32_t* dst = (c.fp8 ? owner.xq_recv : owner.x_recv).data() + static_cast<size_t>(dest_row[t * K + j]) * H;
+          for (int i = 0; i < H; ++i) dst[i] = x_word(me, step, t, i) ^ (c.fp8 ? 0x5a5a0000u : 0u);
           ++sent[e];
         }
       for (int e = 0; e < E; ++e)
         if (sent[e]) w.r[e / El]->arrive[0 * El + e % El].fetch_add(static_cast<uint64_t>(sent[e]), std::memory_order_release);
-    });
-    // ---- gated expert GEMMs: per local expert, wait for its rows, read them (pad rows too), write y ----
-    parallel(kWorkers, [&](int k, int n) {
+    };
+    auto gemms = [&](int k, int n) {
       for (int le = k; le < El; le += n) {
-        if (!wait_ge(w, my.arrive[0 * El + le], my.target[0 * El + le])) return;
+        if (!c.fp8 && !wait_ge(w, my.arrive[0 * El + le], my.target[0 * El + le])) return;
         for (int row = my.group_off[le]; row < my.group_off[le + 1]; ++row)
           for (int i = 0; i < H; ++i) {
             const uint32_t v = my.x_recv[static_cast<size_t>(row) * H + i];
@@ -141,7 +147,22 @@ void run_rank(World& w, int me) {
             my.y[static_cast<size_t>(row) * H + i] = v * 3 + static_cast<uint32_t>(me * El + le + 1);
           }
       }
-    });
+    };
+    std::thread side;
+    if (c.overlap) side = std::thread([&] { parallel(kWorkers, dispatch); });
+    else parallel(kWorkers, dispatch);
+    if (c.fp8) {
+      // wait_counters + dequant: all local experts complete, then quantised rows -> x_recv (real rows only), pad rows zeroed
+      bool ok = true;
+      for (int le = 0; le < El && ok; ++le) ok = wait_ge(w, my.arrive[0 * El + le], my.target[0 * El + le]);
+      if (ok)
+        for (int le = 0; le < El; ++le)
+          for (int row = my.group_off[le]; row < my.group_off[le] + my.group_rows[le]; ++row)
+            for (int i = 0; i < H; ++i) my.x_recv[static_cast<size_t>(row) * H + i] = my.xq_recv[static_cast<size_t>(row) * H + i] ^ 0x5a5a0000u;
+      zero_pad(my.x_recv);
+    }
+    parallel(kWorkers, gemms);
+    if (side.joinable()) side.join();  // the main stream re-joins the side stream before it signals
     if (w.abort.load()) return;
     for (int p = 0; p < W; ++p) w.r[p]->flags[1 * W + me].store(epoch, std::memory_order_release);  // peer_signal: my y is complete
     // ---- combine_pull: every token pulls its K rows from the owners and sums them ------------------
@@ -216,7 +237,7 @@ int run(const Cfg& c) {
     k->arrive.reset(new std::atomic<uint64_t>[2 * c.El]);
     for (int i = 0; i < 4 * c.W; ++i) k->flags[i].store(0);
     for (int i = 0; i < 2 * c.El; ++i) k->arrive[i].store(0);
-    for (auto* b : {&k->x_recv, &k->y, &k->dy_recv, &k->dx_recv, &k->gu}) b->assign(static_cast<size_t>(w.cap) * H, 0);
+    for (auto* b : {&k->x_recv, &k->xq_recv, &k->y, &k->dy_recv, &k->dx_recv, &k->gu}) b->assign(static_cast<size_t>(w.cap) * H, 0);
     k->target.assign(2 * c.El, 0);
     k->send_base.assign(w.E, 0); k->group_off.assign(c.El + 1, 0); k->group_rows.assign(c.El, 0);
     w.r.push_back(std::move(k));
@@ -241,6 +262,13 @@ int main(int argc, char** argv) {
           Cfg c{W, El, K, 10 + 3 * W, steps, training, !no_handshake};
           failures += run(c);
           ++runs;
+          if (!training) {  // the forward-only variants: fp8 receive path, dispatch overlapped with the gated GEMMs
+            Cfg f = c; f.fp8 = true;
+            failures += run(f);
+            Cfg o = c; o.overlap = true;
+            failures += run(o);
+            runs += 2;
+          }
         }
   std::printf("{\"twin_check\":\"moe step protocol\",\"runs\":%d,\"steps\":%d,\"failures\":%d}\n", runs, steps, failures);
   return failures ? 1 : 0;
