@@ -70,6 +70,7 @@ class Communicator:
         import torch.distributed as dist
 
         self._C = runtime.ext()
+        self._virtual = _heap is not None  # one of several ranks of a LocalGroup inside this process
         if _heap is not None:
             self.rank, self.world, self.heap = _rank, _world, _heap
             self.device = torch.device("cuda", device if device is not None else torch.cuda.current_device())
@@ -105,11 +106,23 @@ class Communicator:
         self.liveness_max_age_s = 2.0
 
     # ---- symmetric memory ---------------------------------------------------------------------
-    def alloc(self, shape, dtype=torch.uint8) -> torch.Tensor:
-        """A tensor inside the symmetric heap; all ranks must allocate in the same order."""
+    def alloc(self, shape, dtype=torch.uint8, verify: Optional[bool] = None) -> torch.Tensor:
+        """A tensor inside the symmetric heap. Every rank must make the same allocations (sizes and
+        order): an offset then names the same buffer on every rank, which is what peers rely on when
+        they write into it. Size receive buffers by ``Schedule.max_bytes``, not by a rank's own need.
+        ``verify=True`` (default: the FASTB_CHECK_SYMM=1 switch) compares offset and size across the
+        ranks with one small host collective and raises on a mismatch."""
         shape = (shape,) if isinstance(shape, int) else tuple(shape)
         nbytes = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
         off = self.heap.alloc(max(nbytes, 1))
+        if (CONFIG.check_symm if verify is None else verify) and self.world > 1 and not self._virtual:
+            import torch.distributed as dist
+
+            if dist.is_initialized():
+                seen: List[Optional[tuple]] = [None] * self.world
+                dist.all_gather_object(seen, (int(off), int(nbytes)), group=self.group)
+                if any(x != seen[0] for x in seen):
+                    raise RuntimeError(f"symmetric allocation differs across ranks (offset, bytes per rank): {seen}")
         t = self.heap.tensor(off, list(shape), dtype)
         t._symm_off = off
         return t

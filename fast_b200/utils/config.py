@@ -9,6 +9,7 @@ these are the knobs of this implementation:
   FASTB_NVTX=1            NVTX ranges around the phases of the expert-parallel engine
   FASTB_TIMEOUT_S=<sec>   default limit of device-side waits for new communicators (default 5)
   FASTB_LOG=1             one line per scheduled collective (stages, ops, modeled time) on rank 0
+  FASTB_CHECK_SYMM=1      every symmetric allocation is compared across ranks (one host collective each)
 """
 from __future__ import annotations
 
@@ -23,6 +24,7 @@ class Config:
     nvtx: bool = os.environ.get("FASTB_NVTX", "0") == "1"
     timeout_s: float = float(os.environ.get("FASTB_TIMEOUT_S", "5"))
     log: bool = os.environ.get("FASTB_LOG", "0") == "1"
+    check_symm: bool = os.environ.get("FASTB_CHECK_SYMM", "0") == "1"
 
 
 CONFIG = Config()
