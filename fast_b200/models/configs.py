@@ -100,3 +100,23 @@ def flops_per_step(cfg: MoEConfig, world: int) -> Dict[str, float]:
     total = fwd * (3 if cfg.training else 1)
     router = 2.0 * cfg.tokens_per_rank * cfg.hidden * cfg.num_experts * (3 if cfg.training else 1)
     return {"expert_gemm_fwd": fwd, "expert_gemm_total": total, "router": router, "total": total + router}
+
+
+def step_roofline(cfg: MoEConfig, world: int, bf16_tflops: float, hbm_gbs: float, nvlink_gbs: float = 770.0) -> Dict[str, float]:
+    """Lower bound of one step on one GPU, in ms, from the measured peaks: tensor-core time of the
+    expert GEMMs, memory time of the passes that must stream HBM once (optimizer state, saved
+    activations that do not fit on chip) and NVLink time of the all-to-alls (balanced routing).
+    The phases overlap little in this design (GEMMs, then optimizer), so the bound is their sum."""
+    f = flops_per_step(cfg, world)
+    el = cfg.experts_per_rank(world)
+    rows = cfg.tokens_per_rank * cfg.top_k
+    params = el * 3 * cfg.hidden * cfg.inter
+    gemm_ms = f["expert_gemm_total"] / (bf16_tflops * 1e12) * 1e3
+    # AdamW: bf16 grad + bf16 weight (read, write) + fp32 master, m, v (read, write) = 2 + 4 + 24 bytes per parameter
+    adamw_ms = (params * 28 / (hbm_gbs * 1e9) * 1e3) if cfg.training else 0.0
+    # rows that leave the GPU: dispatch + combine (and their transposes in training), (world - 1) / world of them
+    row_bytes = cfg.hidden * (1 if cfg.fp8_dispatch else 2)
+    off_gpu = rows * (world - 1) / max(world, 1)
+    a2a_bytes = off_gpu * (row_bytes + cfg.hidden * 2) * (2 if cfg.training else 1)
+    a2a_ms = a2a_bytes / (nvlink_gbs * 1e9) * 1e3
+    return {"gemm_ms": gemm_ms, "adamw_ms": adamw_ms, "a2a_ms": a2a_ms, "total_ms": gemm_ms + adamw_ms + a2a_ms}

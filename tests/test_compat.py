@@ -183,3 +183,16 @@ def test_torch_custom_ops_are_registered_with_schemas_and_trace_with_fake_tensor
         assert torch.ops.fast_b200.grouped_gemm_fwd(a, wt, off, out, False, None) is None
         assert torch.ops.fast_b200.grouped_gemm_dgrad(out, wt, off, a, None) is None
         assert torch.ops.fast_b200.grouped_gemm_wgrad(out, a, off, torch.empty_like(wt)) is None
+
+
+def test_step_roofline_adds_up():
+    from fast_b200.models.configs import DEEPSEEK_V3_MOE_LAYER, MIXTRAL_8X7B_BLOCK, step_roofline
+
+    r1 = step_roofline(MIXTRAL_8X7B_BLOCK, 1, 1395.2, 6546.6)
+    r8 = step_roofline(MIXTRAL_8X7B_BLOCK, 8, 1395.2, 6546.6)
+    assert r1["gemm_ms"] == pytest.approx(69.27e12 / 1395.2e12 * 1e3, rel=1e-3) and r1["a2a_ms"] == 0.0
+    assert r1["adamw_ms"] == pytest.approx(8 * 3 * 4096 * 14336 * 28 / 6546.6e9 * 1e3, rel=1e-6)
+    assert r8["adamw_ms"] == pytest.approx(r1["adamw_ms"] / 8) and r8["a2a_ms"] > 0 and r8["gemm_ms"] == r1["gemm_ms"]
+    assert all(abs(r["total_ms"] - (r["gemm_ms"] + r["adamw_ms"] + r["a2a_ms"])) < 1e-9 for r in (r1, r8))
+    d = step_roofline(DEEPSEEK_V3_MOE_LAYER, 8, 1395.2, 6546.6)
+    assert d["adamw_ms"] == 0.0 and d["a2a_ms"] == pytest.approx(4096 * 8 * 7 / 8 * (7168 + 14336) / 770e9 * 1e3)
