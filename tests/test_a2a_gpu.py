@@ -213,3 +213,18 @@ def test_rail_segments_bit_exact(servers, gpus, kind):
         grp.check()
         for r in range(n):
             assert np.array_equal(d_out[r][: want[r].size].cpu().numpy(), want[r]), f"rank {r} differs"
+
+
+def test_differentiable_all_to_all_on_one_rank():
+    """The autograd wrapper: forward through the plan, gradients back through the transposed plan."""
+    from fast_b200.parallel import Communicator, all_to_all_v
+
+    with Communicator(heap_bytes=32 << 20, device=0) as comm:
+        x = torch.randn(300, 64, device="cuda", dtype=torch.float32, requires_grad=True)
+        y = all_to_all_v(x, comm, np.array([[300]], dtype=np.int64), kind=PlanKind.FANOUT)
+        comm.check()
+        assert y.shape == x.shape and torch.equal(y.detach(), x.detach())
+        w = torch.randn_like(y)
+        (y * w).sum().backward()
+        comm.check()
+        assert torch.equal(x.grad, w)
