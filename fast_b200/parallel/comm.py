@@ -63,10 +63,16 @@ class Schedule:
 
 class Communicator:
     """One rank of an all-to-all domain. Use ``Communicator(group)`` with one process per GPU, or
-    ``LocalGroup`` for several virtual ranks on a single GPU (tests, single-GPU runs)."""
+    ``LocalGroup`` for several virtual ranks on a single GPU (tests, single-GPU runs). With ``store``
+    (any ``torch.distributed`` store shared by the ranks) the IPC handles are exchanged through it
+    with a deadline of ``bootstrap_timeout_s``; every rank must then construct its communicators
+    in the same order."""
+
+    _bootstraps = 0  # generation counter of store-based bootstraps in this process
 
     def __init__(self, group=None, heap_bytes: int = 1 << 30, topo: Optional[Topology] = None, device=None,
-                 timeout_s: Optional[float] = None, ctas: Optional[int] = None, threads: int = 512, _heap=None, _rank=None, _world=None):
+                 timeout_s: Optional[float] = None, ctas: Optional[int] = None, threads: int = 512, store=None,
+                 bootstrap_timeout_s: float = 60.0, _heap=None, _rank=None, _world=None):
         import torch.distributed as dist
 
         self._C = runtime.ext()
@@ -82,8 +88,17 @@ class Communicator:
             self.device = torch.device("cuda", device if device is not None else torch.cuda.current_device())
             self.heap = self._C.SymmHeap(self.rank, self.world, int(heap_bytes), self.device.index)
             if self.world > 1:
-                handles: List[Optional[bytes]] = [None] * self.world
-                dist.all_gather_object(handles, self.heap.ipc_handle(), group=group)
+                if store is not None:
+                    # Exchange through a key-value store with a deadline: a rank that never shows up is
+                    # named in the error instead of blocking everyone in a collective.
+                    from .liveness import bounded_exchange
+
+                    Communicator._bootstraps += 1
+                    handles = bounded_exchange(store, self.rank, self.world, f"fastb/ipc/{Communicator._bootstraps}", self.heap.ipc_handle(),
+                                               timeout_s=bootstrap_timeout_s)
+                else:
+                    handles: List[Optional[bytes]] = [None] * self.world
+                    dist.all_gather_object(handles, self.heap.ipc_handle(), group=group)
                 self.heap.open_peers(handles)
                 dist.barrier(group=group)
         self.topo = topo or Topology.flat(self.world)
