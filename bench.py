@@ -91,7 +91,8 @@ def reference_arm(args):
     why = ("reference (MangoBoost/FAST) has no setup.py/pyproject at its root, so the offline pip install fails; its NVIDIA library does build "
            "for sm_100a with a hand-written nvcc line (baseline/build_ref_nvshmem.sh) but exports only all-to-all self-tests on a self-generated "
            "workload, is a no-op on one server, and contains no MoE layer, GEMM or training step to time")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also when launched with one process per GPU
+        print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
