@@ -196,3 +196,32 @@ def test_step_roofline_adds_up():
     assert all(abs(r["total_ms"] - (r["gemm_ms"] + r["adamw_ms"] + r["a2a_ms"])) < 1e-9 for r in (r1, r8))
     d = step_roofline(DEEPSEEK_V3_MOE_LAYER, 8, 1395.2, 6546.6)
     assert d["adamw_ms"] == 0.0 and d["a2a_ms"] == pytest.approx(4096 * 8 * 7 / 8 * (7168 + 14336) / 770e9 * 1e3)
+
+
+def test_differentiable_all_to_all_wrapper_logic_on_a_stand_in():
+    """The autograd wrapper with a stand-in communicator (identity exchange on one rank): output
+    shape from the plan's sizes, gradient routed through the transposed schedule."""
+    from types import SimpleNamespace
+
+    from fast_b200.parallel import autograd as ag
+
+    class _Comm:
+        def __init__(self):
+            self.calls = []
+
+        def schedule(self, matrix, unit_bytes=1, kind=None, transpose=False):
+            rows = int(np.asarray(matrix).sum())
+            return SimpleNamespace(unit_bytes=unit_bytes, output_bytes=rows * unit_bytes, transpose=transpose)
+
+        def all_to_all_v(self, out, inp, s):
+            self.calls.append(s.transpose)
+            out.view(-1).copy_(inp.reshape(-1))
+            return out
+
+    comm = _Comm()
+    x = torch.randn(30, 8, requires_grad=True)
+    y = ag.all_to_all_v(x, comm, np.array([[30]]), kind="auto")
+    assert y.shape == (30, 8) and torch.equal(y.detach(), x.detach())
+    w = torch.randn(30, 8)
+    (y * w).sum().backward()
+    assert torch.equal(x.grad, w) and comm.calls == [False, True]
