@@ -225,3 +225,41 @@ def test_differentiable_all_to_all_wrapper_logic_on_a_stand_in():
     w = torch.randn(30, 8)
     (y * w).sum().backward()
     assert torch.equal(x.grad, w) and comm.calls == [False, True]
+
+
+def _bare_communicator(rank, world, topo):
+    """A Communicator without a device: enough state for ``schedule`` (planning, validation,
+    lowering, caching); the device program is replaced by a recorder."""
+    from types import SimpleNamespace
+
+    from fast_b200.parallel.comm import Communicator
+
+    c = object.__new__(Communicator)
+    c.rank, c.world, c.topo, c.ctas, c.group = rank, world, topo, 148, None
+    c.plan_cache, c._sched_cache = sched.PlanCache(), {}
+    c.device = SimpleNamespace(index=0)
+    c._C = SimpleNamespace(A2AProgram=lambda items, rail, out, bal, dev: SimpleNamespace(n_items=int(items.shape[0]), rail=list(rail)))
+    return c
+
+
+def test_communicator_schedule_paths_without_a_device():
+    m = sched.workload_uniform(8, 4000, 3, False)
+    c = _bare_communicator(2, 8, Topology(2, 4))
+    s = c.schedule(m, unit_bytes=16, kind=PlanKind.STAGED)
+    assert s.plan.only_rank == -1 and s.program.n_items > 0 and len(s.program.rail) == s.plan.num_stages
+    assert c.schedule(m, unit_bytes=16, kind=PlanKind.STAGED) is s                       # cached
+    seg = c.schedule(m, unit_bytes=16, kind=PlanKind.STAGED, rail_segment_bytes=512)
+    assert seg is not s and len(seg.program.rail) > s.plan.num_stages and sum(seg.program.rail) == sum(s.program.rail)
+    auto = c.schedule(m, unit_bytes=16, kind="auto")
+    assert auto.plan.kind in (PlanKind.FANOUT, PlanKind.STAGED, PlanKind.SINGLE_BURST) and auto.plan.validate() == ""
+    back = c.schedule(m, unit_bytes=16, kind=PlanKind.STAGED, transpose=True)
+    assert back.input_bytes == int(m[:, 2].sum()) * 16 and back.output_bytes == int(m[2].sum()) * 16
+    # beyond 64 ranks a communicator plans a one-rank view, with the same work list as the full plan
+    big = sched.workload_uniform(72, 300, 5, False)
+    c72 = _bare_communicator(7, 72, Topology(9, 8))
+    v = c72.schedule(big, unit_bytes=4, kind=PlanKind.STAGED)
+    full = sched.build_plan(big, Topology(9, 8), split_align=4)
+    assert v.plan.only_rank == 7 and v.plan.num_ops < full.num_ops / 10
+    ref = full.lower(7, 4, 65536)                                                          # 64 KiB work items are what schedule() picks here
+    assert v.lowered["items"].shape == ref["items"].shape and (v.lowered["items"] == ref["items"]).all()
+    assert v.lowered["expect_output_bytes"] == ref["expect_output_bytes"] and v.max_bytes["rail"] == int(full.buffers[:, 3].max()) * 4
