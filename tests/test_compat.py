@@ -263,3 +263,52 @@ def test_communicator_schedule_paths_without_a_device():
     ref = full.lower(7, 4, 65536)                                                          # 64 KiB work items are what schedule() picks here
     assert v.lowered["items"].shape == ref["items"].shape and (v.lowered["items"] == ref["items"]).all()
     assert v.lowered["expect_output_bytes"] == ref["expect_output_bytes"] and v.max_bytes["rail"] == int(full.buffers[:, 3].max()) * 4
+
+
+def test_communicator_launch_arguments_and_close_without_a_device():
+    from types import SimpleNamespace
+
+    from fast_b200.parallel.liveness import PeerLost
+
+    class _Heap:
+        bytes = 1 << 30
+
+        def __init__(self):
+            self.next, self.freed = 256, []
+
+        def alloc(self, n):
+            off, self.next = self.next, self.next + (n + 255) // 256 * 256
+            return off
+
+        def free(self, off):
+            self.freed.append(off)
+
+        def base_ptr(self, rank):
+            return 1 << 40                                   # no CPU tensor lies inside this "slab"
+
+        def tensor(self, off, shape, dtype):
+            return torch.zeros(shape, dtype=dtype)
+
+    c = _bare_communicator(0, 4, Topology(2, 2))
+    c.heap, c.broken, c.liveness, c.liveness_max_age_s, c._staging = _Heap(), False, None, 2.0, {}
+    s = c.schedule(sched.workload_uniform(4, 100, 1, False), unit_bytes=4, kind=PlanKind.STAGED)
+    inp, out = torch.zeros(s.input_bytes, dtype=torch.uint8), torch.zeros(s.output_bytes, dtype=torch.uint8)
+    src, dst, copy_back = c._launch_args(s, out, inp)
+    assert copy_back is not None and src[0] == inp.data_ptr() and dst[0] == 0 and dst[1] == c._staging["recv"][0]
+    assert dst[2] == c._staging["balance"][0] and dst[3] == c._staging["rail"][0] and src[2] == (1 << 40) + dst[2]
+    again = c._launch_args(s, out, inp)
+    assert again[1] == dst and c.heap.freed == []                          # staging is reused, not re-allocated
+    with pytest.raises(ValueError):
+        c._launch_args(s, out[:-1], inp)
+    with pytest.raises(ValueError):
+        c._launch_args(s, out, inp, staging={"rail": torch.zeros(8, dtype=torch.uint8)})   # not symmetric memory
+    c.liveness = SimpleNamespace(require_alive=lambda age: (_ for _ in ()).throw(PeerLost([3], "no heartbeat")), leave=lambda: None)
+    with pytest.raises(PeerLost):
+        c._launch_args(s, out, inp)                                          # a lost peer stops the launch on the host
+    c.liveness = None
+    c.broken = True
+    with pytest.raises(RuntimeError, match="reset"):
+        c._launch_args(s, out, inp)
+    c.broken, c.heap = False, None
+    with pytest.raises(RuntimeError, match="closed"):
+        c._launch_args(s, out, inp)
