@@ -141,7 +141,8 @@ def run(args):
                     variants["nccl_sendrecv"] = lambda: nccl_sendrecv_group(nccl_out, inp, in_splits, out_splits, rank, world)
                 for name, kind, opts in [("ours_fanout", PlanKind.FANOUT, {}), ("ours_staged", PlanKind.STAGED, {}),
                                          ("ours_staged_bottleneck", PlanKind.STAGED, {"match": sched.MatchPolicy.BOTTLENECK}),
-                                         ("ours_spreadout", PlanKind.SPREAD_OUT, {})] + ([("ours_single_burst", PlanKind.SINGLE_BURST, {})] if args.servers else []):
+                                         ("ours_spreadout", PlanKind.SPREAD_OUT, {})] + ([("ours_single_burst", PlanKind.SINGLE_BURST, {})] if args.servers else []) + (
+                                         [("ours_staged_pieces", PlanKind.STAGED, {"rail_segment_bytes": args.rail_segment})] if args.servers and args.rail_segment > 0 else []):
                     s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk or None, **opts)
                     variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
                 if args.p2p_baseline:
@@ -192,6 +193,7 @@ def main():
     ap.add_argument("--p2p-baseline", action="store_true", help="also run the staged plan over NCCL send/recv groups (the reference's executor style)")
     ap.add_argument("--servers", type=int, default=0, help="treat the ranks as this many virtual servers (hierarchical FAST plan + single-burst ablation)")
     ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--rail-segment", type=int, default=0, help="with --servers: also time the staged plan with one arrival counter per this many bytes of rail staging")
     ap.add_argument("--out", default="", help="append every result row to this file (JSON lines)")
     run(ap.parse_args())
 
