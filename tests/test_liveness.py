@@ -51,12 +51,13 @@ def test_heartbeat_sees_silence_and_goodbye():
     [h.start() for h in hbs]
     hbs[0].wait_all_started(timeout_s=2.0)
     time.sleep(0.1)
-    hbs[0].require_alive(max_age_s=0.5)            # everyone beats
+    hbs[0].require_alive(max_age_s=5.0)            # everyone beats
     hbs[1].stop()                                  # rank 1 goes silent (as if its process died)
-    time.sleep(0.3)
-    assert hbs[0].dead_peers(max_age_s=0.2) == [1]
+    hbs[0].poll()
+    time.sleep(1.2)
+    assert hbs[0].dead_peers(max_age_s=0.8) == [1]  # rank 2 beats every 20 ms: far inside the window even on a loaded host
     with pytest.raises(PeerLost) as e:
-        hbs[0].require_alive(max_age_s=0.2)
+        hbs[0].require_alive(max_age_s=0.8)
     assert e.value.ranks == [1] and "no heartbeat" in str(e.value)
     hbs[2].leave()                                 # orderly exit is seen at once, without waiting
     with pytest.raises(PeerLost) as e:
