@@ -85,7 +85,7 @@ hb.wait_all_started(10.0)
 steps = 0
 try:
     for step in range(200):
-        hb.require_alive(max_age_s=0.6)   # the check a rank makes before it launches a collective
+        hb.require_alive(max_age_s=1.5)   # the check a rank makes before it launches a collective
         steps += 1
         if rank == world - 1 and step == 3:
             if mode == "leave":
@@ -96,7 +96,7 @@ try:
 except PeerLost as e:
     print(f"rank {rank} detected {e.ranks} after {steps} steps", flush=True)
     if rank == 0:
-        time.sleep(1.0)                  # keep the store up until the other survivors have reported
+        time.sleep(2.5)                  # keep the store up until the other survivors have reported
 """
 
 
