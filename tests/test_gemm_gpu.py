@@ -139,7 +139,6 @@ def test_dgrad_with_fused_swiglu_backward(kernel_variant):
         _close(got[:, :, 1].reshape(e - s, I), ut.grad)
 
 
-@pytest.mark.xfail(reason="not yet run on a GPU", strict=False)
 def test_custom_operators_run_the_same_kernels():
     """torch.ops.fast_b200.* (schemas, mutation annotations) give the same bits as the direct calls."""
     from fast_b200.ops import gemm, registry  # noqa: F401
