@@ -134,8 +134,9 @@ struct SplitsArgs {
 };
 cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream);
 // list[send_pos[e] + rank of (t, j) among my entries for e] = t*K + j  (see SplitsArgs::send_pos).
+// Entries whose expert id is outside [0, E) are skipped and reported in `status` (kSiteExpertId).
 cudaError_t launch_build_send_list(const int* topk_idx, const int* slot_in_block, const int* block_base, const int* send_pos, int T, int K, int E,
-                                   int* list, cudaStream_t stream);
+                                   int* list, DeviceStatus* status, cudaStream_t stream);
 cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* group_off, const int* group_rows, int groups, cudaStream_t stream);
 
 struct DispatchArgs {

@@ -74,6 +74,10 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
       if (j >= jbeg && j < jend) {
         const long long tj = static_cast<long long>(t) * a.K + j;
         const int e = a.topk_idx[tj];
+        if (e < 0 || e >= E) {  // not an expert: nothing is indexed with it; the step is flagged and the entry skipped
+          if (lane == 0) report_failure(a.status, kStatusBadArg, kSiteExpertId, static_cast<unsigned long long>(tj), static_cast<unsigned long long>(static_cast<unsigned int>(e)), static_cast<unsigned long long>(E));
+          continue;
+        }
         int row;
         if (a.compute_rows) {
           row = a.send_base[e] + a.block_base[static_cast<long long>(t / tpb) * E + e] + a.slot_in_block[tj];
@@ -105,7 +109,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
           if (a.row_scale) unpack8(v[u], f);
 #pragma unroll
           for (int j = 0; j < kMaxK; ++j) {
-            if (j < jbeg || j >= jend) continue;
+            if (j < jbeg || j >= jend || dst[j] == nullptr) continue;
             uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + (static_cast<long long>(row_of[j]) * a.H) * 2) + c;
             if (a.row_scale) {
               float g[8];
@@ -152,7 +156,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
         for (int i = 0; i < 16; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
-          if (j < jbeg || j >= jend || !active) continue;
+          if (j < jbeg || j >= jend || !active || dst[j] == nullptr) continue;
           uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
           *out = q;
           if ((lane & 7) == 0)
@@ -195,6 +199,10 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
       if (j < a.K) {
         const long long tj = static_cast<long long>(t) * a.K + j;
         const int e = a.topk_idx[tj];
+        if (e < 0 || e >= a.num_experts) {  // flagged and left out of the sum (rows[j] stays null)
+          if (lane == 0) report_failure(a.status, kStatusBadArg, kSiteExpertId, static_cast<unsigned long long>(tj), static_cast<unsigned long long>(static_cast<unsigned int>(e)), static_cast<unsigned long long>(a.num_experts));
+          continue;
+        }
         rows[j] = reinterpret_cast<const uint4*>(static_cast<unsigned char*>(a.peer_table[e / El]) + a.src_heap_off +
                                                  static_cast<long long>(a.dest_row[tj]) * a.H * 2);
         w[j] = a.weights ? a.weights[tj] : 1.0f;
@@ -209,7 +217,7 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
         for (int u = 0; u < U; ++u)
 #pragma unroll
           for (int j = 0; j < kMaxK; ++j)
-            if (j < a.K && c0 + 32 * u < chunks) v[u][j] = __ldcg(rows[j] + c0 + 32 * u);
+            if (j < a.K && c0 + 32 * u < chunks) v[u][j] = rows[j] ? __ldcg(rows[j] + c0 + 32 * u) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int c = c0 + 32 * u;
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const Combin
         for (int j = 0; j < kMaxK; ++j) {
           if (j >= a.K) break;
           float f[8];
-          unpack8(__ldcg(rows[j] + c), f);
+          unpack8(rows[j] ? __ldcg(rows[j] + c) : make_uint4(0, 0, 0, 0), f);
 #pragma unroll
           for (int i = 0; i < 8; ++i) dots[j] = fmaf(gf[i], f[i], dots[j]);
         }

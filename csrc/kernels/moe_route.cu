@@ -31,18 +31,27 @@ __global__ void __launch_bounds__(kRouteThreads) route_topk_kernel(const float* 
       continue;
     }
     float sel[MAX_PER_LANE], raw[MAX_PER_LANE];
+    unsigned taken = 0u;  // bit i: candidate lane + 32 i is chosen already, or past the last expert
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
       const int e = lane + 32 * i;
-      raw[i] = e < E ? logits[static_cast<long long>(t) * E + e] : -INFINITY;
-      sel[i] = e < E ? raw[i] + (bias ? bias[e] : 0.0f) : -INFINITY;
-      mx = fmaxf(mx, raw[i]);
+      // NaN logits count as -inf: the selection below stays total and the weights stay finite.
+      float r = e < E ? logits[static_cast<long long>(t) * E + e] : -INFINITY;
+      if (r != r) r = -INFINITY;
+      float s = e < E ? r + (bias ? bias[e] : 0.0f) : -INFINITY;
+      if (s != s) s = -INFINITY;
+      raw[i] = r;
+      sel[i] = s;
+      if (e >= E) taken |= 1u << i;
+      mx = fmaxf(mx, r);
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     // Selection uses logits + bias; the weights are the softmax of the raw logits over the
     // chosen experts (renormalised), which for bias == 0 is Mixtral's softmax-over-top-k.
+    // A token with fewer than K selectable values (-inf / NaN rows, masked experts) still gets K
+    // distinct expert ids in range: the lowest unchosen ids, with weight 0.
     float wsum = 0.0f;
     float my_w = 0.0f;
     int my_e = -1;
@@ -51,25 +60,25 @@ __global__ void __launch_bounds__(kRouteThreads) route_topk_kernel(const float* 
       int best_e = 0x7fffffff;
 #pragma unroll
       for (int i = 0; i < MAX_PER_LANE; ++i)
-        if (sel[i] > best) { best = sel[i]; best_e = lane + 32 * i; }
+        if (!((taken >> i) & 1u) && (best_e == 0x7fffffff || sel[i] > best)) { best = sel[i]; best_e = lane + 32 * i; }
 #pragma unroll
       for (int o = 16; o; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
         const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
       }
-      float r = 0.0f;
+      float r = -INFINITY;
 #pragma unroll
       for (int i = 0; i < MAX_PER_LANE; ++i)
-        if (lane + 32 * i == best_e) { r = raw[i]; sel[i] = -INFINITY; }
+        if (lane + 32 * i == best_e) { r = raw[i]; taken |= 1u << i; }
       r = __shfl_sync(0xffffffffu, r, best_e & 31);
-      const float p = __expf(r - mx);
+      const float p = r > -INFINITY ? __expf(r - mx) : 0.0f;
       wsum += p;
       if (lane == j) { my_w = p; my_e = best_e; }
     }
     if (lane < K) {
       topk_idx[static_cast<long long>(t) * K + lane] = my_e;
-      topk_w[static_cast<long long>(t) * K + lane] = my_w / wsum;
+      topk_w[static_cast<long long>(t) * K + lane] = wsum > 0.0f ? my_w / wsum : 0.0f;
       s_eid[lt * K + lane] = my_e;
     }
   }
@@ -200,10 +209,14 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
 }
 
 __global__ void build_send_list_kernel(const int* __restrict__ topk_idx, const int* __restrict__ slot_in_block, const int* __restrict__ block_base,
-                                       const int* __restrict__ send_pos, int T, int K, int E, int* __restrict__ list) {
+                                       const int* __restrict__ send_pos, int T, int K, int E, int* __restrict__ list, DeviceStatus* status) {
   const long long tj = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (tj >= static_cast<long long>(T) * K) return;
   const int e = topk_idx[tj];
+  if (e < 0 || e >= E) {  // an id no router of this library produces: skip the entry, say so, touch nothing
+    if (status) report_failure(status, kStatusBadArg, kSiteExpertId, static_cast<unsigned long long>(tj), static_cast<unsigned long long>(static_cast<unsigned int>(e)), static_cast<unsigned long long>(E));
+    return;
+  }
   const int t = static_cast<int>(tj / K);
   list[send_pos[e] + block_base[static_cast<long long>(t / kTokensPerBlock) * E + e] + slot_in_block[tj]] = static_cast<int>(tj);
 }
@@ -247,10 +260,10 @@ cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_build_send_list(const int* topk_idx, const int* slot_in_block, const int* block_base, const int* send_pos, int T, int K, int E,
-                                   int* list, cudaStream_t stream) {
+                                   int* list, DeviceStatus* status, cudaStream_t stream) {
   const long long n = static_cast<long long>(T) * K;
   if (n == 0) return cudaSuccess;
-  build_send_list_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(topk_idx, slot_in_block, block_base, send_pos, T, K, E, list);
+  build_send_list_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(topk_idx, slot_in_block, block_base, send_pos, T, K, E, list, status);
   note_launch();
   return cudaGetLastError();
 }
@@ -268,6 +281,7 @@ cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* grou
 // ---------------------------------------------------------------------------------------------
 // Allocation-free entry point (declared in route_noalloc.h).
 // ---------------------------------------------------------------------------------------------
+#include <atomic>
 #include <cstdio>
 
 #include "route_noalloc.h"
@@ -286,7 +300,9 @@ constexpr size_t kNoAllocBytes = kNoAllocCntBytes + kNoAllocSlotBytes;          
 static __device__ __align__(256) unsigned char g_route_scratch[kNoAllocBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices] = {};
+// One address per device, filled by the first call on that device. Atomic: several host threads
+// may make that first call at once (they would all store the same value).
+std::atomic<void*> g_scratch_addr[kMaxDevices] = {};
 thread_local char g_noalloc_error[256] = "";
 
 __global__ void sum_block_counts_kernel(const int* __restrict__ block_cnt, int blocks, int E, int* __restrict__ expert_counts) {
@@ -325,17 +341,19 @@ extern "C" int fastb_route_topk_noalloc(const float* logits, const float* bias, 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return refuse(e, "fastb_route_topk_noalloc: cudaGetDevice failed");
   if (dev < 0 || dev >= kMaxDevices) return refuse(cudaErrorInvalidDevice, "fastb_route_topk_noalloc: device index %d not supported (max %d)", dev, kMaxDevices - 1);
-  if (g_scratch_addr[dev] == nullptr) {
+  void* scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // Once per device, with that device current: translate the symbol into its device address.
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_route_scratch);
     if (e != cudaSuccess || p == nullptr) return refuse(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "fastb_route_topk_noalloc: cudaGetSymbolAddress failed");
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);
+    scratch = p;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   const int blocks = (T + kRouteTokensPerBlock - 1) / kRouteTokensPerBlock;
-  int* block_cnt = reinterpret_cast<int*>(static_cast<unsigned char*>(g_scratch_addr[dev]));
-  int* slot_in_block = reinterpret_cast<int*>(static_cast<unsigned char*>(g_scratch_addr[dev]) + kNoAllocCntBytes);
+  int* block_cnt = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch));
+  int* slot_in_block = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + kNoAllocCntBytes);
   if (blocks > 0) {
     e = launch_route_topk(logits, bias, T, E, K, topk_idx, topk_w, slot_in_block, block_cnt, stream);
     if (e != cudaSuccess) return refuse(e, "fastb_route_topk_noalloc: routing kernel launch failed");

@@ -25,6 +25,9 @@ extern "C" {
 // share the array, so two calls whose kernels may overlap on the GPU (different streams without
 // an ordering between them) race on it; calls on one stream are safe. The array keeps whatever
 // the previous call left; this routine reads no word it has not written in the same call.
+// Host threads: the function may be called from several threads at once (the per-device address
+// cache is atomic and the error text is per thread); the device-side race above still applies to
+// their kernels unless their streams are ordered.
 int fastb_route_topk_noalloc(const float* logits, const float* bias, int T, int E, int K, int* topk_idx, float* topk_w, int* expert_counts,
                              void* stream);
 

@@ -25,7 +25,7 @@ struct DeviceStatus {
 constexpr unsigned long long kStatusOk = 0, kStatusTimeout = 1, kStatusBadArg = 2;
 enum WaitSite : unsigned long long {
   kSiteEntryReady = 1, kSiteBalanceArrive = 2, kSiteRailArrive = 3, kSiteOutputArrive = 4,
-  kSiteCountsArrive = 5, kSiteCombineReady = 6, kSiteReuse = 7, kSiteMbarrier = 8, kSiteTest = 9, kSiteCapacity = 10,
+  kSiteCountsArrive = 5, kSiteCombineReady = 6, kSiteReuse = 7, kSiteMbarrier = 8, kSiteTest = 9, kSiteCapacity = 10, kSiteExpertId = 11,
 };
 
 #ifdef __CUDACC__

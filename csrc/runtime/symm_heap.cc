@@ -43,13 +43,29 @@ std::vector<SymmHeap*> SymmHeap::create_local_group(int world, size_t bytes) {
   return hs;
 }
 
-SymmHeap::~SymmHeap() {
+void SymmHeap::close_peers() {
   for (int r = 0; r < world_; ++r) {
-    if (!peer_base_[r]) continue;
-    if (r == rank_) cudaFree(peer_base_[r]);
-    else if (r < static_cast<int>(ipc_opened_.size()) && ipc_opened_[r]) cudaIpcCloseMemHandle(peer_base_[r]);
+    if (r == rank_ || !peer_base_[r]) continue;
+    if (r < static_cast<int>(ipc_opened_.size()) && ipc_opened_[r]) {
+      cudaIpcCloseMemHandle(peer_base_[r]);
+      ipc_opened_[r] = 0;
+      peer_base_[r] = nullptr;
+    }
   }
-  if (d_table_) cudaFree(d_table_);
+  ipc_opened_.clear();
+}
+
+void SymmHeap::free_local() {
+  if (owns_slab_ && peer_base_[rank_]) cudaFree(peer_base_[rank_]);
+  peer_base_[rank_] = nullptr;
+  if (d_table_) { cudaFree(d_table_); d_table_ = nullptr; }
+}
+
+// Peers are unmapped before the local slab goes. Ranks that want the defined order across
+// processes call close_peers(), meet in a barrier, and then drop the heap.
+SymmHeap::~SymmHeap() {
+  close_peers();
+  free_local();
 }
 
 std::string SymmHeap::ipc_handle() const {

@@ -29,6 +29,14 @@ class SymmHeap {
   std::string ipc_handle() const;                          // 64 raw bytes
   void open_peers(const std::vector<std::string>& handles);  // handles[r] from rank r
 
+  // Two-phase teardown. CUDA leaves freeing an exported allocation undefined while an importer
+  // still has it mapped, so every rank first unmaps its peers (close_peers), the ranks meet in a
+  // host barrier, and only then does anybody free its own slab (free_local, or the destructor).
+  // Both are idempotent; after close_peers the heap can no longer reach a peer.
+  void close_peers();
+  void free_local();
+  bool peers_open() const { return opened_ && world_ > 1 && !ipc_opened_.empty(); }
+
   int rank() const { return rank_; }
   int world() const { return world_; }
   size_t bytes() const { return bytes_; }
@@ -47,6 +55,7 @@ class SymmHeap {
   int rank_ = 0, world_ = 1;
   size_t bytes_ = 0;
   bool opened_ = false;
+  bool owns_slab_ = true;
   std::vector<char> ipc_opened_;  // peers mapped through an IPC handle (closed in the destructor)
   std::vector<void*> peer_base_;
   void** d_table_ = nullptr;

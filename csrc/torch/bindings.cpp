@@ -106,6 +106,7 @@ PYBIND11_MODULE(_C, m) {
       })
       .def("ipc_handle", [](const HeapPy& h) { return py::bytes(h.h->ipc_handle()); })
       .def("open_peers", [](HeapPy& h, std::vector<std::string> handles) { c10::cuda::CUDAGuard g(h.device); h.h->open_peers(handles); })
+      .def("close_peers", [](HeapPy& h) { c10::cuda::CUDAGuard g(h.device); h.h->close_peers(); })
       .def("alloc", [](HeapPy& h, int64_t bytes) { return static_cast<int64_t>(h.h->alloc(static_cast<size_t>(bytes))); })
       .def("free", [](HeapPy& h, int64_t off) { h.h->free(static_cast<size_t>(off)); })
       .def("tensor", &HeapPy::tensor)

@@ -169,12 +169,12 @@ void bind_moe(py::module_& m) {
   m.def("route_topk", &route_topk);
   m.def("splits_scan", &splits_scan);
   m.def("zero_pad_rows", &zero_pad_rows);
-  m.def("build_send_list", [](torch::Tensor topk_idx, torch::Tensor slot_in_block, torch::Tensor block_base, torch::Tensor send_pos, torch::Tensor list) {
+  m.def("build_send_list", [](torch::Tensor topk_idx, torch::Tensor slot_in_block, torch::Tensor block_base, torch::Tensor send_pos, torch::Tensor list, const StatusPy& st) {
     want(topk_idx, torch::kInt32, "topk_idx"); want(send_pos, torch::kInt32, "send_pos"); want(list, torch::kInt32, "list");
     TORCH_CHECK(list.numel() >= topk_idx.numel(), "build_send_list: list too short");
     cu_check(launch_build_send_list(topk_idx.data_ptr<int>(), slot_in_block.data_ptr<int>(), block_base.data_ptr<int>(), send_pos.data_ptr<int>(),
                                     static_cast<int>(topk_idx.size(0)), static_cast<int>(topk_idx.size(1)), static_cast<int>(send_pos.numel()),
-                                    list.data_ptr<int>(), stream_now()), "build_send_list");
+                                    list.data_ptr<int>(), st.d, stream_now()), "build_send_list");
   });
   m.def("dispatch_push", &dispatch_push);
   m.def("combine_pull", &combine_pull);

@@ -321,16 +321,23 @@ class Communicator:
         self.broken = False
 
     def close(self) -> None:
-        """Collective: every rank calls it after its last collective. Synchronises the device,
-        waits for the peers (nobody unmaps memory a peer may still write), stops an attached
-        heartbeat and lets go of the symmetric heap; the slab and the peer mappings are released
-        when the last tensor carved from the heap is gone. The communicator is unusable afterwards."""
+        """Collective: every rank calls it after its last collective. Teardown has two phases, because
+        freeing a slab that a peer still has mapped is undefined in CUDA: (1) synchronise the device,
+        meet the peers (nobody unmaps memory a peer may still write), unmap every peer's slab;
+        (2) meet again, then let go of the local heap - its slab is freed once the last tensor
+        carved from it is gone, which by then no peer can see. Stops an attached heartbeat. The
+        communicator is unusable afterwards."""
         import torch.distributed as dist
 
         if self.heap is None:
             return
+        multi = self.group is not None or (dist.is_initialized() and self.world > 1 and not self._virtual)
         torch.cuda.synchronize(self.device)
-        if self.group is not None or (dist.is_initialized() and self.world > 1):
+        if multi:
+            dist.barrier(group=self.group)
+        if not self._virtual:
+            self.heap.close_peers()
+        if multi:
             dist.barrier(group=self.group)
         if self.liveness is not None:
             self.liveness.leave()

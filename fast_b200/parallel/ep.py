@@ -185,7 +185,7 @@ class ExpertParallel:
             x.record_stream(self.side)
             ctx = torch.cuda.stream(self.side)
             ctx.__enter__()
-            C.build_send_list(rs.topk_idx, rs.slot_in_block, rs.block_base, self.send_pos, self.send_list)
+            C.build_send_list(rs.topk_idx, rs.slot_in_block, rs.block_base, self.send_pos, self.send_list, self.status)
             send_list = self.send_list
         try:
             if self.fp8:

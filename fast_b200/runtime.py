@@ -34,7 +34,7 @@ def available() -> bool:
 
 
 SITE_NAMES = {1: "entry-ready", 2: "balance-arrival", 3: "rail-arrival", 4: "output-arrival", 5: "counts-arrival",
-              6: "combine-ready", 7: "buffer-reuse", 8: "mbarrier", 9: "test-probe", 10: "receive-capacity"}
+              6: "combine-ready", 7: "buffer-reuse", 8: "mbarrier", 9: "test-probe", 10: "receive-capacity", 11: "expert-id"}
 
 
 class CollectiveTimeout(RuntimeError):
@@ -44,5 +44,7 @@ class CollectiveTimeout(RuntimeError):
         self.code, self.site, self.detail, self.seen, self.want = code, site, detail, seen, want
         if site == 10:
             super().__init__(f"MoE step refused: a rank needs {seen} receive rows but capacity_rows is {want}")
+        elif site == 11:
+            super().__init__(f"MoE step refused: routing entry {detail} names expert {seen if seen < 2**31 else seen - 2**32}, outside 0..{want - 1}")
         else:
             super().__init__(f"device wait gave up at {SITE_NAMES.get(site, site)} (detail {detail}): saw {seen}, wanted {want}")

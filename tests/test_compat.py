@@ -312,3 +312,38 @@ def test_communicator_launch_arguments_and_close_without_a_device():
     c.broken, c.heap = False, None
     with pytest.raises(RuntimeError, match="closed"):
         c._launch_args(s, out, inp)
+
+
+def test_close_unmaps_peers_between_two_barriers_before_the_slab_goes(monkeypatch):
+    """Teardown order across ranks: sync, barrier, unmap peers, barrier, and only then drop the heap
+    (whose destructor frees the local slab). A peer that still had the slab mapped when its owner
+    freed it would be undefined behaviour in CUDA."""
+    import torch.distributed as dist
+
+    log = []
+
+    class _Heap:
+        def close_peers(self):
+            log.append("close_peers")
+
+        def __del__(self):
+            log.append("free_local")
+
+    c = _bare_communicator(1, 4, Topology.flat(4))
+    c.heap, c.group, c._virtual, c.liveness, c._staging, c.broken = _Heap(), object(), False, None, {}, False
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda dev=None: log.append("sync"))
+    monkeypatch.setattr(dist, "barrier", lambda group=None: log.append("barrier"))
+    c.close()
+    import gc
+
+    gc.collect()
+    assert log == ["sync", "barrier", "close_peers", "barrier", "free_local"]
+    c.close()                                                   # idempotent: nothing more happens
+    assert log[-1] == "free_local" and len(log) == 5
+    # virtual ranks of an in-process group share one address space: no mappings to close, no barrier
+    v = _bare_communicator(0, 2, Topology.flat(2))
+    v.heap, v.group, v._virtual, v.liveness, v._staging, v.broken = _Heap(), None, True, None, {}, False
+    del log[:]
+    v.close()
+    gc.collect()
+    assert log == ["sync", "free_local"]

@@ -68,6 +68,65 @@ def test_route_topk_matches_torch(E, K):
         seen[e] = seen.get(e, 0) + 1
 
 
+def test_route_topk_is_total_on_nan_inf_and_masked_rows():
+    """Rows of NaN, of -inf, or with fewer than K selectable experts still get K distinct ids inside
+    [0, E) and finite weights; rows with enough finite values route exactly like PyTorch."""
+    from fast_b200 import runtime
+
+    C = runtime.ext()
+    T, E, K = 256, 64, 6
+    g = torch.Generator(device="cuda").manual_seed(9)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    logits[0] = float("nan")
+    logits[1] = float("-inf")
+    logits[2, 3:] = float("-inf")            # three selectable experts, K = 6
+    logits[3, ::2] = float("nan")            # half the experts unusable, still >= K finite
+    logits[4, 5] = float("inf")
+    idx = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, K, dtype=torch.float32, device="cuda")
+    slot = torch.zeros(256, K, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(2, E, dtype=torch.int32, device="cuda")
+    C.route_topk(logits, None, K, idx, w, slot, cnt)
+    torch.cuda.synchronize()
+    assert int(idx.min()) >= 0 and int(idx.max()) < E
+    assert all(len(set(r)) == K for r in idx[:8].cpu().tolist())
+    assert bool(torch.isfinite(w[[0, 1, 2, 3] + list(range(5, T))]).all())
+    assert float(w[0].abs().sum()) == 0.0 and float(w[1].abs().sum()) == 0.0
+    assert sorted(idx[2, :3].cpu().tolist()) == [0, 1, 2] and abs(float(w[2, :3].sum()) - 1.0) < 1e-5 and float(w[2, 3:].abs().sum()) == 0.0
+    assert all(e % 2 == 1 for e in idx[3].cpu().tolist())
+    ref = logits[5:].topk(K, dim=-1).indices
+    assert torch.equal(idx[5:].long(), ref)
+    assert int(cnt.sum()) == T * K
+
+
+def test_expert_ids_out_of_range_are_skipped_and_reported():
+    """Routing tables that name an expert outside [0, E) (a caller's own router gone wrong) are not
+    used as indices: the entries are skipped, the status block names the site, the context lives."""
+    from fast_b200 import runtime
+    from fast_b200.models import MoELayer
+    from fast_b200.parallel import Communicator
+
+    comm = Communicator(heap_bytes=128 << 20, device=0)
+    layer = MoELayer(comm, 256, 256, 4, 2, max_tokens=512, training=False)
+    eng = layer.engine
+    x = torch.randn(300, 256, device="cuda").to(torch.bfloat16)
+    rs = eng.route((x @ layer.gate.t()).float())
+    rs.topk_idx[7, 1] = 0x7FFFFFFF
+    rs.topk_idx[9, 0] = -3
+    eng.dispatch(x, rs)
+    with pytest.raises(runtime.CollectiveTimeout) as e:
+        comm.check()
+    assert e.value.code == 2 and e.value.site == 11 and e.value.want == 4
+    comm.reset()
+    out = torch.empty(300, 256, dtype=torch.bfloat16, device="cuda")
+    eng._C.combine_pull(comm.heap, eng.E, rs.topk_idx, rs.dest_row, rs.topk_w, eng._off(eng.y), eng._flag_off(1), 0, out, None, None, eng.H, eng.status,
+                        eng.timeout_ns, 8, 0)
+    with pytest.raises(runtime.CollectiveTimeout) as e:
+        comm.check()
+    assert e.value.site == 11
+    assert int((torch.ones(8, device="cuda") * 3).sum().item()) == 24  # context still healthy
+
+
 def test_elementwise_kernels():
     from fast_b200 import runtime
     from fast_b200.models.moe import split_gate_up

@@ -4,7 +4,7 @@ Some hosts cannot call cudaMalloc while they use this library (a server that own
 through its own pool, a latency-critical thread that must not take allocator locks). For them
 `fastb_route_topk_noalloc` keeps its intermediate tables in a fixed array inside the library. This
 test calls it with ctypes, twice in a row with different inputs, and compares with the regular
-routing entry point. It is collected last so that a failure here cannot hide other results.
+routing entry point and with a plain PyTorch top-k. It is collected last so that a failure here cannot hide other results.
 """
 import ctypes
 
@@ -60,6 +60,11 @@ def test_no_alloc_route_matches_regular_twice():
         assert torch.allclose(w, rw, atol=1e-6, rtol=0)
         assert torch.equal(counts, rcounts)
         assert int(counts.sum()) == T * K
+        # Independent of this library: top-k of (logits + bias) in PyTorch, softmax of the raw logits over it.
+        ref = (logits + bias).topk(K, dim=-1).indices
+        assert torch.equal(idx.long(), ref)
+        assert torch.allclose(w, torch.softmax(logits.gather(1, ref), dim=-1), atol=1e-5, rtol=0)
+        assert torch.equal(counts.long(), torch.bincount(ref.reshape(-1), minlength=E))
 
 
 def test_no_alloc_route_rejects_oversize():
