@@ -86,13 +86,55 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+REF_NO_HEADLINE = ("the reference (MangoBoost/FAST) has no MoE layer, GEMM or training step, so the headline metric cannot be run on it; its root has no "
+                   "setup.py/pyproject (the offline pip install fails) and its NVIDIA library, built for sm_100a from the unmodified sources by "
+                   "baseline/build_ref_nvshmem.sh, exports only all-to-all self-tests on a self-generated workload")
+
+
 def reference_arm(args):
-    """The reference's own build cannot run this metric here; say why in one line and exit 0."""
-    why = ("reference (MangoBoost/FAST) has no setup.py/pyproject at its root, so the offline pip install fails; its NVIDIA library does build "
-           "for sm_100a with a hand-written nvcc line (baseline/build_ref_nvshmem.sh) but exports only all-to-all self-tests on a self-generated "
-           "workload, is a no-op on one server, and contains no MoE layer, GEMM or training step to time")
-    if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also when launched with one process per GPU
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    """Runs the UNMODIFIED reference library (baseline/_ref/nv_build/libflash.so) through its own stock
+    path, ``flash_comm_t.test_flash_alltoall()`` (nvidia/alltoall_nvshmem.cpp:563-601): one process per
+    GPU, every GPU a server of its own, the reference's own workload generator, warm-up and timing.
+    The training headline has no counterpart there, so the line keeps ``unavailable`` for it and
+    carries the reference's all-to-all(v) result in ``alltoallv_reference_workload``; the same key of
+    the other arm is this runtime on the identical matrix. With one GPU the reference's scheduler is a
+    no-op and its tester would dereference a null scheduler (:551, :576), so nothing is run."""
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    n = args.gpus
+    out = {"impl": "reference", "unavailable": REF_NO_HEADLINE, "n_gpus": n}
+    lib = os.path.join(ROOT, "baseline", "_ref", "nv_build", "libflash.so")
+    if n < 2:
+        out["alltoallv_reference_workload"] = None
+        out["unavailable"] += "; on one GPU its scheduler does nothing and test_flash_alltoall would dereference a null scheduler"
+    elif not os.path.exists(lib):
+        out["alltoallv_reference_workload"] = None
+        out["unavailable"] += "; baseline/_ref/nv_build/libflash.so is not built on this machine"
+    else:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import run_ref_flash as ref
+
+        port = int(os.environ.get("MASTER_PORT", "29500")) + 17      # the launcher's own store keeps MASTER_PORT
+        if world == n:                                                 # one process per GPU already: this process runs its rank
+            results = [ref.spawn_rank(rank, n, "flash", port, args.ref_timeout)]
+        else:                                                          # plain launch: start every rank from here
+            from concurrent.futures import ThreadPoolExecutor
+
+            with ThreadPoolExecutor(max_workers=n) as ex:
+                results = list(ex.map(lambda r: ref.spawn_rank(r, n, "flash", port, args.ref_timeout), range(n)))
+        rc = max(code for code, _ in results)
+        text = "".join(o for _, o in results)
+        if rank == 0:
+            res = ref.parse(text)
+            if rc == 0 and "algbw_GBps" in res:
+                res.update(workload="uniform_distribution(2**23) x 8-byte units (nvidia/alltoall_nvshmem.cpp:565-569)", warmup=50, iters=50,
+                           servers=n, gpus_per_server=1, timing="the reference's own CUDA events (perf_flash)")
+                out["alltoallv_reference_workload"] = res
+            else:
+                out["alltoallv_reference_workload"] = None
+                out["unavailable"] += f"; its test_flash_alltoall run ended with code {rc}" + (" (stopped at the timeout)" if rc == 124 else "")
+                out["reference_output_tail"] = text[-1500:]
+    if rank == 0:  # one line per job, also when launched with one process per GPU
+        print(json.dumps(out), flush=True)
     return 0
 
 
@@ -102,12 +144,14 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ref-timeout", type=float, default=420.0, help="--impl reference: seconds before the reference's processes are stopped")
     ap.add_argument("--seqs", type=int, default=SEQS)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
     ap.add_argument("--hidden", type=int, default=HIDDEN, help="model width (default: the benchmark's 4096; smaller only for profiling runs)")
     ap.add_argument("--ffn", type=int, default=FFN, help="expert FFN width (default: the benchmark's 14336)")
     ap.add_argument("--capacity-factor", type=float, default=0.0, help="receive rows per rank as a multiple of tokens*top_k (0 = worst case)")
     ap.add_argument("--early-step", action="store_true", help="apply W2's AdamW update inside the backward pass on a side stream (measured neutral under the 1000 W cap)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the torch + NCCL arm of the same step (vs_baseline becomes null)")
     ap.add_argument("--no-extras", action="store_true", help="skip the sub-metrics measured after the training benchmark (skewed all-to-all(v) vs NCCL when N > 1; MoE forward dispatch+combine)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -206,13 +250,35 @@ def main():
         a2av = skewed_point(comm, 256 << 20, 1.0, matrices=3, iters=5, warmup=3)
         a2av["speedup_vs_nccl"] = round(a2av["nccl_alltoallv"]["ms"] / min(a2av["ours_fanout"]["ms"], a2av["ours_staged"]["ms"]), 3)
 
+    # ---- the reference's own tester workload (its rand() matrix, 8-byte units) on this runtime: the other arm's key of the same name ----
+    ref_wl = None
+    if world > 1 and not args.no_extras:
+        from fast_b200.compat import FlashComm
+        from fast_b200.sched import PlanKind
+
+        fc = FlashComm(rank, world, world, comm=comm, generator="glibc", quiet=True)
+        staged = fc.test_flash_alltoall(warmup=20, iters=50)
+        fanout = fc._run(PlanKind.FANOUT, 8, 20, 50, "fanout")
+        best = min(staged, fanout, key=lambda r: r["time_ms"])
+        ref_wl = {"algbw_GBps": round(best["algbw_GBps"], 2), "time_ms": round(best["time_ms"], 4), "per_gpu_MB": round(best["per_gpu_MB"], 3),
+                  "verified": staged["verified"] and fanout["verified"], "staged_ms": round(staged["time_ms"], 4), "fanout_ms": round(fanout["time_ms"], 4),
+                  "workload": "uniform_distribution(2**23) x 8-byte units, the reference tester's matrix (nvidia/alltoall_nvshmem.cpp:565-569)",
+                  "warmup": 20, "iters": 50, "timing": "CUDA events around 50 collectives, max over ranks"}
+
+    # ---- library arm of the same training step: torch ops (cuBLAS) + NCCL all-to-all + torch AdamW, same data, same process ----
+    del model, opt_experts, opt_repl
+    torch.cuda.empty_cache()
+    baseline = None
+    if not args.no_baseline:
+        from fast_b200.bench import torch_block
+
+        baseline = torch_block.measure(dev_ids, steps=min(args.steps, 5), warmup=3, hidden=args.hidden, inter=args.ffn, num_experts=EXPERTS, top_k=TOP_K, vocab=VOCAB)
+
     # ---- MoE forward sub-metric: dispatch + combine latency on DeepSeek-V3-like shapes, fp8 dispatch ----
     moe_fwd = None
     if not args.no_extras:
         from fast_b200.bench import moe_fwd as mf
 
-        del model, opt_experts, opt_repl
-        torch.cuda.empty_cache()
         comm2 = Communicator(heap_bytes=mf.heap_bytes_needed(world, 4096, 7168, 8, 32, True), device=local, timeout_s=20.0)
         moe_fwd = mf.measure(comm2, fp8=True, iters=10, warmup=3, skip_nccl=True)
 
@@ -225,7 +291,8 @@ def main():
     if rank == 0:
         out = {
             "metric": "moe_block_train_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": round(value / baseline["tokens_per_s"], 3) if baseline else None,
             "dtype": "bf16", "data": "synthetic (seeded random token ids, random-init weights)",
             "config": {"model": f"Mixtral-8x7B-shaped MoE block (hidden {args.hidden}, FFN {args.ffn} SwiGLU, 8 experts, top-2)", "global_batch": args.seqs * world,
                        "seq_len": args.seq_len, "parallelism": f"ep{world}", "tokens_per_gpu": tokens,
@@ -236,7 +303,9 @@ def main():
             "clocks": clocks,
             "e2e": {"value": round(total_tokens / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / args.steps, 3),
                     "h2d_bytes_per_step": host_ids[0].numel() * host_ids[0].element_size(), "d2h_bytes_per_step": 4, "last_loss": last},
+            "baseline": baseline,
             "alltoallv_skewed": a2av,
+            "alltoallv_reference_workload": ref_wl,
             "moe_forward_fp8_dispatch": moe_fwd,
             "gpu_launches": int(launches),
             "gpu_launches_per_step": launches / max(args.steps, 1),

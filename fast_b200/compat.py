@@ -163,6 +163,26 @@ def pattern_words(src: int, dst: int, count: int, device) -> torch.Tensor:
     return idx | ((src << 24) | (dst << 16))
 
 
+def reference_uniform_workload(world: int, bound: int = 1 << 23) -> np.ndarray:
+    """The matrix the reference's tester runs on: ``uniform_distribution(workload, n, 2**23)``
+    (nvidia/alltoall_nvshmem.cpp:111-123, called at :510 and :565) draws ``rand() % bound`` for
+    every (i, j) in row-major order from the C library's generator, which the reference never
+    seeds (so it starts from seed 1), rounds each entry up to a multiple of 512 and clears the
+    diagonal. Reproduced here through the same C library so that both runtimes can be timed on
+    the identical workload."""
+    import ctypes
+
+    libc = ctypes.CDLL("libc.so.6")
+    libc.rand.restype = ctypes.c_int
+    libc.srand(1)
+    m = np.zeros((world, world), dtype=np.int64)
+    for i in range(world):
+        for j in range(world):
+            m[i, j] = ((libc.rand() % bound) + 0x1FF) & ~0x1FF
+    np.fill_diagonal(m, 0)
+    return m
+
+
 class FlashComm:
     """The reference's NVIDIA tester class (``flash_comm_t(rank, dev_n, world_size, uid)`` with
     ``test_basic_alltoall()`` and ``test_flash_alltoall()``, nvidia/alltoall_nvshmem.cpp:390-601) on
@@ -172,9 +192,12 @@ class FlashComm:
     ``{"time_ms", "algbw_GBps", "per_gpu_MB", "verified"}``; rank 0 also prints them."""
 
     def __init__(self, rank: int, dev_n: int, world_size: int, uid=None, *, comm=None, mean_units: int = 1 << 23,
-                 heap_bytes: Optional[int] = None, seed: int = 1):
+                 heap_bytes: Optional[int] = None, seed: int = 1, generator: str = "seeded", quiet: bool = False):
         self.rank, self.dev_n, self.world = int(rank), int(dev_n), int(world_size)
         self.mean_units, self.seed = int(mean_units), int(seed)
+        self.quiet = quiet
+        assert generator in ("seeded", "glibc")
+        self.generator = generator  # "glibc": the very matrix the reference's tester draws (see reference_uniform_workload)
         if comm is None:
             from .parallel import Communicator
 
@@ -188,7 +211,10 @@ class FlashComm:
 
         from . import sched
 
-        m = torch.from_numpy(np.ascontiguousarray(sched.workload_uniform(self.world, 2 * self.mean_units, self.seed, False)))
+        if self.generator == "glibc":
+            m = torch.from_numpy(reference_uniform_workload(self.world, 2 * self.mean_units))
+        else:
+            m = torch.from_numpy(np.ascontiguousarray(sched.workload_uniform(self.world, 2 * self.mean_units, self.seed, False)))
         if self.world > 1:
             dev = self.comm.device if dist.get_backend() == "nccl" else torch.device("cpu")
             t = m.to(dev)
@@ -225,7 +251,7 @@ class FlashComm:
         total = int(m.sum()) * data_size
         res = {"time_ms": float(ms.item()), "algbw_GBps": total / self.world / (float(ms.item()) * 1e-3) / 1e9 if ms.item() > 0 else 0.0,
                "per_gpu_MB": total / self.world / 1e6, "verified": bool(ok.item())}
-        if self.rank == 0:
+        if self.rank == 0 and not self.quiet:
             print(f"per-GPU size: {res['per_gpu_MB']:.1f} MB, {name} algbw: {res['algbw_GBps']:.1f} GBps, total time: {res['time_ms']:.3f} ms, "
                   f"verified: {res['verified']}", flush=True)
         return res

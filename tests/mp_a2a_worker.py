@@ -12,6 +12,52 @@ from fast_b200.parallel import Communicator  # noqa: E402
 from fast_b200.sched import PlanKind, Topology  # noqa: E402
 
 
+def compat_on_real_peers(rank, world):
+    """The reference-shaped classes on real peers: flash_t's token-unit schedule / all_to_all /
+    all_to_all_2 / all_to_all_v against torch.distributed.all_to_all_single, forward and transposed,
+    and the tester class with the reference's own workload generator."""
+    from fast_b200.compat import FlashAllToAll, FlashComm, code_of
+
+    hidden = 64
+    server_n = 2 if world % 2 == 0 and world >= 4 else world
+    fa = FlashAllToAll(rank, world, server_n, world // server_n, hidden, code_of(torch.bfloat16), heap_bytes=256 << 20)
+    m = sched.workload_zipf_rows(world, 0.8, 3000, 11, 1)        # tokens
+    for backward in (0, 1):
+        mm = m.T if backward else m
+        fa.schedule(m.reshape(-1), backward)
+        x = torch.randn(int(mm[rank].sum()), hidden, device="cuda", generator=torch.Generator(device="cuda").manual_seed(100 + rank)).to(torch.bfloat16)
+        ref = torch.empty(int(mm[:, rank].sum()), hidden, device="cuda", dtype=torch.bfloat16)
+        dist.all_to_all_single(ref, x, [int(v) for v in mm[:, rank]], [int(v) for v in mm[rank]])
+        y = torch.zeros_like(ref)
+        fa.init_buffers(x, y)                                     # library-owned receive staging
+        fa.all_to_all()
+        fa.comm.check()
+        assert torch.equal(y, ref), f"flash_t.all_to_all backward={backward} rank {rank}"
+        fa.free_buffers()
+        szs = fa.get_buffer_szs()
+        y2 = fa.comm.alloc((max(ref.shape[0], 1), hidden), torch.bfloat16)   # caller-owned, symmetric: written in place by the peers
+        lbrecv = fa.comm.alloc((max(int(szs[2]), 1), hidden), torch.bfloat16)
+        cros = fa.comm.alloc((max(int(szs[3]), 1), hidden), torch.bfloat16)
+        y2.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        fa.all_to_all_2(x, y2, None, None, lbrecv, cros, None, None)
+        fa.comm.check()
+        assert torch.equal(y2[: ref.shape[0]], ref), f"flash_t.all_to_all_2 backward={backward} rank {rank}"
+        y3 = torch.zeros_like(ref)
+        fa.all_to_all_v(x, y3, [int(v) for v in mm[rank]], [int(v) for v in mm[:, rank]])
+        fa.comm.check()
+        assert torch.equal(y3, ref), f"flash_t.all_to_all_v backward={backward} rank {rank}"
+        torch.cuda.synchronize()
+        dist.barrier()
+        for t in (cros, lbrecv, y2):
+            fa.comm.free(t)
+    fc = FlashComm(rank, world, world, comm=fa.comm, mean_units=1 << 14, generator="glibc", quiet=True)
+    r1, r2 = fc.test_flash_alltoall(warmup=2, iters=3), fc.test_basic_alltoall(warmup=2, iters=3)
+    assert r1["verified"] and r2["verified"] and r1["time_ms"] > 0, (r1, r2)
+    dist.barrier()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -47,6 +93,7 @@ def main():
         assert torch.equal(y.cpu(), ref)
         comm.free(out)
         dist.barrier()
+    compat_on_real_peers(rank, world)
     if rank == 0:
         print("A2A_MP_OK")
     dist.destroy_process_group()
