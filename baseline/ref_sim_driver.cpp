@@ -1,6 +1,6 @@
 // Driver around the UNMODIFIED reference simulator sources (simulation/algorithm, simulation/scheduler):
 // reads "servers gpus inter_alpha inter_beta intra_alpha intra_beta mb_per_unit" and the n*n matrix
-// from stdin, runs the reference's own SDSM + Birkhoff decomposition and its pipeline2 cost model,
+// from stdin, runs the reference's own SDSM + Birkhoff decomposition and its pipeline / pipeline2 / pipeline3 cost models,
 // and prints one JSON line. Built by baseline/build_ref_sim.sh with
 // `-include cstring -include cstdint` (the reference omits those headers); nothing of the
 // reference is copied into this repository.
@@ -49,9 +49,17 @@ int main() {
   const double full_mesh = with_fabric(&intra_transfer_full_mesh);
   const double ring2 = G == 8 ? with_fabric(&intra_transfer_2ring) : -1.0;
   const double cube = G == 8 ? with_fabric(&intra_transfer_hybrid_cude_mesh) : -1.0;
+  // pipeline = the first variant: balance per stage instead of once up front. Fresh schedulers again.
+  double pipeline1 = -1.0;
+  {
+    std::vector<LocalScheduler*> ls;
+    for (unsigned s = 0; s < S; ++s) ls.push_back(new LocalScheduler(m.data() + static_cast<size_t>(s) * G * n, G, S, s, intra));
+    GlobalScheduler g1(S, G, ls, inter, intra, false, mbpu);
+    pipeline1 = g1.pipeline(mbpu).t;
+  }
   const double spread = spread_out_baseline(m.data(), S, G, inter, intra, mbpu);
   printf("{\"stages\":%zu,\"freq_sum\":%llu,\"exact\":%s,\"decompose_us\":%.2f,\"pipeline2_us\":%.4f,\"spread_out_us\":%.4f,"
-         "\"pipeline3_full_mesh_us\":%.4f,\"pipeline3_2ring_us\":%.4f,\"pipeline3_hybrid_cube_mesh_us\":%.4f}\n", a2a.p_sets.size(), freq_sum,
-         exact ? "true" : "false", std::chrono::duration<double, std::micro>(t1 - t0).count(), r.t, spread, full_mesh, ring2, cube);
+         "\"pipeline1_us\":%.4f,\"pipeline3_full_mesh_us\":%.4f,\"pipeline3_2ring_us\":%.4f,\"pipeline3_hybrid_cube_mesh_us\":%.4f}\n", a2a.p_sets.size(), freq_sum,
+         exact ? "true" : "false", std::chrono::duration<double, std::micro>(t1 - t0).count(), r.t, spread, pipeline1, full_mesh, ring2, cube);
   return 0;
 }

@@ -96,9 +96,11 @@ cudaError_t launch_grouped_gemm(GemmMode mode, GemmEpilogue epi, const CUtensorM
                                 int ctas, cudaStream_t stream);
 // CTA-pair variant (256 x 256 tiles, cta_group::2). Group offsets must be multiples of 256,
 // fixed_m_tiles counts 256-row tiles, and operand B's boxes are forward {64,128}; dgrad / wgrad
-// boxes are as above.
-cudaError_t launch_grouped_gemm_pair(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
-                                     int ctas, cudaStream_t stream);
+// boxes are as above. Outputs leave through TMA stores: map_c describes args.c and map_c2
+// (null exactly when args.c2 is null) describes args.c2, both with boxes {64,128}; for the fused
+// SwiGLU backward map_c2 is the saved gate|up matrix, which the epilogue TMA-loads.
+cudaError_t launch_grouped_gemm_pair(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                                     const CUtensorMap* map_c2, const GemmArgs& args, int ctas, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // MoE routing / dispatch / combine

@@ -12,9 +12,11 @@
 //   empty[s]     each CTA: released by the leader's commit, multicast to both CTAs.
 //   acc_full[a]  each CTA: leader's commit after the last k step, multicast to both.
 //   acc_empty[a] leader only: 8 arrivals (4 epilogue warps of each CTA; the peer's arrive remotely).
-// Same modes, epilogues, arrival gate and bounded waits as the one-CTA kernel; group offsets must
-// be multiples of 256.
-#include "gemm_common.cuh"
+//   epi_load     each CTA: bytes of the saved gate|up tiles the fused SwiGLU-backward epilogue loads.
+// Same modes, arrival gate and bounded waits as the one-CTA kernel; group offsets must be multiples
+// of 256. The epilogues leave through a two-buffer shared-memory ring and TMA stores
+// (gemm_epilogue_tma.cuh): output matrices are described by tensor maps of 64 x 128 boxes.
+#include "gemm_epilogue_tma.cuh"
 
 namespace fastb {
 
@@ -36,11 +38,11 @@ constexpr int kThreads = 192;
 constexpr int kEpiWarps = 4;
 
 struct __align__(8) SmemCtl {
-  uint64_t full[kStages], empty[kStages], acc_full[kAccStages], acc_empty[kAccStages];
+  uint64_t full[kStages], empty[kStages], acc_full[kAccStages], acc_empty[kAccStages], epi_load;
   uint32_t tmem_base;
   int abort_flag;
 };
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + sizeof(SmemCtl);
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + sizeof(SmemCtl);
 static_assert(kSmemBytes <= 227 * 1024, "dynamic shared memory of one CTA on sm_100a");
 static_assert(kABytes % 1024 == 0 && kBBytes % 1024 == 0, "operand tiles start on 1024-byte boundaries (128-byte swizzle atoms)");
 static_assert(kAccStages * BN <= kTmemCols && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tensor memory columns: power of two, at most 512");
@@ -49,10 +51,12 @@ static_assert(kThreads == 32 * (2 + kEpiWarps) && kEpiWarps == 4, "warp roles: p
 
 template <GemmMode MODE, GemmEpilogue EPI>
 __global__ void __launch_bounds__(kThreads, 1)
-grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs p) {
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                         const __grid_constant__ CUtensorMap map_c2, const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(tiles + kStages * kStageBytes);
+  uint8_t* epi_stage = tiles + kStages * kStageBytes;  // two 16 KiB buffers, 1024-byte aligned like the operand tiles
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(epi_stage + kEpiBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_cta_rank();  // 0 = leader
   const bool leader = cta == 0;
@@ -62,10 +66,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
     for (int a = 0; a < kAccStages; ++a) { mbar_init(&ctl->acc_full[a], 1); mbar_init(&ctl->acc_empty[a], 2 * kEpiWarps); }
+    mbar_init(&ctl->epi_load, 1);
     ctl->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&map_a);
     prefetch_tmap(&map_b);
+    prefetch_tmap(&map_c);
+    if (EPI != GemmEpilogue::kStore) prefetch_tmap(&map_c2);
   }
   if (warp == 1) { tmem_alloc_pair(&ctl->tmem_base, kTmemCols); tmem_relinquish_pair(); }
   tc_fence_before_sync();
@@ -154,7 +161,9 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else {
     // ---------------- epilogue (both CTAs, each for its 128 rows) ----------------
     const int quarter = warp & 3;
-    uint32_t acc_it = 0;
+    const int r = quarter * 32 + lane;  // my accumulator row inside this CTA's half
+    EpiRing ring{epi_stage, threadIdx.x == 64, 0u};
+    uint32_t acc_it = 0, load_phase = 0;
     bool ok = true;
     for (int tile = pair; ok && walk.locate(tile, tc); tile += pairs) {
       const int a = acc_it % kAccStages;
@@ -165,18 +174,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (!(ok = mbar_wait_bounded(&ctl->acc_full[a], aph, abort_flag, p.status, 400 + a, p.timeout_ns))) break;
         tc_fence_after_sync();
       }
-      const int row_in_tile = static_cast<int>(cta) * PM + quarter * 32 + lane;
-      const long long c_row = MODE == GemmMode::kWgrad ? static_cast<long long>(tc.g) * p.c_rows_per_group + tc.m_idx * TILE_M + row_in_tile
-                                                        : static_cast<long long>(tc.row0) + tc.m_idx * TILE_M + row_in_tile;
+      // first output row of this CTA's half (TMA store coordinate)
+      const int c_row0 = (MODE == GemmMode::kWgrad ? tc.g * p.c_rows_per_group : tc.row0) + tc.m_idx * TILE_M + static_cast<int>(cta) * PM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
       if (EPI == GemmEpilogue::kStore) {
-        epilogue_store_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * BN, t_row, empty_reduction);
+        epilogue_store_tma(ring, &map_c, tc.n_idx * BN, c_row0, r, t_row, empty_reduction);
       } else if (EPI == GemmEpilogue::kSwiGLUBwd) {
-        epilogue_swiglu_bwd_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (2 * BN),
-                                p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * (2 * BN), t_row);
+        ok = epilogue_swiglu_bwd_tma(ring, &map_c, &map_c2, tc.n_idx * (2 * BN), c_row0, r, t_row, &ctl->epi_load, load_phase, abort_flag, p.status, p.timeout_ns);
       } else {
-        epilogue_swiglu_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (BN / 2),
-                            p.c2 ? p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * BN : nullptr, t_row);
+        epilogue_swiglu_tma(ring, &map_c, tc.n_idx * (BN / 2), p.c2 ? &map_c2 : nullptr, tc.n_idx * BN, c_row0, r, t_row);
       }
       if (!empty_reduction) {
         tc_fence_before_sync();
@@ -184,6 +190,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->acc_empty[a]), 0));
       }
     }
+    ring.drain();  // every bulk store of this CTA has landed before anything is torn down
   }
   // ---------------- teardown: nobody frees tensor memory while the pair still uses it ----------------
   tc_fence_before_sync();
@@ -193,7 +200,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 }
 
 template <GemmMode MODE, GemmEpilogue EPI>
-cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const GemmArgs& args, int ctas, cudaStream_t stream) {
+cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& c2, const GemmArgs& args, int ctas,
+                       cudaStream_t stream) {
   auto kern = grouped_gemm_pair_kernel<MODE, EPI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -207,28 +215,30 @@ cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const GemmArg
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kern, a, b, args);
+  e = cudaLaunchKernelEx(&cfg, kern, a, b, c, c2, args);
   if (e == cudaSuccess) note_launch();
   return e;
 }
 
 }  // namespace
 
-cudaError_t launch_grouped_gemm_pair(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
-                                     int ctas, cudaStream_t stream) {
+cudaError_t launch_grouped_gemm_pair(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c,
+                                     const CUtensorMap* map_c2, const GemmArgs& args, int ctas, cudaStream_t stream) {
   if (ctas < 2) return cudaErrorInvalidValue;
+  if ((args.c2 != nullptr) != (map_c2 != nullptr)) return cudaErrorInvalidValue;
+  const CUtensorMap& c2 = map_c2 ? *map_c2 : map_c;  // unused by the kernel when args.c2 is null
   if (epi == GemmEpilogue::kSwiGLU) {
     if (mode != GemmMode::kForward) return cudaErrorInvalidValue;
-    return launch_one<GemmMode::kForward, GemmEpilogue::kSwiGLU>(map_a, map_b, args, ctas, stream);
+    return launch_one<GemmMode::kForward, GemmEpilogue::kSwiGLU>(map_a, map_b, map_c, c2, args, ctas, stream);
   }
   if (epi == GemmEpilogue::kSwiGLUBwd) {
     if (mode != GemmMode::kDgrad || args.c2 == nullptr) return cudaErrorInvalidValue;
-    return launch_one<GemmMode::kDgrad, GemmEpilogue::kSwiGLUBwd>(map_a, map_b, args, ctas, stream);
+    return launch_one<GemmMode::kDgrad, GemmEpilogue::kSwiGLUBwd>(map_a, map_b, map_c, c2, args, ctas, stream);
   }
   switch (mode) {
-    case GemmMode::kForward: return launch_one<GemmMode::kForward, GemmEpilogue::kStore>(map_a, map_b, args, ctas, stream);
-    case GemmMode::kDgrad: return launch_one<GemmMode::kDgrad, GemmEpilogue::kStore>(map_a, map_b, args, ctas, stream);
-    default: return launch_one<GemmMode::kWgrad, GemmEpilogue::kStore>(map_a, map_b, args, ctas, stream);
+    case GemmMode::kForward: return launch_one<GemmMode::kForward, GemmEpilogue::kStore>(map_a, map_b, map_c, c2, args, ctas, stream);
+    case GemmMode::kDgrad: return launch_one<GemmMode::kDgrad, GemmEpilogue::kStore>(map_a, map_b, map_c, c2, args, ctas, stream);
+    default: return launch_one<GemmMode::kWgrad, GemmEpilogue::kStore>(map_a, map_b, map_c, c2, args, ctas, stream);
   }
 }
 

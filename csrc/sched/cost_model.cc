@@ -220,6 +220,37 @@ PlanCost model_cost(const Plan& p, const CostModel& cm) {
   c.total_us = t;
   c.exposed_intra_us = t - c.inter_us;
   {
+    // Balance per stage: a rail piece whose origin is not the rail GPU was relayed by the balance
+    // phase, so the provenance of stage k's rail ops is exactly the balancing stage k needs.
+    std::vector<std::vector<int64_t>> sbal(static_cast<size_t>(std::max(K, 1)) * S, std::vector<int64_t>());
+    for (const Op& o : p.ops) {
+      if (o.phase != Phase::kRail || o.origin == o.src_rank || o.stage < 0 || o.stage >= K) continue;
+      auto& m = sbal[static_cast<size_t>(o.stage) * S + o.src_rank / G];
+      if (m.empty()) m.assign(static_cast<size_t>(G) * G, 0);
+      m[static_cast<size_t>(o.origin % G) * G + o.src_rank % G] += o.len;
+    }
+    auto bal_time = [&](int k, int s) { const auto& m = sbal[static_cast<size_t>(k) * S + s]; return m.empty() ? 0.0 : intra_time(m, G, cm); };
+    auto red_time = [&](int k, int s) { const auto& m = redis[static_cast<size_t>(k) * S + s]; return m.empty() ? 0.0 : intra_time(m, G, cm); };
+    c.stage_balance_us.assign(K, 0);
+    for (int k = 0; k < K; ++k)
+      for (int s = 0; s < S; ++s) c.stage_balance_us[k] = std::max(c.stage_balance_us[k], bal_time(k, s));
+    double tv = K > 0 ? c.stage_balance_us[0] : 0.0;
+    if (K == 0) tv += intrinsic_us;
+    for (int k = 0; k < K; ++k) {
+      // While stage k is on the wire each server forwards stage k - 1 and prepares stage k + 1
+      // (after the last preparation: the traffic that never leaves the server).
+      double intra = 0;
+      for (int s = 0; s < S; ++s) {
+        const double fwd_prev = k > 0 ? red_time(k - 1, s) : 0.0;
+        const double next = k + 1 < K ? bal_time(k + 1, s) : intra_time(intrinsic[s], G, cm);
+        intra = std::max(intra, fwd_prev + next);
+      }
+      tv += std::max(intra, c.stage_inter_us[k]);
+    }
+    if (K > 0) tv += c.stage_redistribute_us[K - 1];
+    c.balance_per_stage_total_us = tv;
+  }
+  {
     // Two resources, pieces of fraction f of a stage: the NIC runs the stages back to back (stage k
     // ends at A_k); the intra-server fabric forwards stage k from the moment its first piece has
     // landed and the previous forward is done, and ends no earlier than one piece after A_k.

@@ -150,6 +150,13 @@ struct PlanCost {
   // redistribution of a stage follows its inter-server transfer piece by piece instead of waiting
   // for the whole stage. Equal to total_us for plans without redistribution.
   double chunked_total_us = 0;
+  // The same plan with the balancing spread over the stages instead of done up front (the reference
+  // simulator's first pipeline variant, simulation/scheduler/global.cpp:404-529): before stage k's
+  // inter-server transfer only the units stage k ships are balanced, and that balancing shares the
+  // intra-server fabric with the redistribution of stage k - 1, both hidden under the inter-server
+  // transfer that runs at that time. stage_balance_us[k] is the slowest server's balancing for stage k.
+  double balance_per_stage_total_us = 0;
+  std::vector<double> stage_balance_us;
 };
 // Pipeline model: balance, then stage k's inter-server transfer overlaps stage k-1's
 // redistribution (simulation/scheduler/global.cpp:237-402 pipeline2). For one server per GPU

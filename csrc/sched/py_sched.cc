@@ -163,6 +163,7 @@ PYBIND11_MODULE(_sched, m) {
         py::dict d;
         d["total_us"] = c.total_us; d["balance_us"] = c.balance_us; d["inter_us"] = c.inter_us; d["exposed_intra_us"] = c.exposed_intra_us;
         d["lower_bound_us"] = c.lower_bound_us; d["spread_out_us"] = c.spread_out_us; d["chunked_total_us"] = c.chunked_total_us;
+        d["balance_per_stage_total_us"] = c.balance_per_stage_total_us; d["stage_balance_us"] = c.stage_balance_us;
         d["stage_inter_us"] = c.stage_inter_us; d["stage_redistribute_us"] = c.stage_redistribute_us;
         return d; }, py::arg("inter"), py::arg("intra"), py::arg("mb_per_unit") = 1.0, py::arg("intra_topology") = "switch",
            py::arg("links") = std::vector<int>())

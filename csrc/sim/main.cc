@@ -106,11 +106,11 @@ int cmd_plan(const Args& a) {
   PlanCost c = model_cost(p, cost_of(a, S));
   std::printf("{\"cmd\":\"plan\",\"kind\":%d,\"servers\":%d,\"gpus\":%d,\"stages\":%d,\"ops\":%zu,\"valid\":%s,\"error\":\"%s\",\"delivered_exact\":%s,"
               "\"stages_sum_to_matrix\":%s,\"decomposition_exact\":%s,\"line_sum\":%lld,\"max_line_sum_input\":%lld,\"scheduler_us\":%.2f,"
-              "\"modeled_us\":%.3f,\"modeled_chunked_us\":%.3f,\"lower_bound_us\":%.3f,\"spread_out_us\":%.3f,\"speedup_vs_spread_out\":%.4f,\"bound_fraction\":%.4f}\n",
+              "\"modeled_us\":%.3f,\"modeled_chunked_us\":%.3f,\"modeled_balance_per_stage_us\":%.3f,\"lower_bound_us\":%.3f,\"spread_out_us\":%.3f,\"speedup_vs_spread_out\":%.4f,\"bound_fraction\":%.4f}\n",
               static_cast<int>(o.kind), S, G, p.num_stages, p.ops.size(), err.empty() ? "true" : "false", err.c_str(), exact ? "true" : "false",
               stages_sum ? "true" : "false", (o.kind != PlanKind::kStaged || verify_decomposition(p.decomp)) ? "true" : "false",
               static_cast<long long>(p.decomp.line_sum), static_cast<long long>(p.matrix.max_line_sum()), t1 - t0, c.total_us, c.chunked_total_us,
-              c.lower_bound_us, c.spread_out_us, c.total_us > 0 ? c.spread_out_us / c.total_us : 0.0,
+              c.balance_per_stage_total_us, c.lower_bound_us, c.spread_out_us, c.total_us > 0 ? c.spread_out_us / c.total_us : 0.0,
               c.total_us > 0 ? c.lower_bound_us / c.total_us : 0.0);
   if (a.integer("dump", 0)) std::printf("%s\n", plan_to_json(p, a.integer("dump", 0) > 1).c_str());
   return err.empty() && exact && stages_sum ? 0 : 1;

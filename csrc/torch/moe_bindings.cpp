@@ -54,7 +54,8 @@ struct TensorMap2D {
 
 void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2D& b, torch::Tensor group_off, int tiles_n, int fixed_m_tiles,
                   int red_len, int b_rows_per_group, int c_rows_per_group, torch::Tensor c, c10::optional<torch::Tensor> c2, int64_t status_ptr,
-                  uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target, bool pair, int band_rows) {
+                  uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target, bool pair, int band_rows,
+                  const TensorMap2D* map_c, const TensorMap2D* map_c2) {
   TORCH_CHECK(group_off.is_cuda() && group_off.dtype() == torch::kInt32 && group_off.is_contiguous() && group_off.numel() >= 2, "group_off: cuda int32[G+1]");
   TORCH_CHECK(c.is_cuda() && c.dtype() == torch::kBFloat16 && c.dim() == 2 && c.stride(1) == 1, "c: cuda bf16 [rows, cols]");
   TORCH_CHECK(red_len % 64 == 0 && tiles_n >= 1, "reduction length must be a multiple of 64");
@@ -77,9 +78,11 @@ void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2
     g.gate_counter = reinterpret_cast<const unsigned long long*>(gate_counter_ptr);
     g.gate_target = reinterpret_cast<const unsigned long long*>(gate_target->data_ptr());
   }
-  if (pair)
-    cu_check(launch_grouped_gemm_pair(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, g, ctas, stream_now()), "grouped_gemm pair launch");
-  else
+  if (pair) {
+    TORCH_CHECK(map_c != nullptr && (map_c2 != nullptr) == c2.has_value(), "the CTA-pair kernel stores through tensor maps: give one for c, and one for c2 when c2 is given");
+    cu_check(launch_grouped_gemm_pair(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, map_c->map, map_c2 ? &map_c2->map : nullptr, g,
+                                      ctas, stream_now()), "grouped_gemm pair launch");
+  } else
     cu_check(launch_grouped_gemm(static_cast<GemmMode>(mode), static_cast<GemmEpilogue>(epilogue), a.map, b.map, g, ctas, stream_now()), "grouped_gemm launch");
 }
 
@@ -163,7 +166,10 @@ void combine_pull(const HeapPy& heap, int num_experts, torch::Tensor topk_idx, t
 
 void bind_moe(py::module_& m) {
   py::class_<TensorMap2D>(m, "TensorMap2D").def(py::init<int64_t, int64_t, int64_t, int64_t, int, int>());
-  m.def("grouped_gemm", &grouped_gemm);
+  m.def("grouped_gemm", &grouped_gemm, py::arg("mode"), py::arg("epilogue"), py::arg("a"), py::arg("b"), py::arg("group_off"), py::arg("tiles_n"),
+        py::arg("fixed_m_tiles"), py::arg("red_len"), py::arg("b_rows_per_group"), py::arg("c_rows_per_group"), py::arg("c"), py::arg("c2"),
+        py::arg("status_ptr"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("gate_counter_ptr"), py::arg("gate_target"), py::arg("pair"),
+        py::arg("band_rows"), py::arg("map_c") = nullptr, py::arg("map_c2") = nullptr);
   m.def("grouped_gemm_smem_bytes", &grouped_gemm_smem_bytes);
   m.attr("ROUTE_TOKENS_PER_BLOCK") = kRouteTokensPerBlock;
   m.def("route_topk", &route_topk);

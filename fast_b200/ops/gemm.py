@@ -57,6 +57,13 @@ def _tmap(t: torch.Tensor, box_rows: int):
     return m
 
 
+def _out_maps(c: torch.Tensor, c2: Optional[torch.Tensor]):
+    """Tensor maps of the outputs for the CTA-pair kernel's TMA stores (boxes of 64 columns x 128 rows)."""
+    if not USE_PAIR:
+        return None, None
+    return _tmap(c, _BM), (_tmap(c2, _BM) if c2 is not None else None)
+
+
 def _ctas() -> int:
     return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
 
@@ -84,7 +91,7 @@ def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, 
     assert out.shape[0] == a.shape[0] and out.shape[1] == (N // 2 if swiglu else N)
     C = runtime.ext()
     C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), 128 if USE_PAIR else _BN), group_off, N // _BN, 0, K, N,
-                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
+                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, gate_up_out))
     return out
 
 
@@ -102,10 +109,10 @@ def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tenso
     if swiglu_bwd_of is not None:
         assert USE_PAIR and out.shape[1] == 2 * K and swiglu_bwd_of.shape == out.shape
         C.grouped_gemm(DGRAD, SWIGLU_BWD, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, swiglu_bwd_of,
-                       _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
+                       _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, swiglu_bwd_of))
         return out
     C.grouped_gemm(DGRAD, STORE, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS)
+                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, None))
     return out
 
 
@@ -117,5 +124,5 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, group_off: torch.Tenso
     assert dy.shape[1] == N and x.shape[1] == K and N % bm == 0 and K % _BN == 0
     C = runtime.ext()
     C.grouped_gemm(WGRAD, STORE, _tmap(dy, _BK), _tmap(x, _BK), group_off, K // _BN, N // bm, 0, 0, N, out.view(G * N, K), None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas(), 0, None, USE_PAIR, BAND_ROWS)
+                   int(timeout_s * 1e9), _ctas(), 0, None, USE_PAIR, BAND_ROWS, *_out_maps(out.view(G * N, K), None))
     return out

@@ -61,6 +61,24 @@ def test_hierarchical_model_tracks_reference(ref_sim, S, G):
     assert 0.85 < float(np.mean(ratios)) < 1.1, ratios
 
 
+@pytest.mark.parametrize("S,G", [(2, 8), (4, 4), (3, 2)])
+def test_balance_per_stage_variant_tracks_reference_pipeline(ref_sim, S, G):
+    """The first pipeline variant of the reference simulator (balance before every stage instead of
+    once, simulation/scheduler/global.cpp:404-529) against the same timeline computed from this
+    plan's provenance: the balancing a stage needs is what its rail pieces say was relayed."""
+    inter, intra = sched.gbps_model(400, 0.7), sched.LinkModel(0.1, 2.3)
+    ratios = []
+    for seed in range(4):
+        m = sched.workload_uniform(S * G, 10000, seed + 11 * S)
+        ref = _run_ref(ref_sim, m, S, G, inter, intra, 1.0)
+        c = sched.build_plan(m, Topology(S, G)).cost(inter, intra, 1.0)
+        assert len(c["stage_balance_us"]) == len(c["stage_inter_us"])
+        # never better than the port bound, and the up-front balance of the default model moves the same units in total
+        assert c["balance_per_stage_total_us"] >= c["lower_bound_us"] * 0.999
+        ratios.append(c["balance_per_stage_total_us"] / ref["pipeline1_us"])
+    assert 0.9 < float(np.mean(ratios)) < 1.1 and all(0.85 < r < 1.15 for r in ratios), ratios
+
+
 def test_intra_fabric_models_match_reference_pipeline3(ref_sim):
     """Full mesh and bidirectional ring reproduce the reference's pipeline3 numbers; the link-graph
     model of the hybrid cube mesh stays within a few percent of its hand-written formula."""
