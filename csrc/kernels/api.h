@@ -87,6 +87,7 @@ struct GemmArgs {
   const unsigned long long* gate_counter;
   const unsigned long long* gate_target;
   int band_rows;           // rows of a raster band (0 = default 4096): tiles are visited band by band, all columns per band
+  int direct_epilogue;     // CTA-pair kernel: 1 = epilogue threads access global memory row by row instead of staging tiles for TMA
 };
 
 int grouped_gemm_smem_bytes();

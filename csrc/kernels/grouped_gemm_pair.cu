@@ -49,7 +49,9 @@ static_assert(kAccStages * BN <= kTmemCols && kTmemCols <= 512 && (kTmemCols & (
 static_assert(BK * 2 == 128, "one k block is one 128-byte swizzle row of bf16");
 static_assert(kThreads == 32 * (2 + kEpiWarps) && kEpiWarps == 4, "warp roles: producer, MMA issuer, four epilogue warps (one per TMEM lane quarter)");
 
-template <GemmMode MODE, GemmEpilogue EPI>
+// TMA_EPI: outputs leave through the shared-memory ring and TMA stores; otherwise every epilogue
+// thread writes (and, for the fused SwiGLU backward, reads) its own row in global memory.
+template <GemmMode MODE, GemmEpilogue EPI, bool TMA_EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
                          const __grid_constant__ CUtensorMap map_c2, const GemmArgs p) {
@@ -177,7 +179,18 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       // first output row of this CTA's half (TMA store coordinate)
       const int c_row0 = (MODE == GemmMode::kWgrad ? tc.g * p.c_rows_per_group : tc.row0) + tc.m_idx * TILE_M + static_cast<int>(cta) * PM;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
-      if (EPI == GemmEpilogue::kStore) {
+      if (!TMA_EPI) {
+        const long long c_row = static_cast<long long>(c_row0) + r;
+        if (EPI == GemmEpilogue::kStore) {
+          epilogue_store_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * BN, t_row, empty_reduction);
+        } else if (EPI == GemmEpilogue::kSwiGLUBwd) {
+          epilogue_swiglu_bwd_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (2 * BN),
+                                  p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * (2 * BN), t_row);
+        } else {
+          epilogue_swiglu_row(p.c + c_row * p.ldc + static_cast<long long>(tc.n_idx) * (BN / 2),
+                              p.c2 ? p.c2 + c_row * p.ldc2 + static_cast<long long>(tc.n_idx) * BN : nullptr, t_row);
+        }
+      } else if (EPI == GemmEpilogue::kStore) {
         epilogue_store_tma(ring, &map_c, tc.n_idx * BN, c_row0, r, t_row, empty_reduction);
       } else if (EPI == GemmEpilogue::kSwiGLUBwd) {
         ok = epilogue_swiglu_bwd_tma(ring, &map_c, &map_c2, tc.n_idx * (2 * BN), c_row0, r, t_row, &ctl->epi_load, load_phase, abort_flag, p.status, p.timeout_ns);
@@ -202,7 +215,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 template <GemmMode MODE, GemmEpilogue EPI>
 cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& c, const CUtensorMap& c2, const GemmArgs& args, int ctas,
                        cudaStream_t stream) {
-  auto kern = grouped_gemm_pair_kernel<MODE, EPI>;
+  auto kern = args.direct_epilogue ? grouped_gemm_pair_kernel<MODE, EPI, false> : grouped_gemm_pair_kernel<MODE, EPI, true>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg{};

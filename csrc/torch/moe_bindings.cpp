@@ -55,7 +55,7 @@ struct TensorMap2D {
 void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2D& b, torch::Tensor group_off, int tiles_n, int fixed_m_tiles,
                   int red_len, int b_rows_per_group, int c_rows_per_group, torch::Tensor c, c10::optional<torch::Tensor> c2, int64_t status_ptr,
                   uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target, bool pair, int band_rows,
-                  const TensorMap2D* map_c, const TensorMap2D* map_c2) {
+                  const TensorMap2D* map_c, const TensorMap2D* map_c2, bool direct_epilogue) {
   TORCH_CHECK(group_off.is_cuda() && group_off.dtype() == torch::kInt32 && group_off.is_contiguous() && group_off.numel() >= 2, "group_off: cuda int32[G+1]");
   TORCH_CHECK(c.is_cuda() && c.dtype() == torch::kBFloat16 && c.dim() == 2 && c.stride(1) == 1, "c: cuda bf16 [rows, cols]");
   TORCH_CHECK(red_len % 64 == 0 && tiles_n >= 1, "reduction length must be a multiple of 64");
@@ -72,6 +72,7 @@ void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2
   g.status = reinterpret_cast<DeviceStatus*>(status_ptr);
   g.timeout_ns = timeout_ns;
   g.band_rows = band_rows;
+  g.direct_epilogue = direct_epilogue ? 1 : 0;
   if (gate_counter_ptr != 0) {
     TORCH_CHECK(gate_target.has_value() && gate_target->is_cuda() && gate_target->scalar_type() == torch::kInt64 && gate_target->numel() >= g.num_groups,
                 "gate_target: cuda int64[G]");
@@ -169,7 +170,7 @@ void bind_moe(py::module_& m) {
   m.def("grouped_gemm", &grouped_gemm, py::arg("mode"), py::arg("epilogue"), py::arg("a"), py::arg("b"), py::arg("group_off"), py::arg("tiles_n"),
         py::arg("fixed_m_tiles"), py::arg("red_len"), py::arg("b_rows_per_group"), py::arg("c_rows_per_group"), py::arg("c"), py::arg("c2"),
         py::arg("status_ptr"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("gate_counter_ptr"), py::arg("gate_target"), py::arg("pair"),
-        py::arg("band_rows"), py::arg("map_c") = nullptr, py::arg("map_c2") = nullptr);
+        py::arg("band_rows"), py::arg("map_c") = nullptr, py::arg("map_c2") = nullptr, py::arg("direct_epilogue") = false);
   m.def("grouped_gemm_smem_bytes", &grouped_gemm_smem_bytes);
   m.attr("ROUTE_TOKENS_PER_BLOCK") = kRouteTokensPerBlock;
   m.def("route_topk", &route_topk);

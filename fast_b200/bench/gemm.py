@@ -36,10 +36,15 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--kernel", default="pair", choices=["pair", "one"])
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--direct-epilogue", action="store_true", help="CTA-pair kernel: row-per-thread global accesses in the epilogue instead of TMA stores")
+    ap.add_argument("--band-rows", type=int, default=0, help="rows of a raster band (0 = kernel default)")
     ap.add_argument("--only", default="", help="comma-separated case names to run (default: all)")
     ap.add_argument("--sustain-s", type=float, default=0.0, help="also time back-to-back launches for this many seconds (power-capped regime)")
     a = ap.parse_args()
     gemm.USE_PAIR = a.kernel == "pair"
+    gemm.DIRECT_EPILOGUE = a.direct_epilogue
+    if a.band_rows:
+        gemm.BAND_ROWS = a.band_rows
     G, H, I = a.experts, a.hidden, a.inter
     per = a.rows // G // 256 * 256
     R = per * G

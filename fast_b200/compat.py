@@ -197,7 +197,9 @@ class FlashComm:
         self.mean_units, self.seed = int(mean_units), int(seed)
         self.quiet = quiet
         assert generator in ("seeded", "glibc")
-        self.generator = generator  # "glibc": the very matrix the reference's tester draws (see reference_uniform_workload)
+        # "glibc": the very matrix the reference's tester draws (reference_uniform_workload with bound = mean_units,
+        # 2**23 by default as in the reference); "seeded": this library's generator with mean mean_units.
+        self.generator = generator
         if comm is None:
             from .parallel import Communicator
 
@@ -212,7 +214,7 @@ class FlashComm:
         from . import sched
 
         if self.generator == "glibc":
-            m = torch.from_numpy(reference_uniform_workload(self.world, 2 * self.mean_units))
+            m = torch.from_numpy(reference_uniform_workload(self.world, self.mean_units))  # the reference's bound: entries in [0, mean_units)
         else:
             m = torch.from_numpy(np.ascontiguousarray(sched.workload_uniform(self.world, 2 * self.mean_units, self.seed, False)))
         if self.world > 1:

@@ -20,6 +20,8 @@ _BM, _BN, _BK = 128, 256, 64
 USE_PAIR = CONFIG.gemm != "one"
 # Rows of a raster band (see csrc/kernels/gemm_common.cuh); 0 = kernel default.
 BAND_ROWS = CONFIG.band_rows
+# CTA-pair kernel: True = epilogue threads write global memory row by row; False = staged tiles + TMA stores.
+DIRECT_EPILOGUE = False
 
 
 def row_align() -> int:
@@ -91,7 +93,7 @@ def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, 
     assert out.shape[0] == a.shape[0] and out.shape[1] == (N // 2 if swiglu else N)
     C = runtime.ext()
     C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), 128 if USE_PAIR else _BN), group_off, N // _BN, 0, K, N,
-                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, gate_up_out))
+                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, gate_up_out), DIRECT_EPILOGUE)
     return out
 
 
@@ -109,10 +111,10 @@ def grouped_gemm_dgrad(dy: torch.Tensor, w: torch.Tensor, group_off: torch.Tenso
     if swiglu_bwd_of is not None:
         assert USE_PAIR and out.shape[1] == 2 * K and swiglu_bwd_of.shape == out.shape
         C.grouped_gemm(DGRAD, SWIGLU_BWD, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, swiglu_bwd_of,
-                       _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, swiglu_bwd_of))
+                       _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, swiglu_bwd_of), DIRECT_EPILOGUE)
         return out
     C.grouped_gemm(DGRAD, STORE, _tmap(dy, _BM), _tmap(w.view(G * N, K), _BK), group_off, K // _BN, 0, N, N, 0, out, None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, None))
+                   int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, None), DIRECT_EPILOGUE)
     return out
 
 
@@ -124,5 +126,5 @@ def grouped_gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, group_off: torch.Tenso
     assert dy.shape[1] == N and x.shape[1] == K and N % bm == 0 and K % _BN == 0
     C = runtime.ext()
     C.grouped_gemm(WGRAD, STORE, _tmap(dy, _BK), _tmap(x, _BK), group_off, K // _BN, N // bm, 0, 0, N, out.view(G * N, K), None, _st().ptr(),
-                   int(timeout_s * 1e9), _ctas(), 0, None, USE_PAIR, BAND_ROWS, *_out_maps(out.view(G * N, K), None))
+                   int(timeout_s * 1e9), _ctas(), 0, None, USE_PAIR, BAND_ROWS, *_out_maps(out.view(G * N, K), None), DIRECT_EPILOGUE)
     return out
