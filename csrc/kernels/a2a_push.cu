@@ -50,6 +50,14 @@ __device__ __forceinline__ void copy_bytes(unsigned char* __restrict__ dst, cons
   for (long long i = tid; i < bytes; i += nt) dst[i] = src[i];
 }
 
+// Phase of a work item for the optional time stamps: 0 balance, 1 rail (inter-server stage),
+// 2 redistribute (forward of staged data), 3 direct (intrinsic traffic and flat plans).
+__device__ __forceinline__ int phase_of(const A2AWork& w) {
+  if (w.signal_kind == 1) return 0;
+  if (w.signal_kind == 2) return 1;
+  return w.wait_kind == 2 ? 2 : 3;
+}
+
 __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
   __shared__ int s_ok;
   // Bytes this CTA has stored into each peer's OUTPUT and not yet announced. Output arrivals are
@@ -57,12 +65,21 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
   // the whole list instead of one per work item); staged data is announced item by item because a
   // forwarder is waiting for it.
   __shared__ unsigned long long s_pending[kSigMaxWorld];
+  // Peers whose entry flag this CTA has already seen for this epoch: the flag is polled once per
+  // CTA and peer, not once per work item.
+  __shared__ unsigned char s_peer_ready[kSigMaxWorld];
   const int tid = threadIdx.x;
-  for (int i = tid; i < kSigMaxWorld; i += blockDim.x) s_pending[i] = 0ull;
+  for (int i = tid; i < kSigMaxWorld; i += blockDim.x) { s_pending[i] = 0ull; s_peer_ready[i] = 0; }
+  if (tid == 0) s_ok = 1;
   __syncthreads();
   unsigned char* my_slab = static_cast<unsigned char*>(a.peer_table[a.rank]);
   unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(my_slab + a.sig_heap_off);
   unsigned long long* my_cnt = my_sig + kSigCounterOff;
+  // Optional per-phase stamps (globaltimer ns of this GPU): [0] first CTA in, [1 + 2 p] / [2 + 2 p]
+  // first start / last end of a work item of phase p, [9] last CTA out. The host clears them (start
+  // slots to ~0) before the launch.
+  unsigned long long* stamps = a.phase_stamps;
+  if (stamps && tid == 0) atomicMin(stamps + 0, global_timer_ns());
 
   // Tell every peer that this rank's buffers may be written for this epoch.
   if (blockIdx.x == 0 && tid < a.world) {
@@ -72,31 +89,40 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
   bool alive = true;
   for (int it = blockIdx.x; it < a.n_items && alive; it += gridDim.x) {
     const A2AWork w = a.items[it];
-    if (tid == 0) {
-      bool ok = wait_ge_bounded(my_sig + kSigReadyOff + w.dst_rank, a.epoch, a.status, kSiteEntryReady, w.dst_rank, a.timeout_ns);
-      if (ok && w.wait_kind == 1)
-        ok = wait_ge_bounded(my_cnt + 0, a.expect_balance, a.status, kSiteBalanceArrive, it, a.timeout_ns);
-      if (ok && w.wait_kind == 2)
-        ok = wait_ge_bounded(my_cnt + 2 + w.wait_stage, a.expect_rail[w.wait_stage], a.status, kSiteRailArrive, w.wait_stage, a.timeout_ns);
-      s_ok = ok ? 1 : 0;
+    // Every thread evaluates the same condition (shared memory is only written by thread 0 between
+    // barriers), so the barriers below are taken by all threads or by none.
+    const bool must_wait = !s_peer_ready[w.dst_rank] || w.wait_kind != 0;
+    if (must_wait) {
+      if (tid == 0) {
+        bool ok = s_peer_ready[w.dst_rank] || wait_ge_bounded(my_sig + kSigReadyOff + w.dst_rank, a.epoch, a.status, kSiteEntryReady, w.dst_rank, a.timeout_ns);
+        if (ok && w.wait_kind == 1)
+          ok = wait_ge_bounded(my_cnt + 0, a.expect_balance, a.status, kSiteBalanceArrive, it, a.timeout_ns);
+        if (ok && w.wait_kind == 2)
+          ok = wait_ge_bounded(my_cnt + 2 + w.wait_stage, a.expect_rail[w.wait_stage], a.status, kSiteRailArrive, w.wait_stage, a.timeout_ns);
+        s_ok = ok ? 1 : 0;
+      }
+      __syncthreads();
+      alive = s_ok != 0;
+      if (!alive) break;
+      if (tid == 0) s_peer_ready[w.dst_rank] = 1;  // read again only after the next barrier every thread takes
     }
-    __syncthreads();
-    alive = s_ok != 0;
-    if (alive) {
-      unsigned char* dst_slab = static_cast<unsigned char*>(a.peer_table[w.dst_rank]);
-      copy_bytes(dst_slab + a.dst_heap_off[w.dst_buf] + w.dst_off, a.src_base[w.src_buf] + w.src_off, w.bytes);
-    }
-    __syncthreads();  // every thread's stores precede thread 0's release below
-    if (alive && tid == 0) {
-      if (w.signal_kind == 3) {
-        s_pending[w.dst_rank] += static_cast<unsigned long long>(w.bytes);
-      } else {
+    if (stamps && tid == 0) atomicMin(stamps + 1 + 2 * phase_of(w), global_timer_ns());
+    unsigned char* dst_slab = static_cast<unsigned char*>(a.peer_table[w.dst_rank]);
+    copy_bytes(dst_slab + a.dst_heap_off[w.dst_buf] + w.dst_off, a.src_base[w.src_buf] + w.src_off, w.bytes);
+    if (w.signal_kind == 3) {
+      // Output bytes are announced once, after the whole list (one barrier below covers them all).
+      if (tid == 0) s_pending[w.dst_rank] += static_cast<unsigned long long>(w.bytes);
+      if (must_wait) __syncthreads();  // publishes s_peer_ready to the other threads
+    } else {
+      __syncthreads();  // every thread's stores precede thread 0's release below
+      if (tid == 0) {
         unsigned long long* dst_cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[w.dst_rank]) + a.sig_heap_off) + kSigCounterOff;
         const int slot = w.signal_kind == 1 ? 0 : 2 + w.stage;
         fence_sys();
         red_add_release_sys(dst_cnt + slot, static_cast<unsigned long long>(w.bytes));
       }
     }
+    if (stamps && tid == 0) atomicMax(stamps + 2 + 2 * phase_of(w), global_timer_ns());
   }
   __syncthreads();  // all copies of this CTA are issued; announce the output bytes, one peer per thread
   if (tid < a.world && s_pending[tid] != 0ull) {
@@ -104,20 +130,23 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
     fence_sys();
     red_add_release_sys(dst_cnt + 1, s_pending[tid]);
   }
-  // The collective is over for this rank once everything addressed to its output has landed.
+  // The collective is over for this rank once everything addressed to its output has landed. Only
+  // the last CTA to finish its pushes waits for that (the others leave their SM at once); it then
+  // clears the counters: all local waits are done by then and no peer can signal the next epoch
+  // before this rank publishes `ready` again.
   if (tid == 0) {
-    bool ok = alive && wait_ge_bounded(my_cnt + 1, a.expect_output, a.status, kSiteOutputArrive, 0, a.timeout_ns);
-    // Last CTA out clears the counters: all local waits are done and no peer can signal the
-    // next epoch before this rank publishes `ready` again.
     __threadfence();
     const unsigned long long ticket = atomicAdd(my_sig + kSigTicketOff, 1ull);
     if (ticket == gridDim.x - 1) {
+      const bool aborted = *reinterpret_cast<volatile unsigned long long*>(&a.status->abort) != 0ull;
+      const bool ok = !aborted && wait_ge_bounded(my_cnt + 1, a.expect_output, a.status, kSiteOutputArrive, 0, a.timeout_ns);
       if (ok) {
         my_cnt[0] = 0; my_cnt[1] = 0;
         for (int k = 0; k < a.num_stages; ++k) my_cnt[2 + k] = 0;
       }
       my_sig[kSigTicketOff] = 0;
       __threadfence_system();
+      if (stamps) atomicMax(stamps + 9, global_timer_ns());
     }
   }
 }

@@ -45,7 +45,12 @@ struct A2ARankArgs {
   const unsigned long long* expect_rail; // [num_stages] bytes landing in my rail staging
   DeviceStatus* status;
   unsigned long long timeout_ns;
+  // Optional, device u64[10] of globaltimer stamps: [0] kernel start, [1 + 2 p] / [2 + 2 p] first start /
+  // last end of the work items of phase p (0 balance, 1 rail, 2 redistribute, 3 direct), [9] end. The caller
+  // presets start slots ([0] and odd slots) to all ones and the others to zero.
+  unsigned long long* phase_stamps;
 };
+constexpr int kPhaseStampWords = 10;
 
 // device_args == nullptr: one real rank, `host_args` is passed by value. Otherwise one cooperative
 // launch with gridDim.y = virtual_ranks runs every rank of an in-process group (single-GPU

@@ -51,7 +51,7 @@ struct A2AProgramPy {
   }
 
   A2ARankArgs args(const HeapPy& heap, std::array<int64_t, 4> src_ptrs, std::array<int64_t, 4> dst_offs, int64_t sig_off,
-                   uint64_t epoch, const StatusPy& st, uint64_t timeout_ns) const {
+                   uint64_t epoch, const StatusPy& st, uint64_t timeout_ns, int64_t stamps_ptr = 0) const {
     A2ARankArgs a{};
     a.items = reinterpret_cast<const A2AWork*>(items_dev.data_ptr());
     a.n_items = n_items; a.rank = heap.h->rank(); a.world = heap.h->world(); a.num_stages = num_stages;
@@ -60,14 +60,15 @@ struct A2AProgramPy {
     a.sig_heap_off = sig_off; a.epoch = epoch; a.expect_output = expect_output; a.expect_balance = expect_balance;
     a.expect_rail = reinterpret_cast<const unsigned long long*>(expect_rail_dev.data_ptr());
     a.status = st.d; a.timeout_ns = timeout_ns;
+    a.phase_stamps = reinterpret_cast<unsigned long long*>(stamps_ptr);
     return a;
   }
 };
 
 void a2a_launch(const A2AProgramPy& p, const HeapPy& heap, std::array<int64_t, 4> src_ptrs, std::array<int64_t, 4> dst_offs,
-                int64_t sig_off, uint64_t epoch, const StatusPy& st, uint64_t timeout_ns, int ctas, int threads) {
+                int64_t sig_off, uint64_t epoch, const StatusPy& st, uint64_t timeout_ns, int ctas, int threads, int64_t stamps_ptr) {
   TORCH_CHECK(heap.h->world() <= kSigMaxWorld, "world larger than the signal block supports");
-  A2ARankArgs a = p.args(heap, src_ptrs, dst_offs, sig_off, epoch, st, timeout_ns);
+  A2ARankArgs a = p.args(heap, src_ptrs, dst_offs, sig_off, epoch, st, timeout_ns, stamps_ptr);
   cuda_check(launch_a2a_push(&a, nullptr, 1, ctas, threads, cur_stream()), "a2a_push launch");
 }
 
@@ -129,7 +130,10 @@ PYBIND11_MODULE(_C, m) {
       .def_readonly("num_stages", &A2AProgramPy::num_stages)
       .def_readonly("total_bytes", &A2AProgramPy::total_bytes);
 
-  m.def("a2a_launch", &a2a_launch);
+  m.def("a2a_launch", &a2a_launch, py::arg("program"), py::arg("heap"), py::arg("src_ptrs"), py::arg("dst_offs"), py::arg("sig_off"), py::arg("epoch"),
+        py::arg("status"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("threads"), py::arg("stamps_ptr") = 0);
+  m.attr("PHASE_STAMP_WORDS") = kPhaseStampWords;
+  m.attr("SIG_MAX_WORLD") = kSigMaxWorld;
   m.def("a2a_launch_group", &a2a_launch_group);
   m.def("wait_probe", [](int64_t flag_ptr, uint64_t want, const StatusPy& st, uint64_t timeout_ns) {
     cuda_check(launch_wait_probe(reinterpret_cast<const unsigned long long*>(flag_ptr), want, st.d, timeout_ns, cur_stream()), "wait_probe");

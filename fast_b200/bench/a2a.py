@@ -39,6 +39,50 @@ def _time_ms(fn, iters, warmup):
     return float(t.item())
 
 
+def _e2e_fresh_ms(comm, out, inp, m, kind, chunk, **opts):
+    """Wall-clock cost of a collective on a matrix this communicator has never planned: traffic matrix
+    in hand -> ``schedule()`` (hash, plan, validation, lowering, work-list upload) -> launch -> output
+    complete. This is what a step with new routing pays; the device-timed columns reuse a schedule."""
+    import time
+
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=chunk, **opts)
+    t1 = time.perf_counter()
+    comm.all_to_all_v(out, inp, s)
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    t = torch.tensor([(t2 - t0) * 1e3, (t1 - t0) * 1e3], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0]), float(t[1])
+
+
+def phase_breakdown(comm, out, inp, s, reps: int = 3) -> dict:
+    """Per-phase completion of one scheduled collective, from device time stamps: microseconds from
+    the rank's kernel start to the first start / last end of its balance, rail (inter-server stage),
+    redistribute and direct work, max over ranks and mean over ``reps`` runs (the reference's
+    load-balance / cross-node / restore columns, amd/test_alltoall.cpp:1432-1438)."""
+    stamps = comm.new_phase_stamps()
+    acc = {}
+    for _ in range(reps):
+        comm.clear_phase_stamps(stamps)
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.all_to_all_v(out, inp, s, phase_stamps=stamps)
+        torch.cuda.synchronize()
+        ph = comm.read_phase_stamps(stamps)
+        names = ["balance", "rail", "redistribute", "direct", "total"]
+        v = torch.tensor([[ph.get(n, (0.0, 0.0))[0], ph.get(n, (0.0, 0.0))[1]] for n in names], device="cuda", dtype=torch.float64)
+        lo = v[:, 0].clone()
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        for i, n in enumerate(names):
+            acc.setdefault(n, []).append((float(lo[i]), float(v[i, 1])))
+    return {n: {"first_start_us": round(float(np.mean([x[0] for x in xs])), 1), "last_end_us": round(float(np.mean([x[1] for x in xs])), 1)}
+            for n, xs in acc.items() if any(x[1] > 0 for x in xs)}
+
+
 def nccl_alltoallv(out, inp, in_splits, out_splits):
     dist.all_to_all_single(out, inp, out_splits, in_splits)
 
@@ -123,7 +167,7 @@ def run(args):
     for size in args.sizes:
         skews = args.skews if args.mode == "skewed" else [None]
         for skew in skews:
-            acc = {}
+            acc, e2e, phases = {}, {}, None
             nmat = args.matrices if args.mode != "uniform" else 1
             for mi in range(nmat):
                 if args.mode == "uniform":
@@ -158,6 +202,17 @@ def run(args):
                     ms = _time_ms(fn, iters, args.warmup)
                     acc.setdefault(name, []).append((ms, sent, bound_bytes))
                 comm.check()
+                if args.e2e and args.mode != "uniform":
+                    # a matrix of the same law that no cache has seen (seeds above any used for the timed columns)
+                    fresh = draw(size, skew, 100000 + 1000 * len(results) + mi)
+                    room = int(fresh.sum(0).max()) <= need and int(fresh.sum(1).max()) <= inp.numel()
+                    if room:
+                        for name, kind in (("ours_fanout", PlanKind.FANOUT), ("ours_staged", PlanKind.STAGED)):
+                            e2e.setdefault(name, []).append(_e2e_fresh_ms(comm, out, inp, fresh, kind, args.chunk or None))
+                        comm.check()
+                if args.phases and mi == 0:
+                    s = comm.schedule(m, unit_bytes=1, kind=PlanKind.STAGED, chunk_bytes=args.chunk or None)
+                    phases = phase_breakdown(comm, out, inp, s)
                 if mi == 0 and args.verify:
                     s = comm.schedule(m, unit_bytes=1, kind=PlanKind.STAGED, chunk_bytes=args.chunk or None)
                     comm.all_to_all_v(out, inp, s)
@@ -169,6 +224,11 @@ def run(args):
                 ms = float(np.mean([x[0] for x in xs]))
                 row[name] = {"ms": round(ms, 4), "algbw_GBps": round(float(np.mean([x[1] / x[0] / 1e6 for x in xs])), 2),
                              "bound_frac_770": round(float(np.mean([x[2] / 770e9 / (x[0] * 1e-3) for x in xs])), 4)}
+            for name, xs in e2e.items():
+                row[name]["e2e_fresh_matrix_ms"] = round(float(np.mean([x[0] for x in xs])), 4)
+                row[name]["schedule_ms"] = round(float(np.mean([x[1] for x in xs])), 4)
+            if phases is not None:
+                row["ours_staged"]["phases"] = phases
             results.append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)
@@ -183,7 +243,9 @@ def main():
     ap.add_argument("--mode", default="skewed", choices=["uniform", "skewed", "random"], help="uniform: equal splits; skewed: Zipf rows; random: i.i.d. uniform entries (mean row = size)")
     ap.add_argument("--sizes", type=int, nargs="+", default=[64 << 20])
     ap.add_argument("--skews", type=float, nargs="+", default=[0.0, 0.5, 1.0, 1.5])
-    ap.add_argument("--matrices", type=int, default=4)
+    ap.add_argument("--matrices", type=int, default=20, help="fresh seeded matrices per point")
+    ap.add_argument("--e2e", action="store_true", help="also time schedule() + launch + completion on a never-seen matrix per drawn matrix (wall clock, max over ranks)")
+    ap.add_argument("--phases", action="store_true", help="per-phase breakdown (balance / rail / redistribute / direct) of the staged plan from device time stamps")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ctas", type=int, default=0, help="CTAs of the push kernel (0 = one per SM)")

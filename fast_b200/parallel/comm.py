@@ -20,7 +20,10 @@ from ..utils.config import CONFIG
 
 
 MAX_RAIL_COUNTERS = 4096  # rail arrival counters in the device signal block (kSigMaxStages)
-VIEW_WORLD = 64           # above this many ranks a communicator plans one-rank views instead of full plans
+# Above this many ranks a communicator plans one-rank views instead of full plans. It equals the
+# number of peers the device signal block has room for (kSigMaxWorld in csrc/kernels/api.h): planning
+# (and the host executors) scale past it, a launch on more ranks than that is refused by a2a_launch.
+VIEW_WORLD = 64
 
 
 @dataclass
@@ -257,18 +260,50 @@ class Communicator:
     def free_buffers(self, recv: torch.Tensor) -> None:
         self.free(recv)
 
-    def all_to_all_v(self, output: torch.Tensor, input: torch.Tensor, s: Schedule, staging: Optional[dict] = None) -> torch.Tensor:
+    def new_phase_stamps(self) -> torch.Tensor:
+        """A device buffer for ``all_to_all_v(..., phase_stamps=...)``, cleared for one collective."""
+        t = torch.zeros(self._C.PHASE_STAMP_WORDS, dtype=torch.int64, device=self.device)
+        return self.clear_phase_stamps(t)
+
+    @staticmethod
+    def clear_phase_stamps(t: torch.Tensor) -> torch.Tensor:
+        t.zero_()
+        t[[0, 1, 3, 5, 7]] = -1          # start slots hold a minimum: all ones as unsigned
+        return t
+
+    @staticmethod
+    def read_phase_stamps(t: torch.Tensor) -> dict:
+        """Stamps of one collective as microseconds since this rank's kernel start, per phase
+        ``(first start, last end)``; phases the plan does not have are absent. The reference records
+        the same breakdown with four event stamps per iteration (load balance / cross node /
+        restore, amd/test_alltoall.cpp:903-1106, reported at :1432-1438)."""
+        v = [int(x) for x in t.cpu().tolist()]
+        t0 = v[0]
+        out = {}
+        for p, name in enumerate(("balance", "rail", "redistribute", "direct")):
+            start, end = v[1 + 2 * p], v[2 + 2 * p]
+            if start != -1 and end != 0:
+                out[name] = ((start - t0) / 1e3, (end - t0) / 1e3)
+        out["total"] = (0.0, (v[9] - t0) / 1e3)
+        return out
+
+    def all_to_all_v(self, output: torch.Tensor, input: torch.Tensor, s: Schedule, staging: Optional[dict] = None,
+                     phase_stamps: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run a scheduled all-to-all(v) on the current stream. ``input`` holds the segments for
         rank 0..n-1 back to back; ``output`` receives the segments from rank 0..n-1 back to back.
         ``output`` in the symmetric heap (``alloc``) is written in place by the peers; any other
         tensor goes through a library-owned receive buffer and one extra local copy. ``staging``
         may name caller-owned symmetric tensors for the two-tier plans' ``"balance"`` and ``"rail"``
         areas (sizes from ``Schedule.max_bytes``; same allocation order on every rank), as the
-        reference's all_to_all_2 takes them (amd/flash.cpp:570-629); by default the library keeps its own."""
+        reference's all_to_all_2 takes them (amd/flash.cpp:570-629); by default the library keeps its own.
+        ``phase_stamps`` (``new_phase_stamps()``) makes the kernel record when each phase of the plan
+        (balance, rail, redistribute, direct) started and ended on this rank; read them with
+        ``read_phase_stamps`` after the stream is idle."""
         src, dst, copy_back = self._launch_args(s, output, input, staging)
         self.epoch += 1
         ctas = max(1, min(self.ctas, s.program.n_items))  # a handful of work items needs a handful of CTAs
-        self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, ctas, self.threads)
+        self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, ctas, self.threads,
+                           0 if phase_stamps is None else phase_stamps.data_ptr())
         if copy_back is not None:
             output.view(torch.uint8).reshape(-1)[: s.output_bytes].copy_(copy_back[: s.output_bytes])
         return output
