@@ -93,6 +93,12 @@ struct GemmArgs {
   const unsigned long long* gate_target;
   int band_rows;           // rows of a raster band (0 = default 4096): tiles are visited band by band, all columns per band
   int direct_epilogue;     // CTA-pair kernel: 1 = epilogue threads access global memory row by row instead of staging tiles for TMA
+  // CTA-pair kernel, forward only: operand A is e4m3 (map_a: u8 matrix, boxes {64,128}, no swizzle) with one fp32 scale per
+  // 128 elements of a row in a_scales [rows, red_len / 128]; null = bf16 operand.
+  const float* a_scales;
+  const int* group_rows;   // optional [num_groups]: real rows of each group; the e4m3 feed turns rows past them into zeros
+  int gate_tile_rows;      // 0: gate_counter / gate_target are indexed by group; > 0: by (row of the grouped matrix) / gate_tile_rows
+  int gate_slots;          // entries of gate_counter / gate_target (indices are clamped to the last one)
 };
 
 int grouped_gemm_smem_bytes();
@@ -136,6 +142,10 @@ struct SplitsArgs {
   int* group_off;              // [E/world + 1] out: padded row offsets of my experts
   int* group_rows;             // [E/world] out: real rows of my experts
   unsigned long long* arrive_target;  // [num_channels][E/world] in/out: cumulative rows expected
+  // Optional tile-granular targets: tile_target [num_channels][num_tiles] in/out, cumulative real rows expected in
+  // every tile_rows-row tile of this rank's receive buffer (tile_rows divides row_align). Null = not kept.
+  unsigned long long* tile_target;
+  int tile_rows, num_tiles;
   int* traffic_matrix;         // [world][world] out (tokens), may be null
   DeviceStatus* status;
   unsigned long long timeout_ns;
@@ -162,7 +172,8 @@ struct DispatchArgs {
   int fp8;                     // 1: send e4m3 bytes + one fp32 scale per 128 elements
   long long recv_heap_off;     // destination rows: bf16 [cap, H] (or u8 [cap, H] when fp8)
   long long scale_heap_off;    // fp8 only: float [cap, H/128]
-  long long arrive_heap_off;   // u64 [E/world] arrival counters of this channel
+  long long arrive_heap_off;   // u64 arrival counters of this channel: [E/world] per expert, or [num_tiles] per tile
+  int tile_rows, num_tiles;    // tile_rows > 0: arrivals are counted per tile of that many destination rows (num_tiles per rank)
   long long entry_flags_heap_off;  // u64 [world]; used when entry_epoch != 0
   unsigned long long entry_epoch;
   DeviceStatus* status;

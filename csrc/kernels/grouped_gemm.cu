@@ -78,13 +78,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
-      int gated_group = -1;
+      int gated = -1;
       for (int tile = blockIdx.x; ok && walk.locate(tile, tc); tile += gridDim.x) {
-        if (p.gate_counter != nullptr && tc.g != gated_group) {
-          // Arrival gate: rows of this group are pushed by peers; start as soon as they are all in.
-          if (!(ok = wait_ge_bounded(p.gate_counter + tc.g, p.gate_target[tc.g], p.status, kSiteRailArrive, tc.g, p.timeout_ns))) { *abort_flag = 1; break; }
-          asm volatile("fence.proxy.async.global;" ::: "memory");  // peer (generic-proxy) writes before TMA (async-proxy) reads
-          gated_group = tc.g;
+        if (p.gate_counter != nullptr) {
+          // Arrival gate: rows are pushed by peers; start as soon as the group (or, with gate_tile_rows > 0,
+          // the tile of that many rows of the grouped matrix) is all in.
+          const int slot = min(p.gate_tile_rows > 0 ? (tc.row0 + tc.m_idx * BM) / p.gate_tile_rows : tc.g, p.gate_slots - 1);
+          if (slot != gated) {
+            if (!(ok = wait_ge_bounded(p.gate_counter + slot, p.gate_target[slot], p.status, kSiteRailArrive, slot, p.timeout_ns))) { *abort_flag = 1; break; }
+            asm volatile("fence.proxy.async.global;" ::: "memory");  // peer (generic-proxy) writes before TMA (async-proxy) reads
+            gated = slot;
+          }
         }
         for (int kb = 0; kb < tc.red_blocks; ++kb, ++it) {
           const int s = it % kStages;
@@ -199,7 +203,7 @@ static cudaError_t launch_one(const CUtensorMap& a, const CUtensorMap& b, const 
 cudaError_t launch_grouped_gemm(GemmMode mode, GemmEpilogue epi, const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmArgs& args,
                                 int ctas, cudaStream_t stream) {
   if (ctas < 1) return cudaErrorInvalidValue;
-  if (epi == GemmEpilogue::kSwiGLUBwd) return cudaErrorInvalidValue;  // only the CTA-pair kernel carries this epilogue
+  if (epi == GemmEpilogue::kSwiGLUBwd || args.a_scales != nullptr) return cudaErrorInvalidValue;  // only the CTA-pair kernel carries these
   if (epi == GemmEpilogue::kSwiGLU) {
     if (mode != GemmMode::kForward) return cudaErrorInvalidValue;
     return launch_one<GemmMode::kForward, GemmEpilogue::kSwiGLU>(map_a, map_b, args, ctas, stream);

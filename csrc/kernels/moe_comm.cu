@@ -33,12 +33,15 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 constexpr int kMaxK = 8;
+constexpr int kMaxScaleGroups = 128;  // fp8 dispatch: rows of up to 128 x 128 = 16384 elements
 
 __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const DispatchArgs a) {
-  extern __shared__ int s_cnt[];  // [E] rows this CTA sent per expert
+  extern __shared__ int s_cnt[];  // rows this CTA sent: [E] per expert, or [world][num_tiles] per destination tile
   __shared__ int s_ok;
+  __shared__ __align__(16) float s_scales[(kCommThreads / 32) * kMaxScaleGroups];  // fp8 mode: the 1x128 scales of the row each warp is sending
   const int E = a.num_experts, El = E / a.world;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) s_cnt[e] = 0;
+  const int n_cnt = a.tile_rows > 0 ? a.world * a.num_tiles : E;
+  for (int e = threadIdx.x; e < n_cnt; e += blockDim.x) s_cnt[e] = 0;
   if (threadIdx.x == 0) s_ok = 1;
   if (*reinterpret_cast<volatile unsigned long long*>(&a.status->abort) != 0ull) return;  // an earlier kernel of this rank refused the step
   __syncthreads();
@@ -88,7 +91,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
         row_of[j] = row;
         dst[j] = static_cast<unsigned char*>(a.peer_table[e / El]);
         if (a.row_scale) scale[j] = a.row_scale[tj];
-        if (lane == 0) atomicAdd(&s_cnt[e], 1);
+        if (lane == 0) atomicAdd(&s_cnt[a.tile_rows > 0 ? (e / El) * a.num_tiles + min(row / a.tile_rows, a.num_tiles - 1) : e], 1);
       }
     }
     const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.H);
@@ -124,9 +127,11 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
       }
     } else {
       // 16 elements per lane (one 16-byte store of e4m3); 8 consecutive lanes = 128 elements share
-      // one scale (amax / 448).
+      // one scale (amax / 448). The row's scales are collected in shared memory and leave as 16-byte
+      // stores after the payload: 4-byte remote stores would each cost a packet of their own.
       const int sgroups = a.H / 128;
       const int chunks16 = a.H / 16;
+      float* my_scales = s_scales + warp * kMaxScaleGroups;
       // The whole warp walks the row together (the shuffles below need every lane); lanes past
       // the end of a short row carry zeros and store nothing.
       for (int c0 = 0; c0 < chunks16; c0 += 32) {
@@ -148,30 +153,47 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
         for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
 #pragma unroll
         for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float sc = fmaxf(amax, 1e-12f) * (1.0f / 448.0f);
+        // amax / 448, rounded UP to the next value a bf16 can hold: quantised values still fit e4m3, and a receiver
+        // that multiplies in bf16 (the expert GEMM's converter warps) reproduces value x scale without a second rounding.
+        const float sc = __uint_as_float((__float_as_uint(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)) + 0xFFFFu) & 0xFFFF0000u);
         const float inv = 1.0f / sc;
         uint4 q;
         unsigned char* qb = reinterpret_cast<unsigned char*>(&q);
 #pragma unroll
         for (int i = 0; i < 16; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
+        if (active && (lane & 7) == 0) my_scales[c / 8] = sc;
 #pragma unroll
         for (int j = 0; j < kMaxK; ++j) {
           if (j < jbeg || j >= jend || !active || dst[j] == nullptr) continue;
           uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
           *out = q;
-          if ((lane & 7) == 0)
-            reinterpret_cast<float*>(dst[j] + a.scale_heap_off)[static_cast<long long>(row_of[j]) * sgroups + c / 8] = sc;
         }
       }
+      __syncwarp();
+      // sgroups is a multiple of 2 (H % 256 == 0): pairs of scales always; quads when the row's scale block is 16-byte aligned.
+      const bool quad = (sgroups & 3) == 0;
+#pragma unroll
+      for (int j = 0; j < kMaxK; ++j) {
+        if (j < jbeg || j >= jend || dst[j] == nullptr) continue;
+        float* srow = reinterpret_cast<float*>(dst[j] + a.scale_heap_off) + static_cast<long long>(row_of[j]) * sgroups;
+        if (quad) {
+          for (int g = lane * 4; g < sgroups; g += 128) *reinterpret_cast<float4*>(srow + g) = *reinterpret_cast<const float4*>(my_scales + g);
+        } else {
+          for (int g = lane * 2; g < sgroups; g += 64) *reinterpret_cast<float2*>(srow + g) = *reinterpret_cast<const float2*>(my_scales + g);
+        }
+      }
+      __syncwarp();  // the next row reuses my_scales
     }
   }
   __syncthreads();  // every row of this CTA is stored before the counters move
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+  for (int e = threadIdx.x; e < n_cnt; e += blockDim.x) {
     const int n = s_cnt[e];
     if (n == 0) continue;
-    unsigned long long* cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[e / El]) + a.arrive_heap_off);
+    const int peer = a.tile_rows > 0 ? e / a.num_tiles : e / El;
+    const int slot = a.tile_rows > 0 ? e % a.num_tiles : e % El;
+    unsigned long long* cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[peer]) + a.arrive_heap_off);
     fence_sys();
-    red_add_release_sys(cnt + (e % El), static_cast<unsigned long long>(n));
+    red_add_release_sys(cnt + slot, static_cast<unsigned long long>(n));
   }
 }
 
@@ -283,8 +305,16 @@ __global__ void wait_counters_kernel(const unsigned long long* counter, const un
 
 cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t stream) {
   if (a.K < 1 || a.K > kMaxK || a.H % 256 || a.world < 1 || a.num_experts % a.world || ctas < 1) return cudaErrorInvalidValue;
+  if (a.fp8 && a.H / 128 > kMaxScaleGroups) return cudaErrorInvalidValue;
   if (a.T == 0) return cudaSuccess;
-  dispatch_push_kernel<<<ctas, kCommThreads, sizeof(int) * a.num_experts, stream>>>(a);
+  if (a.tile_rows < 0 || (a.tile_rows > 0 && a.num_tiles < 1)) return cudaErrorInvalidValue;
+  const size_t smem = sizeof(int) * (a.tile_rows > 0 ? static_cast<size_t>(a.world) * a.num_tiles : static_cast<size_t>(a.num_experts));
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;  // per-CTA histogram of destination tiles must fit in shared memory
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(dispatch_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  dispatch_push_kernel<<<ctas, kCommThreads, smem, stream>>>(a);
   note_launch();
   return cudaGetLastError();
 }

@@ -196,6 +196,15 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
       if (le == El - 1) a.group_off[El] = base + s_tot[e];
       // Monotone arrival targets, one per channel (forward dispatch, backward dispatch).
       for (int ch = 0; ch < a.num_channels; ++ch) a.arrive_target[ch * El + le] += static_cast<unsigned long long>(tot);
+      if (a.tile_target != nullptr) {
+        // The same per tile of the receive buffer: this expert's rows fill its tiles from `base` on.
+        for (int r0 = 0; r0 < tot; r0 += a.tile_rows) {
+          const int t = (base + r0) / a.tile_rows;
+          if (t >= a.num_tiles) break;
+          const unsigned long long rows = static_cast<unsigned long long>(min(a.tile_rows, tot - r0));
+          for (int ch = 0; ch < a.num_channels; ++ch) a.tile_target[static_cast<long long>(ch) * a.num_tiles + t] += rows;
+        }
+      }
     }
   }
   // Token traffic matrix of this step, [src][dst], for the scheduler / observability.
@@ -249,6 +258,7 @@ cudaError_t launch_route_topk(const float* logits, const float* bias, int T, int
 }
 
 cudaError_t launch_splits_scan(const SplitsArgs& a, cudaStream_t stream) {
+  if (a.tile_target != nullptr && (a.tile_rows < 1 || a.row_align % a.tile_rows || a.num_tiles < 1)) return cudaErrorInvalidValue;
   if ((a.row_align != 128 && a.row_align != 256) || a.num_experts < 1 || a.num_experts > 1024 || a.world < 1 || a.world > a.num_experts || a.num_experts % a.world) return cudaErrorInvalidValue;
   int threads = (std::max(a.num_experts, a.world) + 31) / 32 * 32;
   SplitsArgs b = a;

@@ -37,6 +37,21 @@ EncodeTiledFn encode_tiled() {
 // {box_cols, box_rows} with the 128-byte swizzle. box_cols must be 64 (one 128-byte line).
 struct TensorMap2D {
   alignas(64) CUtensorMap map;
+  TensorMap2D() = default;
+  // A 2-D byte matrix (e4m3 rows) tiled in boxes of {64 bytes, box_rows}, no swizzle: the ring the converter
+  // warps of the e4m3-operand GEMM read from.
+  static TensorMap2D bytes(int64_t ptr, int64_t rows, int64_t cols, int64_t pitch_bytes, int box_rows) {
+    TORCH_CHECK(box_rows >= 1 && box_rows <= 256 && ptr % 16 == 0 && pitch_bytes % 16 == 0 && cols % 64 == 0, "byte tensor map: 16-byte aligned base and pitch, columns a multiple of 64");
+    TensorMap2D t;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
+    cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_tiled()(&t.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (bytes) failed with code ", static_cast<int>(r));
+    return t;
+  }
   TensorMap2D(int64_t ptr, int64_t rows, int64_t cols, int64_t pitch_elems, int box_cols, int box_rows) {
     TORCH_CHECK(box_cols == 64, "128-byte swizzle wants boxes of 64 bf16 in the contiguous dimension");
     TORCH_CHECK(box_rows >= 1 && box_rows <= 256, "box rows out of range");
@@ -55,7 +70,8 @@ struct TensorMap2D {
 void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2D& b, torch::Tensor group_off, int tiles_n, int fixed_m_tiles,
                   int red_len, int b_rows_per_group, int c_rows_per_group, torch::Tensor c, c10::optional<torch::Tensor> c2, int64_t status_ptr,
                   uint64_t timeout_ns, int ctas, int64_t gate_counter_ptr, c10::optional<torch::Tensor> gate_target, bool pair, int band_rows,
-                  const TensorMap2D* map_c, const TensorMap2D* map_c2, bool direct_epilogue) {
+                  const TensorMap2D* map_c, const TensorMap2D* map_c2, bool direct_epilogue, c10::optional<torch::Tensor> a_scales,
+                  c10::optional<torch::Tensor> group_rows, int gate_tile_rows) {
   TORCH_CHECK(group_off.is_cuda() && group_off.dtype() == torch::kInt32 && group_off.is_contiguous() && group_off.numel() >= 2, "group_off: cuda int32[G+1]");
   TORCH_CHECK(c.is_cuda() && c.dtype() == torch::kBFloat16 && c.dim() == 2 && c.stride(1) == 1, "c: cuda bf16 [rows, cols]");
   TORCH_CHECK(red_len % 64 == 0 && tiles_n >= 1, "reduction length must be a multiple of 64");
@@ -73,9 +89,21 @@ void grouped_gemm(int mode, int epilogue, const TensorMap2D& a, const TensorMap2
   g.timeout_ns = timeout_ns;
   g.band_rows = band_rows;
   g.direct_epilogue = direct_epilogue ? 1 : 0;
+  g.gate_tile_rows = gate_tile_rows;
+  if (a_scales.has_value()) {
+    want(*a_scales, torch::kFloat32, "a_scales");
+    TORCH_CHECK(pair && red_len % 128 == 0 && a_scales->dim() == 2 && a_scales->size(1) == red_len / 128, "a_scales: float [rows, red_len / 128], CTA-pair kernel");
+    g.a_scales = a_scales->data_ptr<float>();
+  }
+  if (group_rows.has_value()) {
+    want(*group_rows, torch::kInt32, "group_rows");
+    TORCH_CHECK(group_rows->numel() >= g.num_groups, "group_rows: int32 [G]");
+    g.group_rows = group_rows->data_ptr<int>();
+  }
   if (gate_counter_ptr != 0) {
-    TORCH_CHECK(gate_target.has_value() && gate_target->is_cuda() && gate_target->scalar_type() == torch::kInt64 && gate_target->numel() >= g.num_groups,
-                "gate_target: cuda int64[G]");
+    TORCH_CHECK(gate_target.has_value() && gate_target->is_cuda() && gate_target->scalar_type() == torch::kInt64 &&
+                gate_target->numel() >= (gate_tile_rows > 0 ? 1 : g.num_groups), "gate_target: cuda int64[G], or one entry per tile with gate_tile_rows");
+    g.gate_slots = static_cast<int>(gate_target->numel());
     g.gate_counter = reinterpret_cast<const unsigned long long*>(gate_counter_ptr);
     g.gate_target = reinterpret_cast<const unsigned long long*>(gate_target->data_ptr());
   }
@@ -102,8 +130,15 @@ void route_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int K, 
 void splits_scan(const HeapPy& heap, int64_t counts_off, int64_t flags_off, uint64_t epoch, torch::Tensor block_cnt, torch::Tensor block_base,
                  torch::Tensor send_base, torch::Tensor send_cnt, torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor arrive_target,
                  c10::optional<torch::Tensor> traffic, int num_channels, int row_align, int cap_rows, const StatusPy& st, uint64_t timeout_ns,
-                 c10::optional<torch::Tensor> send_pos, int64_t epoch_dev_ptr) {
+                 c10::optional<torch::Tensor> send_pos, int64_t epoch_dev_ptr, c10::optional<torch::Tensor> tile_target, int tile_rows) {
   SplitsArgs a{};
+  if (tile_target.has_value()) {
+    want(*tile_target, torch::kInt64, "tile_target");
+    TORCH_CHECK(tile_target->dim() == 2 && tile_target->size(0) == num_channels && tile_rows > 0, "tile_target: int64 [channels, tiles]");
+    a.tile_target = reinterpret_cast<unsigned long long*>(tile_target->data_ptr());
+    a.tile_rows = tile_rows;
+    a.num_tiles = static_cast<int>(tile_target->size(1));
+  }
   a.row_align = row_align;
   a.cap_rows = cap_rows;
   a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
@@ -133,7 +168,7 @@ void zero_pad_rows(torch::Tensor buf, torch::Tensor group_off, torch::Tensor gro
 void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, c10::optional<torch::Tensor> row_scale, torch::Tensor slot_in_block,
                    torch::Tensor block_base, torch::Tensor send_base, torch::Tensor dest_row, bool compute_rows, bool fp8, int64_t recv_off,
                    int64_t scale_off, int64_t arrive_off, int64_t entry_flags_off, uint64_t entry_epoch, const StatusPy& st, uint64_t timeout_ns, int ctas,
-                   c10::optional<torch::Tensor> send_list) {
+                   c10::optional<torch::Tensor> send_list, int tile_rows, int num_tiles) {
   want(x, torch::kBFloat16, "x"); want(topk_idx, torch::kInt32, "topk_idx"); want(dest_row, torch::kInt32, "dest_row");
   DispatchArgs a{};
   a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
@@ -143,6 +178,7 @@ void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, 
   a.slot_in_block = slot_in_block.data_ptr<int>(); a.block_base = block_base.data_ptr<int>(); a.send_base = send_base.data_ptr<int>();
   a.dest_row = dest_row.data_ptr<int>(); a.compute_rows = compute_rows; a.fp8 = fp8;
   a.send_list = ptr_or_null<const int>(send_list);
+  a.tile_rows = tile_rows; a.num_tiles = num_tiles;
   a.recv_heap_off = recv_off; a.scale_heap_off = scale_off; a.arrive_heap_off = arrive_off;
   a.entry_flags_heap_off = entry_flags_off; a.entry_epoch = entry_epoch; a.status = st.d; a.timeout_ns = timeout_ns;
   cu_check(launch_dispatch_push(a, ctas, stream_now()), "dispatch_push");
@@ -166,15 +202,19 @@ void combine_pull(const HeapPy& heap, int num_experts, torch::Tensor topk_idx, t
 }  // namespace
 
 void bind_moe(py::module_& m) {
-  py::class_<TensorMap2D>(m, "TensorMap2D").def(py::init<int64_t, int64_t, int64_t, int64_t, int, int>());
+  py::class_<TensorMap2D>(m, "TensorMap2D").def(py::init<int64_t, int64_t, int64_t, int64_t, int, int>()).def_static("bytes", &TensorMap2D::bytes);
   m.def("grouped_gemm", &grouped_gemm, py::arg("mode"), py::arg("epilogue"), py::arg("a"), py::arg("b"), py::arg("group_off"), py::arg("tiles_n"),
         py::arg("fixed_m_tiles"), py::arg("red_len"), py::arg("b_rows_per_group"), py::arg("c_rows_per_group"), py::arg("c"), py::arg("c2"),
         py::arg("status_ptr"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("gate_counter_ptr"), py::arg("gate_target"), py::arg("pair"),
-        py::arg("band_rows"), py::arg("map_c") = nullptr, py::arg("map_c2") = nullptr, py::arg("direct_epilogue") = false);
+        py::arg("band_rows"), py::arg("map_c") = nullptr, py::arg("map_c2") = nullptr, py::arg("direct_epilogue") = false, py::arg("a_scales") = py::none(),
+        py::arg("group_rows") = py::none(), py::arg("gate_tile_rows") = 0);
   m.def("grouped_gemm_smem_bytes", &grouped_gemm_smem_bytes);
   m.attr("ROUTE_TOKENS_PER_BLOCK") = kRouteTokensPerBlock;
   m.def("route_topk", &route_topk);
-  m.def("splits_scan", &splits_scan);
+  m.def("splits_scan", &splits_scan, py::arg("heap"), py::arg("counts_off"), py::arg("flags_off"), py::arg("epoch"), py::arg("block_cnt"), py::arg("block_base"),
+        py::arg("send_base"), py::arg("send_cnt"), py::arg("group_off"), py::arg("group_rows"), py::arg("arrive_target"), py::arg("traffic"),
+        py::arg("num_channels"), py::arg("row_align"), py::arg("cap_rows"), py::arg("status"), py::arg("timeout_ns"), py::arg("send_pos"),
+        py::arg("epoch_dev_ptr"), py::arg("tile_target") = py::none(), py::arg("tile_rows") = 0);
   m.def("zero_pad_rows", &zero_pad_rows);
   m.def("build_send_list", [](torch::Tensor topk_idx, torch::Tensor slot_in_block, torch::Tensor block_base, torch::Tensor send_pos, torch::Tensor list, const StatusPy& st) {
     want(topk_idx, torch::kInt32, "topk_idx"); want(send_pos, torch::kInt32, "send_pos"); want(list, torch::kInt32, "list");
@@ -183,7 +223,10 @@ void bind_moe(py::module_& m) {
                                     static_cast<int>(topk_idx.size(0)), static_cast<int>(topk_idx.size(1)), static_cast<int>(send_pos.numel()),
                                     list.data_ptr<int>(), st.d, stream_now()), "build_send_list");
   });
-  m.def("dispatch_push", &dispatch_push);
+  m.def("dispatch_push", &dispatch_push, py::arg("heap"), py::arg("x"), py::arg("topk_idx"), py::arg("row_scale"), py::arg("slot_in_block"), py::arg("block_base"),
+        py::arg("send_base"), py::arg("dest_row"), py::arg("compute_rows"), py::arg("fp8"), py::arg("recv_off"), py::arg("scale_off"), py::arg("arrive_off"),
+        py::arg("entry_flags_off"), py::arg("entry_epoch"), py::arg("status"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("send_list"),
+        py::arg("tile_rows") = 0, py::arg("num_tiles") = 0);
   m.def("combine_pull", &combine_pull);
   m.def("peer_signal", [](const HeapPy& heap, int64_t flags_off, uint64_t epoch, int64_t epoch_dev_ptr) {
     cu_check(launch_peer_signal(heap.h->device_peer_table(), heap.h->rank(), heap.h->world(), flags_off, epoch,

@@ -61,7 +61,17 @@ def main():
     dw13 = torch.empty_like(w13)
     dx = torch.empty(R, H, device=dev, dtype=torch.bfloat16)
     dgu = torch.empty(R, 2 * I, device=dev, dtype=torch.bfloat16)
+    xq = xs = None
+    if gemm.USE_PAIR and H % 128 == 0:
+        grp = x.float().view(R, H // 128, 128)
+        xs = (grp.abs().amax(-1).clamp_min(1e-12) / 448.0).contiguous()
+        xs = ((xs.view(torch.int32) + 0xFFFF) & ~0xFFFF).view(torch.float32)  # bf16-representable scales, as the dispatch kernel sends them
+        xq = (grp / xs.unsqueeze(-1)).to(torch.float8_e4m3fn).view(R, H).view(torch.uint8).contiguous()
+        del grp
+    rows_real = torch.full((G,), per, device=dev, dtype=torch.int32)
     cases = {
+        **({"fwd_w13_swiglu_from_e4m3": (lambda: gemm.grouped_gemm_fwd(xq, w13, off, act, swiglu=True, a_scales=xs, group_rows=rows_real), 2 * R * H * 2 * I)} if xq is not None else {}),
+        "fwd_w13_swiglu_act_only": (lambda: gemm.grouped_gemm_fwd(x, w13, off, act, swiglu=True), 2 * R * H * 2 * I),
         "fwd_w13_swiglu": (lambda: gemm.grouped_gemm_fwd(x, w13, off, act, swiglu=True, gate_up_out=gu), 2 * R * H * 2 * I),
         "fwd_w13_plain": (lambda: gemm.grouped_gemm_fwd(x, w13, off, gu), 2 * R * H * 2 * I),
         "fwd_w2": (lambda: gemm.grouped_gemm_fwd(act, w2, off, y), 2 * R * H * I),

@@ -86,11 +86,11 @@ def heap_bytes_needed(world, tokens, hidden, top_k, experts_per_gpu, fp8):
     return int(cap * hidden * (3 if fp8 else 4.2)) + (256 << 20)
 
 
-def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False, overlap=False):
+def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False, overlap=False, fp8_direct=False):
     """Runs the forward layer on an existing communicator and returns the result dict (every rank)."""
     rank, world = comm.rank, comm.world
     E, K, H, I, T, El = experts_per_gpu * world, top_k, hidden, inter, tokens, experts_per_gpu
-    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False, overlap_dispatch=overlap)
+    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False, overlap_dispatch=overlap, fp8_direct=fp8_direct)
     g = torch.Generator(device="cuda").manual_seed(7)      # same on every rank: the bias is replicated
     bias = torch.randn(E, generator=g, device="cuda") * 1.5
     gr = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -112,7 +112,8 @@ def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_
         ev[1].record()
         eng.dispatch(x, rs)
         if not overlap:
-            C.wait_counters(eng._arrive_ptr(0), eng.arrive_target[0], eng.status, eng.timeout_ns)  # phase boundary for timing only
+            # phase boundary for timing only: all rows of this rank's experts have landed
+            C.wait_counters(eng._arrive_ptr(0), eng.tile_target[0] if eng.tile_rows else eng.arrive_target[0], eng.status, eng.timeout_ns)
         ev[2].record()
         eng.experts_forward(w13, w2, rs)
         ev[3].record()
@@ -139,7 +140,7 @@ def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_
     route_us, dispatch_us, experts_us, combine_us, layer_us = _max_over_ranks(acc, world)
     tm = eng.traffic_matrix().cpu().numpy()
     res = {"bench": "moe_forward", "world": world, "overlap_dispatch": overlap, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K,
-           "dispatch_dtype": "fp8_e4m3_1x128" if fp8 else "bf16", "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1),
+           "dispatch_dtype": "fp8_e4m3_1x128" if fp8 else "bf16", "expert_feed": "e4m3 rows converted inside the GEMM" if eng.fp8_direct else ("dequantised to bf16 first" if fp8 else "bf16"), "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1),
            "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1), "combine_alone_us": round(combine_alone_us, 1),
            "dispatch_plus_combine_us": round(dispatch_us + combine_alone_us, 1),
            "layer_us": round(layer_us, 1),  # whole layer per iteration, max over ranks (phase maxima above fall on different ranks)
@@ -215,6 +216,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--skip-nccl", action="store_true")
     ap.add_argument("--graph", action="store_true", help="time the whole forward layer eagerly and as one CUDA graph replay")
+    ap.add_argument("--fp8-direct", action="store_true", help="with --fp8: feed the e4m3 rows to the expert GEMM as they are (converter warps) instead of dequantising first")
     ap.add_argument("--overlap", action="store_true", help="send rows expert by expert on a side stream while the gated GEMM runs (dispatch_us then only times the launch)")
     ap.add_argument("--out", default="", help="append the result row to this file (JSON lines)")
     a = ap.parse_args()
@@ -227,7 +229,7 @@ def main():
     if a.graph:
         res = measure_graph(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, max(a.iters, 20))
     else:
-        res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap)
+        res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap, a.fp8_direct)
     if rank == 0:
         print(json.dumps(res), flush=True)
         ResultLog(a.out or None, "moe_fwd").add(res)

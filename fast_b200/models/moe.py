@@ -73,7 +73,7 @@ class MoELayer(nn.Module):
 
     def __init__(self, comm: Communicator, hidden: int, inter: int, num_experts: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
                  router_bias: bool = False, training: bool = True, capacity_rows: Optional[int] = None, init_std: float = 0.02, seed: int = 0,
-                 overlap_dispatch: bool = False, graph_mode: bool = False):
+                 overlap_dispatch: bool = False, graph_mode: bool = False, fp8_direct: bool = False):
         super().__init__()
         self.comm, self.hidden, self.inter, self.num_experts, self.top_k = comm, hidden, inter, num_experts, top_k
         El = num_experts // comm.world
@@ -85,7 +85,7 @@ class MoELayer(nn.Module):
         self.w2 = nn.Parameter((torch.randn(El, hidden, inter, generator=ge, device=dev) * init_std).to(torch.bfloat16))
         self.router_bias = nn.Parameter(torch.zeros(num_experts, device=dev), requires_grad=False) if router_bias else None
         self.engine = ExpertParallel(comm, num_experts, hidden, inter, top_k, max_tokens, fp8_dispatch=fp8_dispatch, training=training,
-                                     capacity_rows=capacity_rows, overlap_dispatch=overlap_dispatch, graph_mode=graph_mode)
+                                     capacity_rows=capacity_rows, overlap_dispatch=overlap_dispatch, graph_mode=graph_mode, fp8_direct=fp8_direct)
 
     @torch.no_grad()
     def capture(self, tokens: int) -> None:

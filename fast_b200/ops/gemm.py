@@ -79,21 +79,47 @@ def pad_group_offsets(counts: torch.Tensor) -> torch.Tensor:
     return off.to(torch.int32)
 
 
+def _tmap_bytes(t: torch.Tensor, box_rows: int):
+    assert t.dtype == torch.uint8 and t.dim() == 2 and t.stride(1) == 1
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows, "u8")
+    m = _maps.get(key)
+    if m is None:
+        m = runtime.ext().TensorMap2D.bytes(t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+        _maps[key] = m
+    return m
+
+
 def grouped_gemm_fwd(a: torch.Tensor, w: torch.Tensor, group_off: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
-                     gate_up_out: Optional[torch.Tensor] = None, timeout_s: float = 5.0, gate=None) -> torch.Tensor:
+                     gate_up_out: Optional[torch.Tensor] = None, timeout_s: float = 5.0, gate=None, a_scales: Optional[torch.Tensor] = None,
+                     group_rows: Optional[torch.Tensor] = None, gate_tile_rows: int = 0, ctas: Optional[int] = None) -> torch.Tensor:
     """out[rows of g] = a[rows of g] @ w[g].T  (a [R, K], w [G, N, K], out [R, N]).
 
     With ``swiglu`` the N columns of every 256-wide tile are [128 gate | 128 up] of the same 128
     features and ``out`` is [R, N/2] = silu(gate) * up; ``gate_up_out`` ([R, N]) optionally keeps
     the raw tile for the backward pass. ``gate=(counter_ptr, target)`` makes the TMA producer
-    wait, group by group, until ``counter[g] >= target[g]`` (rows pushed by peers have landed).
+    wait, group by group, until ``counter[g] >= target[g]`` (rows pushed by peers have landed);
+    with ``gate_tile_rows`` > 0 the counters are per tile of that many rows of ``a`` instead of per
+    group, so a tile is loaded as soon as its own rows are in.
+
+    ``a`` may be uint8 e4m3 rows with ``a_scales`` (float [R, K/128], one scale per 128 elements):
+    the CTA-pair kernel then converts them to bf16 tiles in shared memory on the way to the tensor
+    core (no dequantised copy of ``a`` exists in global memory). ``group_rows`` (int32[G], real rows
+    per group) makes that path treat the rows between a group's real and padded end as zeros.
     """
     G, N, K = w.shape
     assert a.shape[1] == K and K % _BK == 0 and N % _BN == 0 and a.shape[0] % _BM == 0
     assert out.shape[0] == a.shape[0] and out.shape[1] == (N // 2 if swiglu else N)
     C = runtime.ext()
-    C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, _tmap(a, _BM), _tmap(w.view(G * N, K), 128 if USE_PAIR else _BN), group_off, N // _BN, 0, K, N,
-                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), _ctas(), *(gate or (0, None)), USE_PAIR, BAND_ROWS, *_out_maps(out, gate_up_out), DIRECT_EPILOGUE)
+    map_b = _tmap(w.view(G * N, K), 128 if USE_PAIR else _BN)
+    if a.dtype == torch.uint8:
+        assert USE_PAIR and a_scales is not None and K % 128 == 0 and a.is_contiguous(), "e4m3 operand: CTA-pair kernel, scales given, K a multiple of 128"
+        map_a = _tmap_bytes(a, _BM)
+    else:
+        assert a_scales is None
+        map_a = _tmap(a, _BM)
+    C.grouped_gemm(FORWARD, SWIGLU if swiglu else STORE, map_a, map_b, group_off, N // _BN, 0, K, N,
+                   0, out, gate_up_out, _st().ptr(), int(timeout_s * 1e9), min(ctas or _ctas(), _ctas()), *(gate or (0, None)), USE_PAIR, BAND_ROWS,
+                   *_out_maps(out, gate_up_out), DIRECT_EPILOGUE and a_scales is None, a_scales, group_rows, gate_tile_rows)
     return out
 
 

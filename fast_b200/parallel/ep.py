@@ -50,7 +50,7 @@ class ExpertParallel:
 
     def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
                  capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None, overlap_dispatch: bool = False,
-                 graph_mode: bool = False):
+                 graph_mode: bool = False, fp8_direct: bool = False):
         C = runtime.ext()
         self._C, self.comm = C, comm
         W = comm.world
@@ -67,8 +67,14 @@ class ExpertParallel:
         # the main stream already consumes the experts that are complete (forward dispatch only).
         self.overlap = overlap_dispatch
         self.side = torch.cuda.Stream(device=comm.device) if overlap_dispatch else None
+        sms = torch.cuda.get_device_properties(comm.device).multi_processor_count
         # dispatch / combine run alone on the stream: fill the machine (4 CTAs of 256 threads per SM)
-        self.comm_ctas = comm_ctas or 4 * torch.cuda.get_device_properties(comm.device).multi_processor_count
+        self.comm_ctas = comm_ctas or 4 * sms
+        # Overlapped dispatch: the gated GEMM is persistent (one CTA per SM, nearly all of its shared memory) and
+        # waits for rows that this rank's own dispatch kernel must send, so it may never own every SM: it leaves
+        # `reserve` SMs to the dispatch kernel, whose grid is sized for them.
+        self.overlap_reserve_sms = 24 if overlap_dispatch else 0
+        self.gemm1_ctas = (sms - self.overlap_reserve_sms) & ~1
         worst = W * max_tokens * min(top_k, self.El) + 256 * self.El
         self.cap = int(capacity_rows) if capacity_rows else worst
         self.cap = (min(self.cap, worst) + 255) // 256 * 256
@@ -77,18 +83,28 @@ class ExpertParallel:
         # symmetric: control words
         self.counts = comm.alloc((W, self.E), torch.int32)
         self.flags = comm.alloc((8, 64), torch.int64)  # rows: 0 counts, 1 fwd-ready, 2 bwd-entry, 3 bwd-ready
-        self.arrive = comm.alloc((2, self.El), torch.int64)
+        # Arrival counters. Training keeps one per local expert and channel (forward / backward dispatch). The
+        # forward-only layer counts arrivals per 256-row tile of the receive buffer instead, so that the expert
+        # GEMM's producer waits only for the tile it is about to load (CTA-pair kernel: its tiles are 256 rows).
+        self.tile_rows = 256 if (not training and gemm.USE_PAIR) else 0
+        self.ntiles = self.cap // 256
+        # fp8_direct (forward-only layer): e4m3 rows and their scales feed the first expert GEMM as they are (converter
+        # warps build the bf16 tiles in shared memory). Measured slower than the separate dequantisation pass followed
+        # by the bf16 GEMM (the conversion sits in the GEMM's critical path), so it is an option, not the default.
+        self.fp8_direct = bool(fp8_direct and fp8_dispatch and self.tile_rows)
+        self.arrive = comm.alloc((2, max(self.El, self.ntiles if self.tile_rows else 0)), torch.int64)
         for t in (self.counts, self.flags, self.arrive):
             t.zero_()
         # symmetric: payload
         if fp8_dispatch:
             self.xq_recv = comm.alloc((self.cap, hidden), torch.uint8)
             self.xs_recv = comm.alloc((self.cap, hidden // 128), torch.float32)
-            self.x_recv = torch.zeros(self.cap, hidden, dtype=torch.bfloat16, device=dev)
+            self.x_recv = None if self.fp8_direct else torch.zeros(self.cap, hidden, dtype=torch.bfloat16, device=dev)
         else:
             self.x_recv = comm.alloc((self.cap, hidden), torch.bfloat16)
         self.y = comm.alloc((self.cap, hidden), torch.bfloat16)
-        self.x_recv.zero_()
+        if self.x_recv is not None:
+            self.x_recv.zero_()
         self.y.zero_()
         # local work buffers
         self.act = torch.zeros(self.cap, inter, dtype=torch.bfloat16, device=dev)
@@ -112,6 +128,7 @@ class ExpertParallel:
         self.group_off = torch.zeros(self.El + 1, **i32)
         self.group_rows = torch.zeros(self.El, **i32)
         self.arrive_target = torch.zeros(2, self.El, dtype=torch.int64, device=dev)
+        self.tile_target = torch.zeros(1, self.ntiles, dtype=torch.int64, device=dev) if self.tile_rows else None
         self.traffic = torch.zeros(W, W, **i32)
         self.epoch = 0
         self.epoch_dev = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -143,7 +160,7 @@ class ExpertParallel:
         return self.flags._symm_off + row * 64 * 8
 
     def _arrive_ptr(self, ch: int) -> int:
-        return self.arrive.data_ptr() + ch * self.El * 8
+        return self.arrive.data_ptr() + ch * self.arrive.shape[1] * 8
 
     def traffic_matrix(self) -> torch.Tensor:
         """Token traffic matrix [src, dst] of the last routed step (device tensor)."""
@@ -167,7 +184,7 @@ class ExpertParallel:
         C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
                       self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1,
                       gemm.row_align(), self.cap, self.status,
-                      self.timeout_ns, self.send_pos if self.overlap else None, ed)
+                      self.timeout_ns, self.send_pos if self.overlap else None, ed, self.tile_target, self.tile_rows)
         return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows,
                           0 if self.graph_mode else self.epoch)
 
@@ -191,10 +208,11 @@ class ExpertParallel:
             if self.fp8:
                 C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, True,
                                 self._off(self.xq_recv), self._off(self.xs_recv), self.arrive._symm_off, 0, 0, self.status, self.timeout_ns,
-                                self.comm_ctas, send_list)
+                                4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas, send_list, self.tile_rows, self.ntiles)
             else:
                 C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, False,
-                                self._off(self.x_recv), 0, self.arrive._symm_off, 0, 0, self.status, self.timeout_ns, self.comm_ctas, send_list)
+                                self._off(self.x_recv), 0, self.arrive._symm_off, 0, 0, self.status, self.timeout_ns,
+                                4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas, send_list, self.tile_rows, self.ntiles)
         finally:
             if self.overlap:
                 self._dispatch_done = torch.cuda.Event()
@@ -209,13 +227,23 @@ class ExpertParallel:
 
     def experts_forward(self, w13: torch.Tensor, w2: torch.Tensor, rs: RouteState) -> None:
         C = self._C
-        gate = (self._arrive_ptr(0), self.arrive_target[0])
-        if self.fp8:
-            C.wait_counters(self._arrive_ptr(0), self.arrive_target[0], self.status, self.timeout_ns)
-            C.dequant_fp8(self.xq_recv, self.xs_recv, self.x_recv, rs.group_off.data_ptr() + 4 * self.El)
-            C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
-            gate = None
-        gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate)
+        if self.tile_rows:   # forward-only layer: the producer of the first GEMM waits tile by tile
+            gate, gate_tile = (self._arrive_ptr(0), self.tile_target[0]), self.tile_rows
+        else:
+            gate, gate_tile = (self._arrive_ptr(0), self.arrive_target[0]), 0
+        if self.fp8_direct:
+            # e4m3 rows and their scales go straight into the GEMM: converter warps build the bf16 tiles in
+            # shared memory, rows past a group's real end are zeros there. No dequantised copy, no separate wait.
+            gemm.grouped_gemm_fwd(self.xq_recv, w13, rs.group_off, self.act, swiglu=True, gate=gate, a_scales=self.xs_recv, group_rows=rs.group_rows,
+                                  gate_tile_rows=gate_tile, ctas=self.gemm1_ctas)
+        else:
+            if self.fp8:
+                C.wait_counters(self._arrive_ptr(0), self.tile_target[0] if self.tile_rows else self.arrive_target[0], self.status, self.timeout_ns)
+                C.dequant_fp8(self.xq_recv, self.xs_recv, self.x_recv, rs.group_off.data_ptr() + 4 * self.El)
+                C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
+                gate = None
+            gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate,
+                                  gate_tile_rows=gate_tile, ctas=self.gemm1_ctas)
         gemm.grouped_gemm_fwd(self.act, w2, rs.group_off, self.y)
         self._join_dispatch()
         C.peer_signal(self.comm.heap, self._flag_off(1), rs.epoch, self.epoch_dev.data_ptr() if self.graph_mode else 0)

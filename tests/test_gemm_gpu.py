@@ -163,3 +163,46 @@ def test_custom_operators_run_the_same_kernels():
     idx, wts = torch.ops.fast_b200.route_topk(logits, None, 2)
     ref = torch.softmax(logits, -1).topk(2, dim=-1)
     assert torch.equal(idx.long(), ref.indices) and torch.allclose(wts, ref.values / ref.values.sum(-1, keepdim=True), atol=1e-5)
+
+
+def _quant_e4m3_1x128(a):
+    """bf16 [R, K] -> (uint8 e4m3 [R, K], fp32 scales [R, K/128]) with amax / 448 scales, and the dequantised fp32 matrix
+    (rounded to bf16, which is what the kernel feeds the tensor core)."""
+    R, K = a.shape
+    g = a.float().view(R, K // 128, 128)
+    sc = g.abs().amax(-1).clamp_min(1e-12) / 448.0
+    sc = ((sc.view(torch.int32) + 0xFFFF) & ~0xFFFF).view(torch.float32)   # rounded up to bf16 precision, as the dispatch kernel does
+    q = (g / sc.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    deq = (q.float() * sc.unsqueeze(-1)).to(torch.bfloat16).float().view(R, K)
+    return q.view(R, K).view(torch.uint8).contiguous(), sc.contiguous(), deq
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("G,N,K,counts", [(1, 256, 128, [256]), (2, 512, 384, [200, 77]), (4, 768, 512, [0, 300, 128, 1])])
+def test_forward_from_e4m3_rows(G, N, K, counts, swiglu, kernel_variant):
+    """Operand A as e4m3 bytes + 1x128 scales, converted to bf16 tiles inside the kernel: equals the
+    product of the dequantised matrix; rows past a group's real end count as zeros even when the
+    buffer holds stale bytes and scales there."""
+    if kernel_variant != "cta_pair":
+        pytest.skip("the e4m3 operand feed belongs to the CTA-pair kernel")
+    from fast_b200.ops import gemm
+
+    counts_t, off, R, a, w = _setup(G, N, K, counts, seed=5)
+    q, sc, deq = _quant_e4m3_1x128(a)
+    # stale content in the pad rows: must not leak into anything
+    real = torch.zeros(R, dtype=torch.bool, device="cuda")
+    for i in range(G):
+        real[int(off[i]):int(off[i]) + int(counts_t[i])] = True
+    q[~real] = 0x7E                       # 448 in e4m3
+    sc[~real] = 3.0e38
+    out = torch.full((R, N // 2 if swiglu else N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm.grouped_gemm_fwd(q, w, off, out, swiglu=swiglu, a_scales=sc, group_rows=counts_t.to(torch.int32))
+    gemm.check()
+    for i in range(G):
+        s, e = int(off[i]), int(off[i + 1])
+        full = (deq[s:e] * real[s:e].unsqueeze(1)) @ w[i].float().T
+        if swiglu:
+            t = full.view(e - s, N // 256, 2, 128)
+            full = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(e - s, N // 2)
+        _close(out[s:e], full)
+        assert float(out[s + int(counts_t[i]):e].float().abs().max() if e > s + int(counts_t[i]) else 0.0) == 0.0

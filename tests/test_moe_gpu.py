@@ -181,13 +181,15 @@ def test_fused_embedding_and_loss_match_torch():
 
 
 @pytest.mark.parametrize("overlap", [False, True])
-@pytest.mark.parametrize("E,K,H,I,T,fp8", [(4, 2, 256, 256, 300, False), (8, 2, 512, 384, 1000, False), (32, 8, 256, 128, 513, False), (8, 2, 256, 256, 300, True)])
+@pytest.mark.parametrize("E,K,H,I,T,fp8", [(4, 2, 256, 256, 300, False), (8, 2, 512, 384, 1000, False), (32, 8, 256, 128, 513, False), (8, 2, 256, 256, 300, True),
+                                           (8, 2, 256, 256, 300, "direct")])
 def test_moe_forward_single_rank(E, K, H, I, T, fp8, overlap):
     from fast_b200.models import MoELayer
     from fast_b200.parallel import Communicator
 
     comm = Communicator(heap_bytes=256 << 20, device=0)
-    layer = MoELayer(comm, H, I, E, K, max_tokens=1024, fp8_dispatch=fp8, training=False, router_bias=True, overlap_dispatch=overlap)
+    layer = MoELayer(comm, H, I, E, K, max_tokens=1024, fp8_dispatch=bool(fp8), training=False, router_bias=True, overlap_dispatch=overlap,
+                     fp8_direct=fp8 == "direct")
     layer.eval()
     g = torch.Generator(device="cuda").manual_seed(7)
     layer.router_bias.data = torch.randn(E, generator=g, device="cuda") * 0.5
