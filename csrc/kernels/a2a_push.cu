@@ -12,6 +12,7 @@
 #include <atomic>
 
 #include "api.h"
+#include "sm100_ptx.cuh"
 
 namespace fastb {
 
@@ -50,6 +51,64 @@ __device__ __forceinline__ void copy_bytes(unsigned char* __restrict__ dst, cons
   for (long long i = tid; i < bytes; i += nt) dst[i] = src[i];
 }
 
+// ---- bulk-copy variant of copy_bytes ---------------------------------------------------------------
+// One elected thread moves the bytes with the bulk-copy engine instead of every thread with loads and
+// stores: local global memory -> a ring of shared-memory buffers (cp.async.bulk with mbarrier
+// completion), then shared memory -> the peer's global memory (cp.async.bulk store, bulk-group
+// completion). Both legs are plain bulk copies; the load side only ever reads this GPU's own memory.
+// Needs 16-byte aligned pointers and size; other pieces take the load/store loop above.
+constexpr int kBulkBufs = 4;
+constexpr int kBulkChunk = 32 * 1024;
+constexpr int kBulkSmemBytes = kBulkBufs * kBulkChunk;
+
+struct BulkState {
+  unsigned char* ring;       // kBulkBufs x kBulkChunk bytes of dynamic shared memory, 128-byte aligned
+  uint64_t* full;            // kBulkBufs mbarriers (count 1)
+  volatile int* abort_flag;  // CTA-shared give-up word of the bounded mbarrier wait
+  uint32_t loads;            // loads issued so far by this CTA's elected thread (buffer = loads % kBulkBufs)
+  uint32_t stores;           // stores issued so far
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+// Called by ONE thread. Returns false if a load never completed (bounded wait).
+__device__ __forceinline__ bool copy_bytes_bulk(BulkState& b, unsigned char* dst, const unsigned char* src, long long bytes, DeviceStatus* st,
+                                                unsigned long long timeout_ns) {
+  const int n = static_cast<int>((bytes + kBulkChunk - 1) / kBulkChunk);
+  auto size_of = [&](int c) { return static_cast<uint32_t>(c + 1 < n ? kBulkChunk : bytes - static_cast<long long>(c) * kBulkChunk); };
+  auto issue_load = [&](int c) {
+    const uint32_t buf = b.loads % kBulkBufs;
+    const uint32_t bar = smem_addr(b.full + buf), sz = size_of(c);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(sz) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(b.ring + buf * kBulkChunk)), "l"(src + static_cast<long long>(c) * kBulkChunk), "r"(sz), "r"(bar) : "memory");
+    ++b.loads;
+  };
+  // Buffers are taken in ring order by loads and stores alike. Stores of earlier pieces have long been issued:
+  // make sure they are done reading their buffers, then keep kBulkBufs - 1 loads ahead of the stores.
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  int loaded = 0;
+  for (; loaded < n && loaded < kBulkBufs - 1; ++loaded) issue_load(loaded);
+  for (int c = 0; c < n; ++c) {
+    const uint32_t buf = b.stores % kBulkBufs;
+    if (!ptx::mbar_wait_bounded(b.full + buf, (b.stores / kBulkBufs) & 1u, b.abort_flag, st, 900, timeout_ns)) return false;
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(dst + static_cast<long long>(c) * kBulkChunk), "r"(smem_addr(b.ring + buf * kBulkChunk)), "r"(size_of(c)) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    ++b.stores;
+    if (loaded < n) {
+      // The next load takes the buffer that store c - 1 read: every store but the one just issued must be done reading.
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      issue_load(loaded++);
+    }
+  }
+  return true;
+}
+// All bulk stores of this thread have completed and are ordered before what follows in the generic proxy.
+__device__ __forceinline__ void bulk_drain() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
 // Phase of a work item for the optional time stamps: 0 balance, 1 rail (inter-server stage),
 // 2 redistribute (forward of staged data), 3 direct (intrinsic traffic and flat plans).
 __device__ __forceinline__ int phase_of(const A2AWork& w) {
@@ -68,9 +127,21 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
   // Peers whose entry flag this CTA has already seen for this epoch: the flag is polled once per
   // CTA and peer, not once per work item.
   __shared__ unsigned char s_peer_ready[kSigMaxWorld];
+  __shared__ __align__(8) uint64_t s_bulk_full[kBulkBufs];
+  extern __shared__ __align__(128) unsigned char s_bulk_ring[];  // kBulkSmemBytes when a.bulk, else nothing
   const int tid = threadIdx.x;
   for (int i = tid; i < kSigMaxWorld; i += blockDim.x) { s_pending[i] = 0ull; s_peer_ready[i] = 0; }
-  if (tid == 0) s_ok = 1;
+  if (tid == 0) {
+    s_ok = 1;
+    if (a.bulk) {
+      for (int i = 0; i < kBulkBufs; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&s_bulk_full[i])) : "memory");
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+  }
+  __shared__ int s_bulk_abort;
+  if (tid == 0) s_bulk_abort = 0;
+  BulkState bulk{s_bulk_ring, s_bulk_full, &s_bulk_abort, 0u, 0u};  // used by thread 0 only
+  bool bulk_ok = true;
   __syncthreads();
   unsigned char* my_slab = static_cast<unsigned char*>(a.peer_table[a.rank]);
   unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(my_slab + a.sig_heap_off);
@@ -108,14 +179,25 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
     }
     if (stamps && tid == 0) atomicMin(stamps + 1 + 2 * phase_of(w), global_timer_ns());
     unsigned char* dst_slab = static_cast<unsigned char*>(a.peer_table[w.dst_rank]);
-    copy_bytes(dst_slab + a.dst_heap_off[w.dst_buf] + w.dst_off, a.src_base[w.src_buf] + w.src_off, w.bytes);
+    unsigned char* dst_ptr = dst_slab + a.dst_heap_off[w.dst_buf] + w.dst_off;
+    const unsigned char* src_ptr = a.src_base[w.src_buf] + w.src_off;
+    const bool by_engine = a.bulk && ((reinterpret_cast<uintptr_t>(dst_ptr) | reinterpret_cast<uintptr_t>(src_ptr) | static_cast<uintptr_t>(w.bytes)) & 15u) == 0;
+    if (by_engine) {
+      if (tid == 0 && bulk_ok) {
+        if (w.wait_kind != 0) asm volatile("fence.proxy.async.global;" ::: "memory");  // staged bytes were written by peers: order them before the engine's reads
+        bulk_ok = copy_bytes_bulk(bulk, dst_ptr, src_ptr, w.bytes, a.status, a.timeout_ns);
+        if (bulk_ok && w.signal_kind != 3) bulk_drain();  // a forwarder waits for this piece: its stores must have landed before the counter moves
+      }
+    } else {
+      copy_bytes(dst_ptr, src_ptr, w.bytes);
+    }
     if (w.signal_kind == 3) {
       // Output bytes are announced once, after the whole list (one barrier below covers them all).
-      if (tid == 0) s_pending[w.dst_rank] += static_cast<unsigned long long>(w.bytes);
+      if (tid == 0 && bulk_ok) s_pending[w.dst_rank] += static_cast<unsigned long long>(w.bytes);
       if (must_wait) __syncthreads();  // publishes s_peer_ready to the other threads
     } else {
       __syncthreads();  // every thread's stores precede thread 0's release below
-      if (tid == 0) {
+      if (tid == 0 && bulk_ok) {
         unsigned long long* dst_cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[w.dst_rank]) + a.sig_heap_off) + kSigCounterOff;
         const int slot = w.signal_kind == 1 ? 0 : 2 + w.stage;
         fence_sys();
@@ -123,6 +205,11 @@ __device__ __forceinline__ void run_rank(const A2ARankArgs& a) {
       }
     }
     if (stamps && tid == 0) atomicMax(stamps + 2 + 2 * phase_of(w), global_timer_ns());
+  }
+  if (a.bulk && tid == 0) {
+    bulk_drain();  // every engine store of this CTA has landed before anything is announced
+    if (!bulk_ok)  // a load never completed (already reported): announce nothing, the peers' bounded waits will say so
+      for (int i = 0; i < kSigMaxWorld; ++i) s_pending[i] = 0ull;
   }
   __syncthreads();  // all copies of this CTA are issued; announce the output bytes, one peer per thread
   if (tid < a.world && s_pending[tid] != 0ull) {
@@ -169,7 +256,12 @@ cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* dev
   if (ctas < 1 || threads < 32 || threads > 1024 || virtual_ranks < 1) return cudaErrorInvalidValue;
   if (device_args == nullptr) {
     if (host_args == nullptr || virtual_ranks != 1) return cudaErrorInvalidValue;
-    a2a_push_kernel<<<ctas, threads, 0, stream>>>(*host_args);
+    const int smem = host_args->bulk ? kBulkSmemBytes : 0;
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(a2a_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return e;
+    }
+    a2a_push_kernel<<<ctas, threads, smem, stream>>>(*host_args);
     note_launch();
   return cudaGetLastError();
   }

@@ -49,6 +49,10 @@ struct A2ARankArgs {
   // last end of the work items of phase p (0 balance, 1 rail, 2 redistribute, 3 direct), [9] end. The caller
   // presets start slots ([0] and odd slots) to all ones and the others to zero.
   unsigned long long* phase_stamps;
+  // 1: pieces whose pointers and size are multiples of 16 bytes are moved by one thread per CTA with bulk
+  // copies through shared memory (local load, then store to the peer) instead of by every thread with
+  // loads and stores. Real ranks only (the in-process group launch keeps the load/store loop).
+  int bulk;
 };
 constexpr int kPhaseStampWords = 10;
 
@@ -157,6 +161,42 @@ cudaError_t launch_build_send_list(const int* topk_idx, const int* slot_in_block
                                    int* list, DeviceStatus* status, cudaStream_t stream);
 cudaError_t launch_zero_pad_rows(void* buf, long long row_bytes, const int* group_off, const int* group_rows, int groups, cudaStream_t stream);
 
+// Router front end in one pass (moe_gate.cu): RMSNorm, router logits, top-k, softmax-over-top-k weights and the
+// per-block histogram / ranks of route_topk. num_experts <= 32, H % 256 == 0, (num_experts + 1) * H * 2 bytes of
+// shared memory (+ 4 bytes per accumulator in the backward pass).
+struct NormGateArgs {
+  const __nv_bfloat16* h;       // [T, H]
+  const __nv_bfloat16* norm_w;  // [H]
+  const __nv_bfloat16* gate;    // [E, H]
+  const float* bias;            // [E] or null: added for the expert choice only
+  int T, H, num_experts, K;
+  float eps;
+  __nv_bfloat16* hn;            // [T, H] out: h * rstd * norm_w
+  float* rstd;                  // [T] out
+  float* logits;                // [T, E] out: hn . gate^T (fp32 accumulation of the bf16 values)
+  int* topk_idx;                // [T, K] out
+  float* topk_w;                // [T, K] out
+  int* slot_in_block;           // as launch_route_topk
+  int* block_cnt;
+};
+cudaError_t launch_norm_gate_route(const NormGateArgs& a, cudaStream_t stream);
+struct NormGateBwdArgs {
+  const __nv_bfloat16* h;       // [T, H] input of the forward pass
+  const __nv_bfloat16* norm_w;  // [H]
+  const __nv_bfloat16* gate;    // [E, H]
+  const float* rstd;            // [T]
+  const int* topk_idx;          // [T, K]
+  const float* topk_w;          // [T, K]
+  const float* grad_w;          // [T, K] gradient of the routing weights
+  const __nv_bfloat16* grad_hn; // [T, H] gradient of hn from its other consumer (the MoE input)
+  int T, H, num_experts, K;
+  __nv_bfloat16* grad_h;        // [T, H] out
+  float* d_gate;                // [E, H] fp32, accumulated into (zero it first)
+  float* d_norm_w;              // [H] fp32, accumulated into
+};
+cudaError_t launch_norm_gate_bwd(const NormGateBwdArgs& a, cudaStream_t stream);
+size_t norm_gate_smem_bytes(int E, int H, int K, bool backward);
+
 struct DispatchArgs {
   void* const* peer_table;
   int rank, world, num_experts, T, K, H;
@@ -226,6 +266,12 @@ cudaError_t launch_scaled_sum(const __nv_bfloat16* a, const __nv_bfloat16* b, lo
 // Table gradient of an embedding lookup from ids sorted ascending (with their positions); rows of grad_table not named by any id are left as they are.
 cudaError_t launch_embedding_bwd(const long long* sorted_ids, const long long* perm, const __nv_bfloat16* grad_out, __nv_bfloat16* grad_table, long long T,
                                  int H, cudaStream_t stream);
+// Groups token positions by id with a counting sort (stable: positions ascending inside an id): sorted_ids / perm [T] as
+// launch_embedding_bwd takes them; entries past start[V] (ids outside [0, V)) are left as they were. Scratch: hist
+// [ceil(T / embedding_index_block())][V] ints (cleared here), rank_in_block [T], total [V], start [V + 1].
+cudaError_t launch_embedding_index(const long long* ids, long long T, int V, int* hist, int* rank_in_block, int* total, int* start, long long* sorted_ids,
+                                   long long* perm, cudaStream_t stream);
+int embedding_index_block();
 // AdamW on bf16 parameters with fp32 master weights and moments.
 cudaError_t launch_adamw(__nv_bfloat16* param, float* master, float* m, float* v, const __nv_bfloat16* grad, long long n, float lr, float beta1,
                          float beta2, float eps, float weight_decay, float bias_c1, float bias_c2, float grad_scale, cudaStream_t stream);

@@ -173,6 +173,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ sorted_ids, c
   const int lane = threadIdx.x & 31;
   if (i >= T) return;
   const long long id = sorted_ids[i];
+  if (id < 0) return;  // slots no valid id was sorted into
   if (i > 0 && sorted_ids[i - 1] == id) return;
   long long end = i + 1;
   while (end < T && sorted_ids[end] == id) ++end;
@@ -187,6 +188,93 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ sorted_ids, c
     }
     grad_table[id * chunks + c] = pack8(acc);
   }
+}
+
+// ---- ids grouped by value, positions in order: a counting sort the embedding gradient is fed from -----------
+// Work is independent of the data (heavy duplicates cost the same as none). Blocks of kIdxBlock tokens:
+//   1. per-block histogram of the ids (counts) and, per token, its rank among the block's earlier tokens with
+//      the same id (position order, so the grouping is stable and the later summation order is fixed);
+//   2. per id, the running sum over blocks (where a block's tokens of that id start inside the id's run);
+//   3. exclusive scan over the ids (where each id's run starts);
+//   4. scatter: sorted_ids / perm, the arrays embedding_bwd_kernel consumes.
+constexpr int kIdxBlock = 256;
+
+__global__ void __launch_bounds__(kIdxBlock) emb_block_hist_kernel(const long long* __restrict__ ids, long long T, int V, int* __restrict__ hist,
+                                                                   int* __restrict__ rank_in_block) {
+  __shared__ long long s_id[kIdxBlock];
+  const long long p = blockIdx.x * static_cast<long long>(kIdxBlock) + threadIdx.x;
+  long long id = -1;
+  if (p < T) { id = ids[p]; if (id < 0 || id >= V) id = -1; }  // out-of-range ids take no part (F.embedding would have refused them)
+  s_id[threadIdx.x] = id;
+  __syncthreads();
+  if (id < 0) { if (p < T) rank_in_block[p] = -1; return; }
+  int r = 0;
+  for (int j = 0; j < static_cast<int>(threadIdx.x); ++j) r += s_id[j] == id ? 1 : 0;
+  rank_in_block[p] = r;
+  atomicAdd(hist + static_cast<long long>(blockIdx.x) * V + id, 1);
+}
+
+__global__ void emb_scan_blocks_kernel(int* __restrict__ hist, int blocks, int V, int* __restrict__ total) {
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= V) return;
+  int run = 0;
+  // Eight independent loads in flight per round (the running sum is the only serial part).
+  for (int b0 = 0; b0 < blocks; b0 += 8) {
+    int c[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) c[u] = b0 + u < blocks ? hist[static_cast<long long>(b0 + u) * V + v] : 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (b0 + u < blocks) { hist[static_cast<long long>(b0 + u) * V + v] = run; run += c[u]; }  // counts become offsets inside the id's run
+  }
+  total[v] = run;
+}
+
+// Single block: start[v] = sum of total[< v]; start[V] = number of tokens that took part. Four ids per thread and pass.
+__global__ void __launch_bounds__(1024) emb_scan_ids_kernel(const int* __restrict__ total, int V, int* __restrict__ start) {
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int v0 = 0; v0 < V; v0 += 4096) {
+    const int v = v0 + 4 * threadIdx.x;
+    int x[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) x[u] = v + u < V ? total[v + u] : 0;
+    const int mine = x[0] + x[1] + x[2] + x[3];
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, w, o); if (lane >= o) w += y; }
+      s_warp[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    int before = s_carry + (warp ? s_warp[warp - 1] : 0) + incl - mine;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { if (v + u < V) start[v + u] = before; before += x[u]; }
+    __syncthreads();
+    if (threadIdx.x == 1023) s_carry = before;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) start[V] = s_carry;
+}
+
+__global__ void emb_scatter_kernel(const long long* __restrict__ ids, const int* __restrict__ rank_in_block, const int* __restrict__ hist,
+                                   const int* __restrict__ start, long long T, int V, long long* __restrict__ sorted_ids, long long* __restrict__ perm) {
+  const long long p = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (p >= T) return;
+  const int r = rank_in_block[p];
+  if (r < 0) return;
+  const long long id = ids[p];
+  const long long slot = start[id] + hist[(p / kIdxBlock) * V + id] + r;
+  sorted_ids[slot] = id;
+  perm[slot] = p;
 }
 
 int grid_for(long long items) { return static_cast<int>(std::min<long long>((items + 255) / 256, 148 * 8)); }
@@ -237,6 +325,22 @@ cudaError_t launch_embedding_bwd(const long long* sorted_ids, const long long* p
   note_launch();
   return cudaGetLastError();
 }
+cudaError_t launch_embedding_index(const long long* ids, long long T, int V, int* hist, int* rank_in_block, int* total, int* start, long long* sorted_ids,
+                                   long long* perm, cudaStream_t stream) {
+  if (T <= 0 || V <= 0) return cudaErrorInvalidValue;
+  const int blocks = static_cast<int>((T + kIdxBlock - 1) / kIdxBlock);
+  cudaError_t e = cudaMemsetAsync(hist, 0, sizeof(int) * static_cast<size_t>(blocks) * V, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaMemsetAsync(sorted_ids, 0xFF, sizeof(long long) * static_cast<size_t>(T), stream);  // -1: slots that stay unused are skipped downstream
+  if (e != cudaSuccess) return e;
+  emb_block_hist_kernel<<<blocks, kIdxBlock, 0, stream>>>(ids, T, V, hist, rank_in_block);
+  emb_scan_blocks_kernel<<<(V + 255) / 256, 256, 0, stream>>>(hist, blocks, V, total);
+  emb_scan_ids_kernel<<<1, 1024, 0, stream>>>(total, V, start);
+  emb_scatter_kernel<<<blocks, kIdxBlock, 0, stream>>>(ids, rank_in_block, hist, start, T, V, sorted_ids, perm);
+  note_launch(4);
+  return cudaGetLastError();
+}
+int embedding_index_block() { return kIdxBlock; }
 cudaError_t launch_dequant_fp8(const unsigned char* q, const float* scales, __nv_bfloat16* out, long long rows, int H, const int* rows_dev,
                                cudaStream_t stream) {
   if (H % 128) return cudaErrorInvalidValue;

@@ -66,9 +66,10 @@ struct A2AProgramPy {
 };
 
 void a2a_launch(const A2AProgramPy& p, const HeapPy& heap, std::array<int64_t, 4> src_ptrs, std::array<int64_t, 4> dst_offs,
-                int64_t sig_off, uint64_t epoch, const StatusPy& st, uint64_t timeout_ns, int ctas, int threads, int64_t stamps_ptr) {
+                int64_t sig_off, uint64_t epoch, const StatusPy& st, uint64_t timeout_ns, int ctas, int threads, int64_t stamps_ptr, bool bulk) {
   TORCH_CHECK(heap.h->world() <= kSigMaxWorld, "world larger than the signal block supports");
   A2ARankArgs a = p.args(heap, src_ptrs, dst_offs, sig_off, epoch, st, timeout_ns, stamps_ptr);
+  a.bulk = bulk ? 1 : 0;
   cuda_check(launch_a2a_push(&a, nullptr, 1, ctas, threads, cur_stream()), "a2a_push launch");
 }
 
@@ -131,7 +132,7 @@ PYBIND11_MODULE(_C, m) {
       .def_readonly("total_bytes", &A2AProgramPy::total_bytes);
 
   m.def("a2a_launch", &a2a_launch, py::arg("program"), py::arg("heap"), py::arg("src_ptrs"), py::arg("dst_offs"), py::arg("sig_off"), py::arg("epoch"),
-        py::arg("status"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("threads"), py::arg("stamps_ptr") = 0);
+        py::arg("status"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("threads"), py::arg("stamps_ptr") = 0, py::arg("bulk") = false);
   m.attr("PHASE_STAMP_WORDS") = kPhaseStampWords;
   m.attr("SIG_MAX_WORLD") = kSigMaxWorld;
   m.def("a2a_launch_group", &a2a_launch_group);

@@ -223,6 +223,41 @@ void bind_moe(py::module_& m) {
                                     static_cast<int>(topk_idx.size(0)), static_cast<int>(topk_idx.size(1)), static_cast<int>(send_pos.numel()),
                                     list.data_ptr<int>(), st.d, stream_now()), "build_send_list");
   });
+  m.def("norm_gate_smem_bytes", [](int E, int H, int K, bool backward) { return static_cast<int64_t>(norm_gate_smem_bytes(E, H, K, backward)); });
+  m.def("norm_gate_route", [](torch::Tensor h, torch::Tensor norm_w, torch::Tensor gate, c10::optional<torch::Tensor> bias, int K, double eps, torch::Tensor hn,
+                              torch::Tensor rstd, torch::Tensor logits, torch::Tensor topk_idx, torch::Tensor topk_w, torch::Tensor slot_in_block,
+                              torch::Tensor block_cnt) {
+    want(h, torch::kBFloat16, "h"); want(norm_w, torch::kBFloat16, "norm_w"); want(gate, torch::kBFloat16, "gate"); want(hn, torch::kBFloat16, "hn");
+    want(rstd, torch::kFloat32, "rstd"); want(logits, torch::kFloat32, "logits"); want(topk_idx, torch::kInt32, "topk_idx"); want(topk_w, torch::kFloat32, "topk_w");
+    want(slot_in_block, torch::kInt32, "slot_in_block"); want(block_cnt, torch::kInt32, "block_cnt");
+    NormGateArgs a{};
+    a.T = static_cast<int>(h.size(0)); a.H = static_cast<int>(h.size(1)); a.num_experts = static_cast<int>(gate.size(0)); a.K = K; a.eps = static_cast<float>(eps);
+    const int blocks = (a.T + kRouteTokensPerBlock - 1) / kRouteTokensPerBlock;
+    TORCH_CHECK(gate.size(1) == a.H && norm_w.numel() == a.H && hn.sizes() == h.sizes() && rstd.numel() >= a.T && logits.numel() == static_cast<int64_t>(a.T) * a.num_experts &&
+                topk_idx.numel() == static_cast<int64_t>(a.T) * K && topk_w.numel() == topk_idx.numel() &&
+                slot_in_block.numel() >= static_cast<int64_t>(blocks) * kRouteTokensPerBlock * K && block_cnt.numel() >= static_cast<int64_t>(blocks) * a.num_experts,
+                "norm_gate_route: shapes");
+    a.h = reinterpret_cast<const __nv_bfloat16*>(h.data_ptr()); a.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w.data_ptr());
+    a.gate = reinterpret_cast<const __nv_bfloat16*>(gate.data_ptr()); a.bias = ptr_or_null<const float>(bias);
+    a.hn = reinterpret_cast<__nv_bfloat16*>(hn.data_ptr()); a.rstd = rstd.data_ptr<float>(); a.logits = logits.data_ptr<float>();
+    a.topk_idx = topk_idx.data_ptr<int>(); a.topk_w = topk_w.data_ptr<float>(); a.slot_in_block = slot_in_block.data_ptr<int>(); a.block_cnt = block_cnt.data_ptr<int>();
+    cu_check(launch_norm_gate_route(a, stream_now()), "norm_gate_route");
+  });
+  m.def("norm_gate_bwd", [](torch::Tensor h, torch::Tensor norm_w, torch::Tensor gate, torch::Tensor rstd, torch::Tensor topk_idx, torch::Tensor topk_w,
+                            torch::Tensor grad_w, torch::Tensor grad_hn, torch::Tensor grad_h, torch::Tensor d_gate, torch::Tensor d_norm_w) {
+    want(h, torch::kBFloat16, "h"); want(norm_w, torch::kBFloat16, "norm_w"); want(gate, torch::kBFloat16, "gate"); want(rstd, torch::kFloat32, "rstd");
+    want(topk_idx, torch::kInt32, "topk_idx"); want(topk_w, torch::kFloat32, "topk_w"); want(grad_w, torch::kFloat32, "grad_w");
+    want(grad_hn, torch::kBFloat16, "grad_hn"); want(grad_h, torch::kBFloat16, "grad_h"); want(d_gate, torch::kFloat32, "d_gate"); want(d_norm_w, torch::kFloat32, "d_norm_w");
+    NormGateBwdArgs a{};
+    a.T = static_cast<int>(h.size(0)); a.H = static_cast<int>(h.size(1)); a.num_experts = static_cast<int>(gate.size(0)); a.K = static_cast<int>(topk_idx.size(1));
+    TORCH_CHECK(gate.size(1) == a.H && grad_hn.sizes() == h.sizes() && grad_h.sizes() == h.sizes() && d_gate.numel() == gate.numel() && d_norm_w.numel() == a.H &&
+                grad_w.sizes() == topk_idx.sizes() && topk_w.sizes() == topk_idx.sizes() && rstd.numel() >= a.T, "norm_gate_bwd: shapes");
+    a.h = reinterpret_cast<const __nv_bfloat16*>(h.data_ptr()); a.norm_w = reinterpret_cast<const __nv_bfloat16*>(norm_w.data_ptr());
+    a.gate = reinterpret_cast<const __nv_bfloat16*>(gate.data_ptr()); a.rstd = rstd.data_ptr<float>(); a.topk_idx = topk_idx.data_ptr<int>();
+    a.topk_w = topk_w.data_ptr<float>(); a.grad_w = grad_w.data_ptr<float>(); a.grad_hn = reinterpret_cast<const __nv_bfloat16*>(grad_hn.data_ptr());
+    a.grad_h = reinterpret_cast<__nv_bfloat16*>(grad_h.data_ptr()); a.d_gate = d_gate.data_ptr<float>(); a.d_norm_w = d_norm_w.data_ptr<float>();
+    cu_check(launch_norm_gate_bwd(a, stream_now()), "norm_gate_bwd");
+  });
   m.def("dispatch_push", &dispatch_push, py::arg("heap"), py::arg("x"), py::arg("topk_idx"), py::arg("row_scale"), py::arg("slot_in_block"), py::arg("block_base"),
         py::arg("send_base"), py::arg("dest_row"), py::arg("compute_rows"), py::arg("fp8"), py::arg("recv_off"), py::arg("scale_off"), py::arg("arrive_off"),
         py::arg("entry_flags_off"), py::arg("entry_epoch"), py::arg("status"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("send_list"),
@@ -269,6 +304,18 @@ void bind_moe(py::module_& m) {
     cu_check(launch_embedding_bwd(reinterpret_cast<const long long*>(sorted_ids.data_ptr()), reinterpret_cast<const long long*>(perm.data_ptr()),
                                   reinterpret_cast<const __nv_bfloat16*>(grad_out.data_ptr()), reinterpret_cast<__nv_bfloat16*>(grad_table.data_ptr()),
                                   sorted_ids.numel(), static_cast<int>(grad_out.size(1)), stream_now()), "embedding_bwd");
+  });
+  m.def("embedding_index", [](torch::Tensor ids, int V) {
+    want(ids, torch::kInt64, "ids");
+    const int64_t T = ids.numel();
+    const int64_t blocks = (T + embedding_index_block() - 1) / embedding_index_block();
+    auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(ids.device());
+    auto hist = torch::empty({blocks, V}, i32), rank = torch::empty({T}, i32), total = torch::empty({V}, i32), start = torch::empty({V + 1}, i32);
+    auto sorted_ids = torch::empty({T}, ids.options()), perm = torch::empty({T}, ids.options());
+    cu_check(launch_embedding_index(reinterpret_cast<const long long*>(ids.data_ptr()), T, V, hist.data_ptr<int>(), rank.data_ptr<int>(), total.data_ptr<int>(),
+                                    start.data_ptr<int>(), reinterpret_cast<long long*>(sorted_ids.data_ptr()), reinterpret_cast<long long*>(perm.data_ptr()), stream_now()),
+             "embedding_index");
+    return std::make_tuple(sorted_ids, perm);
   });
   m.def("adamw", [](torch::Tensor param, torch::Tensor master, torch::Tensor m1, torch::Tensor v, torch::Tensor grad, double lr, double b1, double b2,
                     double eps, double wd, int64_t step, double grad_scale) {

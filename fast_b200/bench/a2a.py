@@ -189,6 +189,18 @@ def run(args):
                                          [("ours_staged_pieces", PlanKind.STAGED, {"rail_segment_bytes": args.rail_segment})] if args.servers and args.rail_segment > 0 else []):
                     s = comm.schedule(m, unit_bytes=1, kind=kind, chunk_bytes=args.chunk or None, **opts)
                     variants[name] = (lambda s=s: comm.all_to_all_v(out, inp, s))
+                if args.bulk:
+                    # the same fan-out plan with the bulk-copy engine doing the transfers (one thread per CTA)
+                    sb = comm.schedule(m, unit_bytes=1, kind=PlanKind.FANOUT, chunk_bytes=args.chunk or None)
+
+                    def bulk_run(s=sb):
+                        comm.bulk_copy = True
+                        try:
+                            comm.all_to_all_v(out, inp, s)
+                        finally:
+                            comm.bulk_copy = False
+
+                    variants["ours_fanout_bulk_copy"] = bulk_run
                 if args.p2p_baseline:
                     # The reference's executor style: the staged plan run phase by phase over library
                     # send/recv groups (here NCCL), host-synchronised between phases.
@@ -244,6 +256,7 @@ def main():
     ap.add_argument("--sizes", type=int, nargs="+", default=[64 << 20])
     ap.add_argument("--skews", type=float, nargs="+", default=[0.0, 0.5, 1.0, 1.5])
     ap.add_argument("--matrices", type=int, default=20, help="fresh seeded matrices per point")
+    ap.add_argument("--bulk", action="store_true", help="also time the fan-out plan with bulk copies through shared memory instead of load/store loops")
     ap.add_argument("--e2e", action="store_true", help="also time schedule() + launch + completion on a never-seen matrix per drawn matrix (wall clock, max over ranks)")
     ap.add_argument("--phases", action="store_true", help="per-phase breakdown (balance / rail / redistribute / direct) of the staged plan from device time stamps")
     ap.add_argument("--iters", type=int, default=10)

@@ -41,31 +41,64 @@ class _MoEFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         weights, w13, w2 = ctx.saved_tensors
-        eng = ctx.engine
-        if not hasattr(eng, "_dw13") or eng._dw13.shape != w13.shape:
-            eng._dw13, eng._dw2 = torch.empty_like(w13), torch.empty_like(w2)
-        opt = getattr(eng, "optimizer_in_backward", None)
-        early = opt is not None and opt.owns(ctx.w2_param)
-        after = None
-        if early:
-            # W2's update runs on a side stream under the remaining GEMMs (W13 dgrad / wgrad): after the
-            # W2 wgrad nothing in this pass reads W2 any more.
-            main = torch.cuda.current_stream()
-            if not hasattr(eng, "_opt_stream"):
-                eng._opt_stream = torch.cuda.Stream(device=grad_out.device)
+        gx, gw, dw13, dw2 = _experts_backward(ctx.engine, grad_out, ctx.rs, weights.detach().float().contiguous(), w13, w2, ctx.w2_param)
+        return gx, gw.to(weights.dtype), dw13, dw2, None, None
 
-            def after():
-                ev = torch.cuda.Event()
-                ev.record(main)
-                eng._opt_stream.wait_event(ev)
-                opt.step_param(ctx.w2_param, eng._dw2, stream=eng._opt_stream, early=True)
 
-        gx, gw = eng.backward(grad_out.contiguous(), ctx.rs, weights.detach().float().contiguous(), w13, w2, eng._dw13, eng._dw2, after_dw2=after)
-        if early:
-            done = torch.cuda.Event()
-            done.record(eng._opt_stream)
-            torch.cuda.current_stream().wait_event(done)  # the next kernels on this stream may read W2 / reuse dW2
-        return gx, gw.to(weights.dtype), eng._dw13, (None if early else eng._dw2), None, None
+def _experts_backward(eng, grad_out, rs, weights, w13, w2, w2_param):
+    """Backward of dispatch -> experts -> combine through the engine. Returns (grad_x, grad_weights, dW13,
+    dW2 or None); dW2 is None when an attached optimizer applied W2's update inside the pass."""
+    if not hasattr(eng, "_dw13") or eng._dw13.shape != w13.shape:
+        eng._dw13, eng._dw2 = torch.empty_like(w13), torch.empty_like(w2)
+    opt = getattr(eng, "optimizer_in_backward", None)
+    early = opt is not None and opt.owns(w2_param)
+    after = None
+    if early:
+        # W2's update runs on a side stream under the remaining GEMMs (W13 dgrad / wgrad): after the
+        # W2 wgrad nothing in this pass reads W2 any more.
+        main = torch.cuda.current_stream()
+        if not hasattr(eng, "_opt_stream"):
+            eng._opt_stream = torch.cuda.Stream(device=grad_out.device)
+
+        def after():
+            ev = torch.cuda.Event()
+            ev.record(main)
+            eng._opt_stream.wait_event(ev)
+            opt.step_param(w2_param, eng._dw2, stream=eng._opt_stream, early=True)
+
+    gx, gw = eng.backward(grad_out.contiguous(), rs, weights, w13, w2, eng._dw13, eng._dw2, after_dw2=after)
+    if early:
+        done = torch.cuda.Event()
+        done.record(eng._opt_stream)
+        torch.cuda.current_stream().wait_event(done)  # the next kernels on this stream may read W2 / reuse dW2
+    return gx, gw, eng._dw13, (None if early else eng._dw2)
+
+
+class _NormRouteMoEFunction(torch.autograd.Function):
+    """h -> RMSNorm -> router -> dispatch -> experts -> combine, with the router front end fused into one
+    kernel each way (no library GEMM, layer-norm, gather or softmax kernel on the path)."""
+
+    @staticmethod
+    def forward(ctx, h, norm_w, gate, w13, w2, engine, eps, layer):
+        rs, hn, rstd, _ = engine.route_fused(h, norm_w, gate, eps, layer.router_bias)
+        layer.last_route = rs
+        engine.dispatch(hn, rs)
+        engine.experts_forward(w13, w2, rs)
+        out = engine.combine(rs, rs.topk_w)
+        ctx.engine, ctx.rs, ctx.w2_param = engine, rs, w2
+        ctx.save_for_backward(h, norm_w, gate, rstd, w13, w2)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        h, norm_w, gate, rstd, w13, w2 = ctx.saved_tensors
+        eng, rs = ctx.engine, ctx.rs
+        gx, gw, dw13, dw2 = _experts_backward(eng, grad_out, rs, rs.topk_w, w13, w2, ctx.w2_param)
+        grad_h = torch.empty_like(h)
+        d_gate = torch.zeros(gate.shape, dtype=torch.float32, device=h.device)
+        d_nw = torch.zeros(norm_w.shape, dtype=torch.float32, device=h.device)
+        eng._C.norm_gate_bwd(h, norm_w, gate, rstd, rs.topk_idx, rs.topk_w, gw, gx, grad_h, d_gate, d_nw)
+        return grad_h, d_nw.to(norm_w.dtype), d_gate.to(gate.dtype), dw13, dw2, None, None, None
 
 
 class MoELayer(nn.Module):
@@ -121,6 +154,15 @@ class MoELayer(nn.Module):
         self.engine.experts_forward(self.w13, self.w2, rs)
         return self.engine.combine(rs, rs.topk_w)
 
+    def forward_from_residual(self, h: torch.Tensor, norm_w: torch.Tensor, eps: float) -> torch.Tensor:
+        """MoE(RMSNorm(h; norm_w)) for h [tokens, hidden] bf16. When the layer's shapes allow it the norm,
+        the router logits, the top-k and their backward run as one fused kernel each way; otherwise this is
+        ``self(rms_norm(h))`` with stock ops in front."""
+        fused = self.engine.can_fuse_gate() and torch.is_grad_enabled() and self.training and h.dtype == torch.bfloat16
+        if not fused:
+            return self(torch.nn.functional.rms_norm(h, (h.shape[-1],), norm_w, eps))
+        return _NormRouteMoEFunction.apply(h.contiguous(), norm_w, self.gate, self.w13, self.w2, self.engine, eps, self)
+
     def attach_optimizer(self, opt) -> None:
         """Optimizer-in-backward: ``opt`` (a FusedAdamW owning ``w2``) applies W2's update as soon as
         its gradient exists, overlapped with the rest of the backward pass; ``opt.step()`` then
@@ -161,8 +203,7 @@ class MixtralBlockModel(nn.Module):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         h = fused.embedding(token_ids.reshape(-1), self.embed)
-        hn = torch.nn.functional.rms_norm(h, (h.shape[-1],), self.norm_w, self.eps)
-        return fused.residual_mean_square(h, self.moe(hn))
+        return fused.residual_mean_square(h, self.moe.forward_from_residual(h, self.norm_w, self.eps))
 
 
 @torch.no_grad()

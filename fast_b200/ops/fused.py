@@ -18,7 +18,8 @@ class _Embedding(torch.autograd.Function):
     def backward(ctx, grad_out):
         (ids,) = ctx.saved_tensors
         grad_table = torch.zeros(ctx.shape, dtype=grad_out.dtype, device=grad_out.device)
-        sorted_ids, perm = torch.sort(ids.reshape(-1), stable=True)
+        # positions grouped by id by this library's counting sort (stable, cost independent of duplicates)
+        sorted_ids, perm = runtime.ext().embedding_index(ids.reshape(-1).contiguous(), ctx.shape[0])
         runtime.ext().embedding_bwd(sorted_ids, perm, grad_out.reshape(-1, ctx.shape[1]).contiguous(), grad_table)
         return None, grad_table
 

@@ -122,6 +122,9 @@ class Communicator:
         # PeerLost on the host instead of making a kernel wait for its timeout.
         self.liveness = None
         self.liveness_max_age_s = 2.0
+        # True: 16-byte aligned pieces are moved by the bulk-copy engine (one thread per CTA, shared-memory ring)
+        # instead of by load/store loops of every thread.
+        self.bulk_copy = bool(CONFIG.a2a_bulk)
 
     # ---- symmetric memory ---------------------------------------------------------------------
     def alloc(self, shape, dtype=torch.uint8, verify: Optional[bool] = None) -> torch.Tensor:
@@ -303,7 +306,7 @@ class Communicator:
         self.epoch += 1
         ctas = max(1, min(self.ctas, s.program.n_items))  # a handful of work items needs a handful of CTAs
         self._C.a2a_launch(s.program, self.heap, src, dst, self.sig_off, self.epoch, self.status, self.timeout_ns, ctas, self.threads,
-                           0 if phase_stamps is None else phase_stamps.data_ptr())
+                           0 if phase_stamps is None else phase_stamps.data_ptr(), self.bulk_copy and not self._virtual)
         if copy_back is not None:
             output.view(torch.uint8).reshape(-1)[: s.output_bytes].copy_(copy_back[: s.output_bytes])
         return output

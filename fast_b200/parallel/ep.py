@@ -188,6 +188,33 @@ class ExpertParallel:
         return RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows,
                           0 if self.graph_mode else self.epoch)
 
+    def can_fuse_gate(self) -> bool:
+        """Whether ``route_fused`` (RMSNorm + router logits + top-k in one kernel) covers this layer."""
+        C = self._C
+        return self.E <= 32 and self.H <= 8192 and C.norm_gate_smem_bytes(self.E, self.H, self.K, True) <= 220 * 1024 and not self.graph_mode
+
+    def route_fused(self, h: torch.Tensor, norm_w: torch.Tensor, gate: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None):
+        """RMSNorm of ``h``, router logits against ``gate`` and the routing of ``route`` in one kernel:
+        returns ``(RouteState, hn, rstd, logits)`` with ``hn`` the normalised rows (the MoE input)."""
+        C = self._C
+        T = h.shape[0]
+        assert T <= self.T and h.shape[1] == self.H and gate.shape == (self.E, self.H)
+        dev = h.device
+        topk_idx = torch.empty(T, self.K, dtype=torch.int32, device=dev)
+        topk_w = torch.empty(T, self.K, dtype=torch.float32, device=dev)
+        dest_row = torch.empty(T, self.K, dtype=torch.int32, device=dev)
+        hn = torch.empty_like(h)
+        rstd = torch.empty(T, dtype=torch.float32, device=dev)
+        logits = torch.empty(T, self.E, dtype=torch.float32, device=dev)
+        nb = (T + C.ROUTE_TOKENS_PER_BLOCK - 1) // C.ROUTE_TOKENS_PER_BLOCK
+        C.norm_gate_route(h, norm_w, gate, bias, self.K, eps, hn, rstd, logits, topk_idx, topk_w, self.slot_in_block, self.block_cnt[:nb])
+        self.epoch += 1
+        C.splits_scan(self.comm.heap, self._off(self.counts), self._flag_off(0), self.epoch, self.block_cnt[:nb], self.block_base[:nb], self.send_base,
+                      self.send_cnt, self.group_off, self.group_rows, self.arrive_target[: 2 if self.training else 1], self.traffic, 2 if self.training else 1,
+                      gemm.row_align(), self.cap, self.status, self.timeout_ns, self.send_pos if self.overlap else None, 0, self.tile_target, self.tile_rows)
+        rs = RouteState(topk_idx, topk_w, dest_row, self.slot_in_block, self.block_base, self.send_base, self.group_off, self.group_rows, self.epoch)
+        return rs, hn, rstd, logits
+
     def dispatch(self, x: torch.Tensor, rs: RouteState) -> None:
         C = self._C
         send_list = None

@@ -10,6 +10,7 @@ these are the knobs of this implementation:
   FASTB_TIMEOUT_S=<sec>   default limit of device-side waits for new communicators (default 5)
   FASTB_LOG=1             one line per scheduled collective (stages, ops, modeled time) on rank 0
   FASTB_CHECK_SYMM=1      every symmetric allocation is compared across ranks (one host collective each)
+  FASTB_A2A_BULK=1        all-to-all(v) kernel moves 16-byte aligned pieces with bulk copies through shared memory
 """
 from __future__ import annotations
 
@@ -25,6 +26,7 @@ class Config:
     timeout_s: float = float(os.environ.get("FASTB_TIMEOUT_S", "5"))
     log: bool = os.environ.get("FASTB_LOG", "0") == "1"
     check_symm: bool = os.environ.get("FASTB_CHECK_SYMM", "0") == "1"
+    a2a_bulk: bool = os.environ.get("FASTB_A2A_BULK", "0") == "1"
 
 
 CONFIG = Config()

@@ -76,12 +76,18 @@ def main():
                 out.zero_()
                 torch.cuda.synchronize()
                 dist.barrier()
-                for _ in range(2):
-                    comm.all_to_all_v(out, d_in, s)
-                comm.check()
                 want = np.concatenate([((src << 24) | (rank << 16) | (np.arange(int(m[src, rank]) // 4) & 0xFFFF)).astype(np.int32) for src in range(world)])
-                got = out[: want.size * 4].view(torch.int32).cpu().numpy()
-                assert np.array_equal(got, want), f"rank {rank} kind {kind} seed {seed} topo {topo}"
+                for bulk in ((False, True) if seed == 0 else (False,)):   # also with the bulk-copy engine doing the transfers
+                    comm.bulk_copy = bulk
+                    out.zero_()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    for _ in range(2):
+                        comm.all_to_all_v(out, d_in, s)
+                    comm.check()
+                    got = out[: want.size * 4].view(torch.int32).cpu().numpy()
+                    assert np.array_equal(got, want), f"rank {rank} kind {kind} seed {seed} topo {topo} bulk {bulk}"
+                comm.bulk_copy = False
         # torch.distributed-style entry point with uneven row splits
         rows = [(rank + d) % 3 + 1 for d in range(world)]
         x = torch.full((sum(rows), 8), float(rank), device="cuda", dtype=torch.bfloat16)

@@ -127,6 +127,56 @@ def test_expert_ids_out_of_range_are_skipped_and_reported():
     assert int((torch.ones(8, device="cuda") * 3).sum().item()) == 24  # context still healthy
 
 
+@pytest.mark.parametrize("T,H,E,K", [(300, 256, 8, 2), (1000, 512, 32, 6), (129, 1024, 4, 1)])
+def test_fused_norm_router_forward_and_backward_match_torch(T, H, E, K):
+    """RMSNorm + router logits + top-k (+ softmax-over-top-k weights) in one kernel, and its backward
+    (gate, norm-weight and input gradients), against the same chain of plain fp32 PyTorch ops."""
+    from fast_b200 import runtime
+
+    C = runtime.ext()
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    h = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    nw = (1.0 + 0.1 * torch.randn(H, generator=g, device="cuda")).to(torch.bfloat16)
+    gate = (torch.randn(E, H, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    nb = (T + C.ROUTE_TOKENS_PER_BLOCK - 1) // C.ROUTE_TOKENS_PER_BLOCK
+    hn = torch.empty_like(h)
+    rstd = torch.empty(T, device="cuda")
+    logits = torch.empty(T, E, device="cuda")
+    idx = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, K, device="cuda")
+    slot = torch.zeros(nb * C.ROUTE_TOKENS_PER_BLOCK, K, dtype=torch.int32, device="cuda")
+    cnt = torch.zeros(nb, E, dtype=torch.int32, device="cuda")
+    eps = 1e-5
+    C.norm_gate_route(h, nw, gate, None, K, eps, hn, rstd, logits, idx, w, slot, cnt)
+    # fp32 reference with autograd; the expert choice is pinned to the kernel's (near-ties may flip)
+    hr = h.float().requires_grad_()
+    nwr = nw.float().requires_grad_()
+    gr = gate.float().requires_grad_()
+    hn_ref = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + eps) * nwr
+    lg_ref = hn_ref @ gr.t()
+    assert _rel(hn, hn_ref) < 1e-2 and _rel(logits, lg_ref) < 1e-2
+    top_ref = lg_ref.topk(K, dim=-1)
+    agree = (idx.long().sort(-1).values == top_ref.indices.sort(-1).values).all(-1).float().mean().item()
+    assert agree > 0.98                                       # bf16 rounding of hn may flip near-ties
+    assert int(idx.min()) >= 0 and int(idx.max()) < E and int(cnt.sum()) == T * K
+    w_ref = torch.softmax(lg_ref.gather(1, idx.long()), dim=-1)
+    assert torch.allclose(w, w_ref, atol=2e-2)
+    for b in range(nb):
+        blk = idx[b * 128:(b + 1) * 128].reshape(-1).long()
+        assert torch.equal(cnt[b].long(), torch.bincount(blk, minlength=E))
+    # backward: loss = sum(w * gw) + sum(hn * ghn)
+    gw = torch.randn(T, K, generator=g, device="cuda")
+    ghn = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    ((w_ref * gw).sum() + (hn_ref * ghn.float()).sum()).backward()
+    grad_h = torch.empty_like(h)
+    d_gate = torch.zeros(E, H, device="cuda")
+    d_nw = torch.zeros(H, device="cuda")
+    C.norm_gate_bwd(h, nw, gate, rstd, idx, w, gw, ghn, grad_h, d_gate, d_nw)
+    assert _rel(grad_h, hr.grad) < 2e-2
+    assert _rel(d_gate, gr.grad) < 2e-2
+    assert _rel(d_nw, nwr.grad) < 2e-2
+
+
 def test_elementwise_kernels():
     from fast_b200 import runtime
     from fast_b200.models.moe import split_gate_up
@@ -160,6 +210,21 @@ def test_elementwise_kernels():
         opt.step()
     assert torch.allclose(master, ref_p.detach(), atol=1e-5, rtol=1e-5)
     assert torch.equal(pb, master.to(torch.bfloat16))
+
+
+def test_embedding_index_is_a_stable_sort_by_id():
+    """The counting sort that feeds the embedding gradient equals torch's stable sort, with few and with heavy duplicates."""
+    from fast_b200 import runtime
+
+    C = runtime.ext()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    for T, V, hot in ((5000, 3000, 0), (4097, 70000, 0), (3000, 50, 0), (2500, 1000, 2000)):
+        ids = torch.randint(0, V, (T,), generator=g, device="cuda")
+        if hot:
+            ids[torch.randperm(T, generator=g, device="cuda")[:hot]] = 7     # one id taking most of the positions
+        sid, perm = C.embedding_index(ids, V)
+        rs, rp = torch.sort(ids, stable=True)
+        assert torch.equal(sid, rs) and torch.equal(perm, rp)
 
 
 def test_fused_embedding_and_loss_match_torch():
