@@ -9,7 +9,9 @@
 // counters and the ready flags do not order is reported as a data race. Results are also checked
 // against values computed directly from the routing. Forward-only runs are repeated with the fp8
 // receive path (quantised buffer written by peers, converted locally after all experts arrived)
-// and with the dispatch overlapped with the gated GEMMs on a side stream.
+// and with the dispatch overlapped with the gated GEMMs on a side stream, and once more with arrivals
+// counted and gated per tile of the receive buffer (the forward-only layer's scheme), including the
+// direct read of the quantised rows by the GEMM.
 #include <atomic>
 #include <cstdint>
 #include <cstdio>
@@ -25,7 +27,7 @@ constexpr int H = 4;        // words per row
 constexpr int RA = 4;       // group rows are padded to a multiple of this
 constexpr int kWorkers = 3;
 
-struct Cfg { int W, El, K, T, steps; bool training; bool bwd_entry_handshake; bool fp8 = false; bool overlap = false; };
+struct Cfg { int W, El, K, T, steps; bool training; bool bwd_entry_handshake; bool fp8 = false; bool overlap = false; bool tiles = false; };
 
 uint64_t mix(uint64_t x) { x += 0x9e3779b97f4a7c15ull; x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull; x = (x ^ (x >> 27)) * 0x94d049bb133111ebull; return x ^ (x >> 31); }
 
@@ -34,6 +36,8 @@ struct Rank {
   std::vector<int> counts;                                // [W][E] plain: written by peers' split scans
   std::unique_ptr<std::atomic<uint64_t>[]> flags;         // [4][W]: 0 counts, 1 y ready, 2 bwd entry, 3 dx ready
   std::unique_ptr<std::atomic<uint64_t>[]> arrive;        // [2][El] monotone row counters
+  std::unique_ptr<std::atomic<uint64_t>[]> tile_arrive;   // [cap / RA] monotone row counters per tile of RA rows (forward-only layer)
+  std::vector<uint64_t> tile_target;                      // [cap / RA] local
   std::vector<uint32_t> x_recv, y, dy_recv, dx_recv;      // [cap][H] plain
   std::vector<uint32_t> xq_recv;                          // [cap][H] plain: quantised rows (fp8 dispatch); x_recv is then local
   // local
@@ -106,6 +110,8 @@ void run_rank(World& w, int me) {
         my.group_off[le] = base; my.group_rows[le] = tot[e];
         if (le == El - 1) my.group_off[El] = base + padded[e];
         for (int ch = 0; ch < (c.training ? 2 : 1); ++ch) my.target[ch * El + le] += static_cast<uint64_t>(tot[e]);
+        if (c.tiles)  // the same per tile: this expert's rows fill its tiles from `base` on
+          for (int r0 = 0; r0 < tot[e]; r0 += RA) my.tile_target[(base + r0) / RA] += static_cast<uint64_t>(tot[e] - r0 < RA ? tot[e] - r0 : RA);
       }
     }
     if (my.group_off[El] > w.cap) { w.failures.fetch_add(1); w.abort.store(1); std::printf("FAIL: capacity\n"); return; }
@@ -124,8 +130,10 @@ void run_rank(World& w, int me) {
     // its (then purely local) x_recv and runs the GEMMs ungated. overlap mode: the dispatch runs on a
     // side stream at the same time as the gated GEMMs of the main stream.
     if (!c.fp8) zero_pad(my.x_recv);
+    const int ntiles = w.cap / RA;
     auto dispatch = [&](int k, int n) {
       std::vector<int> sent(E, 0);
+      std::vector<int> sent_tile(c.tiles ? static_cast<size_t>(W) * ntiles : 0, 0);  // the kernel's per-CTA histogram of destination tiles
       for (int t = k; t < T; t += n)
         for (int j = 0; j < K; ++j) {
           const int e = topk[t * K + j];
@@ -133,11 +141,37 @@ void run_rank(World& w, int me) {
           uint32_t* dst = (c.fp8 ? owner.xq_recv : owner.x_recv).data() + static_cast<size_t>(dest_row[t * K + j]) * H;
           for (int i = 0; i < H; ++i) dst[i] = x_word(me, step, t, i) ^ (c.fp8 ? 0x5a5a0000u : 0u);
           ++sent[e];
+          if (c.tiles) ++sent_tile[static_cast<size_t>(e / El) * ntiles + dest_row[t * K + j] / RA];
         }
+      if (c.tiles) {
+        for (int p = 0; p < W; ++p)
+          for (int tl = 0; tl < ntiles; ++tl)
+            if (sent_tile[static_cast<size_t>(p) * ntiles + tl])
+              w.r[p]->tile_arrive[tl].fetch_add(static_cast<uint64_t>(sent_tile[static_cast<size_t>(p) * ntiles + tl]), std::memory_order_release);
+        return;
+      }
       for (int e = 0; e < E; ++e)
         if (sent[e]) w.r[e / El]->arrive[0 * El + e % El].fetch_add(static_cast<uint64_t>(sent[e]), std::memory_order_release);
     };
     auto gemms = [&](int k, int n) {
+      if (c.tiles) {
+        // Tile-gated first GEMM of the forward-only layer: a worker takes tiles of RA rows round robin and waits only
+        // for the tile it is about to read. With fp8 it reads the quantised rows directly (the converter warps'
+        // role) and counts rows past the group's real end as zeros.
+        int tile_no = 0;
+        for (int le = 0; le < El; ++le)
+          for (int row0 = my.group_off[le]; row0 < my.group_off[le + 1]; row0 += RA, ++tile_no) {
+            if (tile_no % n != k) continue;
+            if (!wait_ge(w, my.tile_arrive[row0 / RA], my.tile_target[row0 / RA])) return;
+            for (int row = row0; row < row0 + RA; ++row)
+              for (int i = 0; i < H; ++i) {
+                const bool live = row < my.group_off[le] + my.group_rows[le];
+                const uint32_t v = !live ? 0u : c.fp8 ? my.xq_recv[static_cast<size_t>(row) * H + i] ^ 0x5a5a0000u : my.x_recv[static_cast<size_t>(row) * H + i];
+                my.y[static_cast<size_t>(row) * H + i] = v * 3 + static_cast<uint32_t>(me * El + le + 1);
+              }
+          }
+        return;
+      }
       for (int le = k; le < El; le += n) {
         if (!c.fp8 && !wait_ge(w, my.arrive[0 * El + le], my.target[0 * El + le])) return;
         for (int row = my.group_off[le]; row < my.group_off[le + 1]; ++row)
@@ -151,7 +185,7 @@ void run_rank(World& w, int me) {
     std::thread side;
     if (c.overlap) side = std::thread([&] { parallel(kWorkers, dispatch); });
     else parallel(kWorkers, dispatch);
-    if (c.fp8) {
+    if (c.fp8 && !c.tiles) {
       // wait_counters + dequant: all local experts complete, then quantised rows -> x_recv (real rows only), pad rows zeroed
       bool ok = true;
       for (int le = 0; le < El && ok; ++le) ok = wait_ge(w, my.arrive[0 * El + le], my.target[0 * El + le]);
@@ -235,6 +269,9 @@ int run(const Cfg& c) {
     k->counts.assign(static_cast<size_t>(c.W) * w.E, 0);
     k->flags.reset(new std::atomic<uint64_t>[4 * c.W]);
     k->arrive.reset(new std::atomic<uint64_t>[2 * c.El]);
+    k->tile_arrive.reset(new std::atomic<uint64_t>[w.cap / RA]);
+    for (int i = 0; i < w.cap / RA; ++i) k->tile_arrive[i].store(0);
+    k->tile_target.assign(w.cap / RA, 0);
     for (int i = 0; i < 4 * c.W; ++i) k->flags[i].store(0);
     for (int i = 0; i < 2 * c.El; ++i) k->arrive[i].store(0);
     for (auto* b : {&k->x_recv, &k->xq_recv, &k->y, &k->dy_recv, &k->dx_recv, &k->gu}) b->assign(static_cast<size_t>(w.cap) * H, 0);
@@ -267,7 +304,13 @@ int main(int argc, char** argv) {
             failures += run(f);
             Cfg o = c; o.overlap = true;
             failures += run(o);
-            runs += 2;
+            Cfg t1 = c; t1.tiles = true;                     // arrivals counted and gated per tile
+            failures += run(t1);
+            Cfg t2 = c; t2.tiles = true; t2.fp8 = true;      // ... with the quantised rows read by the GEMM itself
+            failures += run(t2);
+            Cfg t3 = c; t3.tiles = true; t3.overlap = true;  // ... with the dispatch on a side stream
+            failures += run(t3);
+            runs += 5;
           }
         }
   std::printf("{\"twin_check\":\"moe step protocol\",\"runs\":%d,\"steps\":%d,\"failures\":%d}\n", runs, steps, failures);
