@@ -9,6 +9,7 @@
 // the rail GPU is the destination, staging regions are never reused inside a collective (no
 // ping-pong credits), counters only grow inside a collective and are cleared by the last CTA
 // after every wait has been satisfied, and each wait is bounded.
+#include <algorithm>
 #include <atomic>
 
 #include "api.h"
@@ -252,7 +253,7 @@ unsigned long long launch_count() { return g_launches.load(std::memory_order_rel
 void note_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
 
 cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* device_args, int virtual_ranks, int ctas, int threads,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, bool needs_coresidency) {
   if (ctas < 1 || threads < 32 || threads > 1024 || virtual_ranks < 1) return cudaErrorInvalidValue;
   if (device_args == nullptr) {
     if (host_args == nullptr || virtual_ranks != 1) return cudaErrorInvalidValue;
@@ -261,9 +262,27 @@ cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* dev
       cudaError_t e = cudaFuncSetAttribute(a2a_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return e;
     }
+    // The grid never exceeds what one GPU can hold at once. A plan with waiting work items (two-tier plans: forwarders
+    // wait for balance / rail arrivals that peers push, while peers' forwarders wait for what this rank pushes) is
+    // launched cooperatively: the driver then starts it only when the whole grid can be resident, so a waiting CTA
+    // can never keep a pushing one of the same launch off the GPU.
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a2a_push_kernel, threads, smem);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    ctas = std::min(ctas, sms * per_sm);
+    if (needs_coresidency) {
+      A2ARankArgs args = *host_args;
+      void* params[] = {&args};
+      e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(a2a_push_kernel), dim3(ctas), dim3(threads), params, smem, stream);
+      if (e == cudaSuccess) note_launch();
+      return e;
+    }
     a2a_push_kernel<<<ctas, threads, smem, stream>>>(*host_args);
     note_launch();
-  return cudaGetLastError();
+    return cudaGetLastError();
   }
   // All virtual ranks wait on one another, so they must be co-resident: cooperative launch.
   void* params[] = {const_cast<A2ARankArgs**>(&device_args)};

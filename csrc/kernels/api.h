@@ -27,6 +27,8 @@ struct A2AWork {
 static_assert(sizeof(A2AWork) == 48, "A2AWork layout is shared with the host packer");
 
 constexpr int kSigReadyOff = 0;      // u64 ready[world]   (written by peers: their current epoch)
+// Peers one signal block has room for. A launch on a larger world is refused by the binding; planning, lowering and
+// the host executors have no such limit (beyond 64 ranks a communicator plans one-rank views of a plan).
 constexpr int kSigMaxWorld = 64;
 constexpr int kSigCounterOff = kSigMaxWorld;  // u64 counters: [0] balance, [1] output, [2+k] rail stage k
 constexpr int kSigMaxStages = 4096;
@@ -59,8 +61,10 @@ constexpr int kPhaseStampWords = 10;
 // device_args == nullptr: one real rank, `host_args` is passed by value. Otherwise one cooperative
 // launch with gridDim.y = virtual_ranks runs every rank of an in-process group (single-GPU
 // emulation); `device_args` points to an array of virtual_ranks structs in device memory.
+// needs_coresidency (real ranks): the work list has items that wait for other items of the same launch; the kernel is
+// then launched cooperatively so that its whole grid is resident at once.
 cudaError_t launch_a2a_push(const A2ARankArgs* host_args, const A2ARankArgs* device_args, int virtual_ranks, int ctas,
-                            int threads, cudaStream_t stream);
+                            int threads, cudaStream_t stream, bool needs_coresidency = false);
 
 // Waits (bounded) on a flag nothing sets; used to test the timeout path without any peer.
 cudaError_t launch_wait_probe(const unsigned long long* flag, unsigned long long want, DeviceStatus* status,

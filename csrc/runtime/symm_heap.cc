@@ -43,6 +43,38 @@ std::vector<SymmHeap*> SymmHeap::create_local_group(int world, size_t bytes) {
   return hs;
 }
 
+std::vector<SymmHeap*> SymmHeap::create_device_group(const std::vector<int>& devices, size_t bytes) {
+  const int world = static_cast<int>(devices.size());
+  if (world < 1) throw std::invalid_argument("SymmHeap: need at least one device");
+  int before = 0;
+  check(cudaGetDevice(&before), "cudaGetDevice");
+  std::vector<void*> slabs(world, nullptr);
+  for (int r = 0; r < world; ++r) {
+    check(cudaSetDevice(devices[r]), "cudaSetDevice");
+    for (int q = 0; q < world; ++q) {
+      if (devices[q] == devices[r]) continue;
+      const cudaError_t e = cudaDeviceEnablePeerAccess(devices[q], 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();  // clears the sticky-free error
+      else check(e, "cudaDeviceEnablePeerAccess");
+    }
+    check(cudaMalloc(&slabs[r], bytes), "cudaMalloc slab");
+    check(cudaMemset(slabs[r], 0, bytes), "cudaMemset slab");
+  }
+  std::vector<SymmHeap*> hs;
+  for (int r = 0; r < world; ++r) {
+    check(cudaSetDevice(devices[r]), "cudaSetDevice");
+    SymmHeap* h = new SymmHeap();
+    h->rank_ = r; h->world_ = world; h->bytes_ = bytes;
+    h->peer_base_ = slabs;
+    h->ranges_ = RangeAllocator(bytes);
+    h->opened_ = true;
+    h->upload_table();  // the table lives on this rank's device
+    hs.push_back(h);
+  }
+  check(cudaSetDevice(before), "cudaSetDevice");
+  return hs;
+}
+
 void SymmHeap::close_peers() {
   for (int r = 0; r < world_; ++r) {
     if (r == rank_ || !peer_base_[r]) continue;

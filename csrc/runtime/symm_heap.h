@@ -24,6 +24,9 @@ class SymmHeap {
   // In-process group of `world` virtual ranks on the current device (single-GPU emulation and
   // tests): returns heaps that already see each other.
   static std::vector<SymmHeap*> create_local_group(int world, size_t bytes);
+  // In-process group with rank r on CUDA device devices[r] (peer access is enabled between them): one process
+  // driving several GPUs, e.g. to profile one rank's kernel while it writes real peer memory over NVLink.
+  static std::vector<SymmHeap*> create_device_group(const std::vector<int>& devices, size_t bytes);
   ~SymmHeap();
 
   std::string ipc_handle() const;                          // 64 raw bytes

@@ -21,6 +21,7 @@ namespace {
 struct A2AProgramPy {
   torch::Tensor items_dev, expect_rail_dev;
   int n_items = 0, num_stages = 0;
+  bool has_waits = false;  // some item waits for bytes another item of a peer's (or this) launch forwards
   unsigned long long expect_output = 0, expect_balance = 0;
   int64_t total_bytes = 0;
 
@@ -42,6 +43,7 @@ struct A2AProgramPy {
       w[i].wait_kind = static_cast<unsigned char>(q[6]); w[i].signal_kind = static_cast<unsigned char>(q[7]);
       w[i].stage = static_cast<int>(q[8]); w[i].wait_stage = static_cast<int>(q[9]); w[i].pad_ = 0;
       total_bytes += q[2];
+      if (q[6] != 0) has_waits = true;
     }
     auto dev = torch::Device(torch::kCUDA, device);
     items_dev = host.to(dev);
@@ -70,7 +72,7 @@ void a2a_launch(const A2AProgramPy& p, const HeapPy& heap, std::array<int64_t, 4
   TORCH_CHECK(heap.h->world() <= kSigMaxWorld, "world larger than the signal block supports");
   A2ARankArgs a = p.args(heap, src_ptrs, dst_offs, sig_off, epoch, st, timeout_ns, stamps_ptr);
   a.bulk = bulk ? 1 : 0;
-  cuda_check(launch_a2a_push(&a, nullptr, 1, ctas, threads, cur_stream()), "a2a_push launch");
+  cuda_check(launch_a2a_push(&a, nullptr, 1, ctas, threads, cur_stream(), p.has_waits), "a2a_push launch");
 }
 
 // One cooperative launch that runs every virtual rank of an in-process group.
@@ -106,6 +108,12 @@ PYBIND11_MODULE(_C, m) {
         for (SymmHeap* h : SymmHeap::create_local_group(world, static_cast<size_t>(bytes))) out.push_back(HeapPy{std::shared_ptr<SymmHeap>(h), device});
         return out;
       })
+      .def_static("create_device_group", [](std::vector<int> devices, int64_t bytes) {
+        std::vector<HeapPy> out;
+        auto hs = SymmHeap::create_device_group(devices, static_cast<size_t>(bytes));
+        for (size_t r = 0; r < hs.size(); ++r) out.push_back(HeapPy{std::shared_ptr<SymmHeap>(hs[r]), devices[r]});
+        return out;
+      })
       .def("ipc_handle", [](const HeapPy& h) { return py::bytes(h.h->ipc_handle()); })
       .def("open_peers", [](HeapPy& h, std::vector<std::string> handles) { c10::cuda::CUDAGuard g(h.device); h.h->open_peers(handles); })
       .def("close_peers", [](HeapPy& h) { c10::cuda::CUDAGuard g(h.device); h.h->close_peers(); })
@@ -129,6 +137,7 @@ PYBIND11_MODULE(_C, m) {
       .def(py::init<torch::Tensor, std::vector<int64_t>, int64_t, int64_t, int>())
       .def_readonly("n_items", &A2AProgramPy::n_items)
       .def_readonly("num_stages", &A2AProgramPy::num_stages)
+      .def_readonly("has_waits", &A2AProgramPy::has_waits)
       .def_readonly("total_bytes", &A2AProgramPy::total_bytes);
 
   m.def("a2a_launch", &a2a_launch, py::arg("program"), py::arg("heap"), py::arg("src_ptrs"), py::arg("dst_offs"), py::arg("sig_off"), py::arg("epoch"),
