@@ -133,40 +133,49 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
       const int chunks16 = a.H / 16;
       float* my_scales = s_scales + warp * kMaxScaleGroups;
       // The whole warp walks the row together (the shuffles below need every lane); lanes past
-      // the end of a short row carry zeros and store nothing.
-      for (int c0 = 0; c0 < chunks16; c0 += 32) {
-        const int c = c0 + lane;
-        const bool active = c < chunks16;
-        float f[16];
-        if (active) {
-          float lo[8], hi[8];
-          unpack8(__ldg(src + 2 * c), lo);
-          unpack8(__ldg(src + 2 * c + 1), hi);
+      // the end of a short row carry zeros and store nothing. Two blocks of 512 elements are in flight per
+      // pass (their loads are issued before either is reduced), the abs / max run on bf16 pairs and the
+      // conversion on float pairs: this path is bound by the sender's arithmetic, not by the link.
+      constexpr int U = 2;
+      for (int c0 = 0; c0 < chunks16; c0 += 32 * U) {
+        uint4 raw[U][2];
+        bool active[U];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) f[i] = 0.0f;
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + 32 * u + lane;
+          active[u] = c < chunks16;
+          raw[u][0] = active[u] ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0);
+          raw[u][1] = active[u] ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
         }
-        float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+        for (int u = 0; u < U; ++u) {
+          if (c0 + 32 * u >= chunks16) break;  // warp-uniform: the second block of the last pass may not exist
+          const int c = c0 + 32 * u + lane;
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][0]);  // 8 pairs = my 16 elements
+          __nv_bfloat162 m2 = __habs2(h[0]);
 #pragma unroll
-        for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        // amax / 448, rounded UP to the next value a bf16 can hold: quantised values still fit e4m3, and a receiver
-        // that multiplies in bf16 (the expert GEMM's converter warps) reproduces value x scale without a second rounding.
-        const float sc = __uint_as_float((__float_as_uint(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)) + 0xFFFFu) & 0xFFFF0000u);
-        const float inv = 1.0f / sc;
-        uint4 q;
-        unsigned char* qb = reinterpret_cast<unsigned char*>(&q);
+          for (int i = 1; i < 8; ++i) m2 = __hmax2(m2, __habs2(h[i]));
+          float amax = fmaxf(__low2float(m2), __high2float(m2));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) qb[i] = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f[i] * inv, __NV_SATFINITE, __NV_E4M3));
-        if (active && (lane & 7) == 0) my_scales[c / 8] = sc;
+          for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          // amax / 448, rounded UP to the next value a bf16 can hold: quantised values still fit e4m3, and a receiver
+          // that multiplies in bf16 (the expert GEMM's converter warps) reproduces value x scale without a second rounding.
+          const float sc = __uint_as_float((__float_as_uint(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)) + 0xFFFFu) & 0xFFFF0000u);
+          const float inv = 1.0f / sc;
+          uint4 q;
+          unsigned short* qs = reinterpret_cast<unsigned short*>(&q);
 #pragma unroll
-        for (int j = 0; j < kMaxK; ++j) {
-          if (j < jbeg || j >= jend || !active || dst[j] == nullptr) continue;
-          uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
-          *out = q;
+          for (int i = 0; i < 8; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            qs[i] = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+          }
+          if (active[u] && (lane & 7) == 0) my_scales[c / 8] = sc;
+#pragma unroll
+          for (int j = 0; j < kMaxK; ++j) {
+            if (j < jbeg || j >= jend || !active[u] || dst[j] == nullptr) continue;
+            uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
+            *out = q;
+          }
         }
       }
       __syncwarp();
