@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
   const int chunks = a.H / 8;  // 16-byte chunks per row
   // Unsorted mode: one warp per token, the row is read once and stored to its K destinations.
   // Sorted mode (send_list != null): one warp per (token, slot) entry, entries ordered by
-  // (local expert index, destination rank), so that every rank's expert 0 fills first, then
+  // (local expert index, destination rank counted from the sender upwards), so that every rank's expert 0 fills first, then
   // expert 1, ... and the gated GEMM of the receivers can start while later experts still arrive.
   const long long n_work = a.send_list ? static_cast<long long>(a.T) * a.K : a.T;
   for (long long wi = blockIdx.x * wpb + warp; wi < n_work; wi += static_cast<long long>(gridDim.x) * wpb) {

@@ -40,6 +40,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Dynamic shared memory: gate [E][H] bf16, norm weight [H] bf16, then int s_eid[kTokensPerBlock * K].
+// A warp takes two tokens per pass: every gate chunk is read and unpacked once for both rows.
+template <int EMAX>
 __global__ void __launch_bounds__(kGateThreads) norm_gate_route_kernel(const NormGateArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int E = a.num_experts, H = a.H, K = a.K;
@@ -53,47 +55,12 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_route_kernel(const Nor
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = kGateThreads / 32;
   const int t0 = blockIdx.x * kTokensPerBlock;
   const int nt = min(kTokensPerBlock, a.T - t0);
-  for (int lt = warp; lt < kTokensPerBlock; lt += nwarps) {
+  // Logits of one token are spread over the lanes' partial sums: reduce, publish, choose the top k.
+  auto finish = [&](int lt, const float (&acc)[EMAX]) {
     const int t = t0 + lt;
-    if (lt >= nt) {
-      for (int j = lane; j < K; j += 32) s_eid[lt * K + j] = -1;
-      continue;
-    }
-    const uint4* hrow = reinterpret_cast<const uint4*>(a.h + static_cast<long long>(t) * H);
-    float ss = 0.0f;
-    for (int c = lane; c < chunks; c += 32) {
-      float f[8];
-      unpack8(__ldg(hrow + c), f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
-    }
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / static_cast<float>(H) + a.eps);
-    if (lane == 0) a.rstd[t] = rstd;
-    // second pass over the row (still in L1): normalised row out, logits accumulated against the gate rows
-    float acc[32];
-#pragma unroll
-    for (int e = 0; e < 32; ++e) acc[e] = 0.0f;
-    uint4* hnrow = reinterpret_cast<uint4*>(a.hn + static_cast<long long>(t) * H);
-    for (int c = lane; c < chunks; c += 32) {
-      float f[8], w[8], y[8];
-      unpack8(__ldg(hrow + c), f);
-      unpack8(s_nw[c], w);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = bf16_round(f[i] * rstd * w[i]);  // normalised and scaled in fp32, rounded once
-      hnrow[c] = pack8(y);
-#pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        if (e >= E) break;
-        float g[8];
-        unpack8(s_gate[static_cast<size_t>(e) * chunks + c], g);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[e] = fmaf(y[i], g[i], acc[e]);
-      }
-    }
     float raw = -INFINITY;  // lane e ends up with logit e
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
+    for (int e = 0; e < EMAX; ++e) {
       if (e >= E) break;
       const float v = warp_sum(acc[e]);
       if (lane == e) raw = v;
@@ -128,6 +95,56 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_route_kernel(const Nor
       a.topk_w[static_cast<long long>(t) * K + lane] = wsum > 0.0f ? my_w / wsum : 0.0f;
       s_eid[lt * K + lane] = my_e;
     }
+  };
+  for (int lt = warp; lt < kTokensPerBlock; lt += 2 * nwarps) {
+    const int ltb = lt + nwarps;
+    const bool va = lt < nt, vb = ltb < nt;   // vb implies va
+    if (!vb)
+      for (int j = lane; j < K; j += 32) s_eid[ltb * K + j] = -1;
+    if (!va) {
+      for (int j = lane; j < K; j += 32) s_eid[lt * K + j] = -1;
+      continue;
+    }
+    const uint4* ha = reinterpret_cast<const uint4*>(a.h + static_cast<long long>(t0 + lt) * H);
+    const uint4* hb = reinterpret_cast<const uint4*>(a.h + static_cast<long long>(t0 + (vb ? ltb : lt)) * H);  // a dead second token re-reads the first
+    float ssa = 0.0f, ssb = 0.0f;
+    for (int c = lane; c < chunks; c += 32) {
+      float fa[8], fb[8];
+      unpack8(__ldg(ha + c), fa);
+      unpack8(__ldg(hb + c), fb);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ssa = fmaf(fa[i], fa[i], ssa); ssb = fmaf(fb[i], fb[i], ssb); }
+    }
+    ssa = warp_sum(ssa);
+    ssb = warp_sum(ssb);
+    const float ra = rsqrtf(ssa / static_cast<float>(H) + a.eps), rb = rsqrtf(ssb / static_cast<float>(H) + a.eps);
+    if (lane == 0) { a.rstd[t0 + lt] = ra; if (vb) a.rstd[t0 + ltb] = rb; }
+    // second pass over the rows (still in L1): normalised rows out, logits accumulated against the gate rows
+    float acca[EMAX], accb[EMAX];
+#pragma unroll
+    for (int e = 0; e < EMAX; ++e) { acca[e] = 0.0f; accb[e] = 0.0f; }
+    uint4* oa = reinterpret_cast<uint4*>(a.hn + static_cast<long long>(t0 + lt) * H);
+    uint4* ob = reinterpret_cast<uint4*>(a.hn + static_cast<long long>(t0 + ltb) * H);
+    for (int c = lane; c < chunks; c += 32) {
+      float fa[8], fb[8], w[8], ya[8], yb[8];
+      unpack8(__ldg(ha + c), fa);
+      unpack8(__ldg(hb + c), fb);
+      unpack8(s_nw[c], w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ya[i] = bf16_round(fa[i] * ra * w[i]); yb[i] = bf16_round(fb[i] * rb * w[i]); }  // normalised and scaled in fp32, rounded once
+      oa[c] = pack8(ya);
+      if (vb) ob[c] = pack8(yb);
+#pragma unroll
+      for (int e = 0; e < EMAX; ++e) {
+        if (e >= E) break;
+        float g[8];
+        unpack8(s_gate[static_cast<size_t>(e) * chunks + c], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { acca[e] = fmaf(ya[i], g[i], acca[e]); accb[e] = fmaf(yb[i], g[i], accb[e]); }
+      }
+    }
+    finish(lt, acca);
+    if (vb) finish(ltb, accb);
   }
   __syncthreads();
   const int n = kTokensPerBlock * K;
@@ -278,11 +295,16 @@ cudaError_t launch_norm_gate_route(const NormGateArgs& a, cudaStream_t stream) {
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   const int blocks = (a.T + kTokensPerBlock - 1) / kTokensPerBlock;
   if (blocks == 0) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(norm_gate_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  if (e != cudaSuccess) return e;
-  norm_gate_route_kernel<<<blocks, kGateThreads, smem, stream>>>(a);
-  note_launch();
-  return cudaGetLastError();
+  auto go = [&](auto kern) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    kern<<<blocks, kGateThreads, smem, stream>>>(a);
+    note_launch();
+    return cudaGetLastError();
+  };
+  if (a.num_experts <= 8) return go(norm_gate_route_kernel<8>);
+  if (a.num_experts <= 16) return go(norm_gate_route_kernel<16>);
+  return go(norm_gate_route_kernel<32>);
 }
 
 cudaError_t launch_norm_gate_bwd(const NormGateBwdArgs& a, cudaStream_t stream) {

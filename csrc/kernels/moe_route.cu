@@ -182,10 +182,12 @@ __global__ void __launch_bounds__(1024) splits_scan_kernel(const SplitsArgs a) {
     a.send_base[e] = base + before_me;
     a.send_cnt[e] = mine;
     if (a.send_pos) {
-      // Entries are sent expert-slot by expert-slot: all ranks' local expert 0, then 1, ...
+      // Entries are sent expert-slot by expert-slot: all ranks' local expert 0, then 1, ... Within a
+      // slot every sender starts with itself and walks the ranks upwards, so that at any moment the
+      // senders aim at different receivers.
       int pos = 0;
       for (int q = 0; q < E; ++q) {
-        const int key_q = (q % El) * W + q / El, key_e = le * W + d;
+        const int key_q = (q % El) * W + (q / El - a.rank + W) % W, key_e = le * W + (d - a.rank + W) % W;
         if (key_q < key_e) pos += count_at(a.rank, q);
       }
       a.send_pos[e] = pos;
