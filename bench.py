@@ -195,10 +195,14 @@ def main():
         opt_repl.zero_grad()
         loss = model(ids)
         loss.backward()
+        works = []
         if world > 1:  # replicated parameters: average gradients over the data-parallel ranks
-            for p in model.replicated_parameters():
-                dist.all_reduce(p.grad, op=dist.ReduceOp.AVG)
+            # NCCL's stream picks the gradients up once the backward pass is done; the experts' AdamW
+            # (the rank's own shard, nothing to reduce) streams through HBM meanwhile.
+            works = [dist.all_reduce(p.grad, op=dist.ReduceOp.AVG, async_op=True) for p in model.replicated_parameters()]
         opt_experts.step()
+        for w in works:
+            w.wait()
         opt_repl.step()
         return loss
 

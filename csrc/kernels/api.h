@@ -214,6 +214,8 @@ struct DispatchArgs {
   int* dest_row;               // [T, K]: written when compute_rows != 0, else read
   int compute_rows;
   int fp8;                     // 1: send e4m3 bytes + one fp32 scale per 128 elements
+  const unsigned char* xq;     // fp8 only, optional: rows already quantised by launch_quantise_rows ([T, H] e4m3); x is then not read
+  const float* xq_scales;      // their scales [T, H/128]
   long long recv_heap_off;     // destination rows: bf16 [cap, H] (or u8 [cap, H] when fp8)
   long long scale_heap_off;    // fp8 only: float [cap, H/128]
   long long arrive_heap_off;   // u64 arrival counters of this channel: [E/world] per expert, or [num_tiles] per tile
@@ -224,6 +226,9 @@ struct DispatchArgs {
   unsigned long long timeout_ns;
 };
 cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t stream);
+// x [T, H] bf16 -> q [T, H] e4m3 + scales [T, H/128] (1 x 128 blocks, bf16-exact scales), all local: the
+// quantisation the fp8 dispatch otherwise does per entry, done once per row.
+cudaError_t launch_quantise_rows(const __nv_bfloat16* x, int T, int H, unsigned char* q, float* scales, int ctas, cudaStream_t stream);
 
 struct CombineArgs {
   void* const* peer_table;

@@ -35,6 +35,67 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 constexpr int kMaxK = 8;
 constexpr int kMaxScaleGroups = 128;  // fp8 dispatch: rows of up to 128 x 128 = 16384 elements
 
+// 16 bf16 elements of a lane -> 16 e4m3 bytes; 8 consecutive lanes (128 elements) share one scale.
+// Every lane of the warp calls this together (lanes past the row's end pass zeros).
+// The scale is amax / 448 rounded UP to the next value a bf16 can hold: quantised values still fit
+// e4m3, and a receiver that multiplies in bf16 (the expert GEMM's converter warps) reproduces
+// value x scale without a second rounding. The abs / max run on bf16 pairs, the conversion on float pairs.
+__device__ __forceinline__ uint4 quantise16(const uint4 (&raw)[2], float& sc) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);  // 8 pairs = my 16 elements
+  __nv_bfloat162 m2 = __habs2(h[0]);
+#pragma unroll
+  for (int i = 1; i < 8; ++i) m2 = __hmax2(m2, __habs2(h[i]));
+  float amax = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+  for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  sc = __uint_as_float((__float_as_uint(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)) + 0xFFFFu) & 0xFFFF0000u);
+  const float inv = 1.0f / sc;
+  uint4 q;
+  unsigned short* qs = reinterpret_cast<unsigned short*>(&q);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    qs[i] = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+  }
+  return q;
+}
+
+// One warp per row: x [T, H] bf16 -> q [T, H] e4m3 bytes + scales [T, H / 128], in this GPU's own memory.
+// The sorted dispatch sends every (token, slot) entry from a warp of its own; with the rows quantised
+// here first, a token's K entries copy bytes instead of each repeating the reduction and the conversions.
+__global__ void __launch_bounds__(kCommThreads) quantise_rows_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, unsigned char* __restrict__ q,
+                                                                      float* __restrict__ scales) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const int chunks16 = H / 16, sgroups = H / 128;
+  for (long long t = blockIdx.x * wpb + warp; t < T; t += static_cast<long long>(gridDim.x) * wpb) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + t * H);
+    uint4* out = reinterpret_cast<uint4*>(q + t * H);
+    constexpr int U = 2;
+    for (int c0 = 0; c0 < chunks16; c0 += 32 * U) {
+      uint4 raw[U][2];
+      bool active[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + 32 * u + lane;
+        active[u] = c < chunks16;
+        raw[u][0] = active[u] ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0);
+        raw[u][1] = active[u] ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (c0 + 32 * u >= chunks16) break;  // warp-uniform
+        const int c = c0 + 32 * u + lane;
+        float sc;
+        const uint4 v = quantise16(raw[u], sc);
+        if (active[u]) {
+          out[c] = v;
+          if ((lane & 7) == 0) scales[t * sgroups + c / 8] = sc;
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const DispatchArgs a) {
   extern __shared__ int s_cnt[];  // rows this CTA sent: [E] per expert, or [world][num_tiles] per destination tile
   __shared__ int s_ok;
@@ -127,54 +188,60 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
       }
     } else {
       // 16 elements per lane (one 16-byte store of e4m3); 8 consecutive lanes = 128 elements share
-      // one scale (amax / 448). The row's scales are collected in shared memory and leave as 16-byte
-      // stores after the payload: 4-byte remote stores would each cost a packet of their own.
+      // one scale (amax / 448). The row's scales leave as 16-byte stores after the payload: 4-byte
+      // remote stores would each cost a packet of their own.
       const int sgroups = a.H / 128;
       const int chunks16 = a.H / 16;
       float* my_scales = s_scales + warp * kMaxScaleGroups;
-      // The whole warp walks the row together (the shuffles below need every lane); lanes past
-      // the end of a short row carry zeros and store nothing. Two blocks of 512 elements are in flight per
-      // pass (their loads are issued before either is reduced), the abs / max run on bf16 pairs and the
-      // conversion on float pairs: this path is bound by the sender's arithmetic, not by the link.
-      constexpr int U = 2;
-      for (int c0 = 0; c0 < chunks16; c0 += 32 * U) {
-        uint4 raw[U][2];
-        bool active[U];
+      if (a.xq != nullptr) {
+        // Rows were quantised once by quantise_rows_kernel: this entry copies bytes.
+        const uint4* qsrc = reinterpret_cast<const uint4*>(a.xq + static_cast<long long>(t) * a.H);
+        constexpr int U = 4;
+        for (int c0 = lane; c0 < chunks16; c0 += 32 * U) {
+          uint4 v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int c = c0 + 32 * u + lane;
-          active[u] = c < chunks16;
-          raw[u][0] = active[u] ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0);
-          raw[u][1] = active[u] ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
-        }
+          for (int u = 0; u < U; ++u)
+            if (c0 + 32 * u < chunks16) v[u] = __ldg(qsrc + c0 + 32 * u);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (c0 + 32 * u >= chunks16) break;  // warp-uniform: the second block of the last pass may not exist
-          const int c = c0 + 32 * u + lane;
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][0]);  // 8 pairs = my 16 elements
-          __nv_bfloat162 m2 = __habs2(h[0]);
+          for (int u = 0; u < U; ++u) {
+            const int c = c0 + 32 * u;
+            if (c >= chunks16) break;
 #pragma unroll
-          for (int i = 1; i < 8; ++i) m2 = __hmax2(m2, __habs2(h[i]));
-          float amax = fmaxf(__low2float(m2), __high2float(m2));
-#pragma unroll
-          for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-          // amax / 448, rounded UP to the next value a bf16 can hold: quantised values still fit e4m3, and a receiver
-          // that multiplies in bf16 (the expert GEMM's converter warps) reproduces value x scale without a second rounding.
-          const float sc = __uint_as_float((__float_as_uint(fmaxf(amax, 1e-12f) * (1.0f / 448.0f)) + 0xFFFFu) & 0xFFFF0000u);
-          const float inv = 1.0f / sc;
-          uint4 q;
-          unsigned short* qs = reinterpret_cast<unsigned short*>(&q);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float2 f = __bfloat1622float2(h[i]);
-            qs[i] = __nv_cvt_float2_to_fp8x2(make_float2(f.x * inv, f.y * inv), __NV_SATFINITE, __NV_E4M3);
+            for (int j = 0; j < kMaxK; ++j) {
+              if (j < jbeg || j >= jend || dst[j] == nullptr) continue;
+              *(reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c) = v[u];
+            }
           }
-          if (active[u] && (lane & 7) == 0) my_scales[c / 8] = sc;
+        }
+        for (int g = lane; g < sgroups; g += 32) my_scales[g] = __ldg(a.xq_scales + static_cast<long long>(t) * sgroups + g);
+      } else {
+        // The whole warp walks the row together (the shuffles in quantise16 need every lane); lanes past
+        // the end of a short row carry zeros and store nothing. Two blocks of 512 elements are in flight
+        // per pass (their loads are issued before either is reduced).
+        constexpr int U = 2;
+        for (int c0 = 0; c0 < chunks16; c0 += 32 * U) {
+          uint4 raw[U][2];
+          bool active[U];
 #pragma unroll
-          for (int j = 0; j < kMaxK; ++j) {
-            if (j < jbeg || j >= jend || !active[u] || dst[j] == nullptr) continue;
-            uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
-            *out = q;
+          for (int u = 0; u < U; ++u) {
+            const int c = c0 + 32 * u + lane;
+            active[u] = c < chunks16;
+            raw[u][0] = active[u] ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0);
+            raw[u][1] = active[u] ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (c0 + 32 * u >= chunks16) break;  // warp-uniform: the second block of the last pass may not exist
+            const int c = c0 + 32 * u + lane;
+            float sc;
+            const uint4 q = quantise16(raw[u], sc);
+            if (active[u] && (lane & 7) == 0) my_scales[c / 8] = sc;
+#pragma unroll
+            for (int j = 0; j < kMaxK; ++j) {
+              if (j < jbeg || j >= jend || !active[u] || dst[j] == nullptr) continue;
+              uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
+              *out = q;
+            }
           }
         }
       }
@@ -315,6 +382,7 @@ __global__ void wait_counters_kernel(const unsigned long long* counter, const un
 cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t stream) {
   if (a.K < 1 || a.K > kMaxK || a.H % 256 || a.world < 1 || a.num_experts % a.world || ctas < 1) return cudaErrorInvalidValue;
   if (a.fp8 && a.H / 128 > kMaxScaleGroups) return cudaErrorInvalidValue;
+  if ((a.xq != nullptr) != (a.xq_scales != nullptr) || (a.xq != nullptr && !a.fp8)) return cudaErrorInvalidValue;
   if (a.T == 0) return cudaSuccess;
   if (a.tile_rows < 0 || (a.tile_rows > 0 && a.num_tiles < 1)) return cudaErrorInvalidValue;
   const size_t smem = sizeof(int) * (a.tile_rows > 0 ? static_cast<size_t>(a.world) * a.num_tiles : static_cast<size_t>(a.num_experts));
@@ -324,6 +392,14 @@ cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t s
     if (e != cudaSuccess) return e;
   }
   dispatch_push_kernel<<<ctas, kCommThreads, smem, stream>>>(a);
+  note_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quantise_rows(const __nv_bfloat16* x, int T, int H, unsigned char* q, float* scales, int ctas, cudaStream_t stream) {
+  if (H % 256 || H / 128 > kMaxScaleGroups || ctas < 1 || T < 0) return cudaErrorInvalidValue;
+  if (T == 0) return cudaSuccess;
+  quantise_rows_kernel<<<ctas, kCommThreads, 0, stream>>>(x, T, H, q, scales);
   note_launch();
   return cudaGetLastError();
 }

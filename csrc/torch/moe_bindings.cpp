@@ -168,7 +168,8 @@ void zero_pad_rows(torch::Tensor buf, torch::Tensor group_off, torch::Tensor gro
 void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, c10::optional<torch::Tensor> row_scale, torch::Tensor slot_in_block,
                    torch::Tensor block_base, torch::Tensor send_base, torch::Tensor dest_row, bool compute_rows, bool fp8, int64_t recv_off,
                    int64_t scale_off, int64_t arrive_off, int64_t entry_flags_off, uint64_t entry_epoch, const StatusPy& st, uint64_t timeout_ns, int ctas,
-                   c10::optional<torch::Tensor> send_list, int tile_rows, int num_tiles) {
+                   c10::optional<torch::Tensor> send_list, int tile_rows, int num_tiles, c10::optional<torch::Tensor> xq,
+                   c10::optional<torch::Tensor> xq_scales) {
   want(x, torch::kBFloat16, "x"); want(topk_idx, torch::kInt32, "topk_idx"); want(dest_row, torch::kInt32, "dest_row");
   DispatchArgs a{};
   a.peer_table = heap.h->device_peer_table(); a.rank = heap.h->rank(); a.world = heap.h->world();
@@ -179,6 +180,12 @@ void dispatch_push(const HeapPy& heap, torch::Tensor x, torch::Tensor topk_idx, 
   a.dest_row = dest_row.data_ptr<int>(); a.compute_rows = compute_rows; a.fp8 = fp8;
   a.send_list = ptr_or_null<const int>(send_list);
   a.tile_rows = tile_rows; a.num_tiles = num_tiles;
+  if (xq.has_value()) {
+    TORCH_CHECK(fp8 && xq_scales.has_value(), "dispatch_push: xq needs fp8 and xq_scales");
+    want(*xq, torch::kUInt8, "xq"); want(*xq_scales, torch::kFloat32, "xq_scales");
+    TORCH_CHECK(xq->numel() >= x.numel() && xq_scales->numel() >= x.numel() / 128, "dispatch_push: xq / xq_scales too small");
+    a.xq = xq->data_ptr<uint8_t>(); a.xq_scales = xq_scales->data_ptr<float>();
+  }
   a.recv_heap_off = recv_off; a.scale_heap_off = scale_off; a.arrive_heap_off = arrive_off;
   a.entry_flags_heap_off = entry_flags_off; a.entry_epoch = entry_epoch; a.status = st.d; a.timeout_ns = timeout_ns;
   cu_check(launch_dispatch_push(a, ctas, stream_now()), "dispatch_push");
@@ -261,7 +268,13 @@ void bind_moe(py::module_& m) {
   m.def("dispatch_push", &dispatch_push, py::arg("heap"), py::arg("x"), py::arg("topk_idx"), py::arg("row_scale"), py::arg("slot_in_block"), py::arg("block_base"),
         py::arg("send_base"), py::arg("dest_row"), py::arg("compute_rows"), py::arg("fp8"), py::arg("recv_off"), py::arg("scale_off"), py::arg("arrive_off"),
         py::arg("entry_flags_off"), py::arg("entry_epoch"), py::arg("status"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("send_list"),
-        py::arg("tile_rows") = 0, py::arg("num_tiles") = 0);
+        py::arg("tile_rows") = 0, py::arg("num_tiles") = 0, py::arg("xq") = py::none(), py::arg("xq_scales") = py::none());
+  m.def("quantise_rows", [](torch::Tensor x, torch::Tensor q, torch::Tensor scales, int ctas) {
+    want(x, torch::kBFloat16, "x"); want(q, torch::kUInt8, "q"); want(scales, torch::kFloat32, "scales");
+    TORCH_CHECK(x.dim() == 2 && q.numel() >= x.numel() && scales.numel() >= x.numel() / 128, "quantise_rows: q / scales too small");
+    cu_check(launch_quantise_rows(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                                  q.data_ptr<uint8_t>(), scales.data_ptr<float>(), ctas, stream_now()), "quantise_rows");
+  });
   m.def("combine_pull", &combine_pull);
   m.def("peer_signal", [](const HeapPy& heap, int64_t flags_off, uint64_t epoch, int64_t epoch_dev_ptr) {
     cu_check(launch_peer_signal(heap.h->device_peer_table(), heap.h->rank(), heap.h->world(), flags_off, epoch,

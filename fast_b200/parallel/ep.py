@@ -125,6 +125,7 @@ class ExpertParallel:
         self.send_cnt = torch.zeros(self.E, **i32)
         self.send_pos = torch.zeros(self.E, **i32)
         self.send_list = torch.zeros(max_tokens * top_k, **i32) if overlap_dispatch else None
+        self._xq_send = self._xs_send = None  # sorted fp8 dispatch: rows quantised once, allocated on first use
         self.group_off = torch.zeros(self.El + 1, **i32)
         self.group_rows = torch.zeros(self.El, **i32)
         self.arrive_target = torch.zeros(2, self.El, dtype=torch.int64, device=dev)
@@ -233,9 +234,17 @@ class ExpertParallel:
             send_list = self.send_list
         try:
             if self.fp8:
+                xq = xs = None
+                if send_list is not None:
+                    # Sorted sending gives every (token, slot) entry a warp of its own: quantise each row once, entries copy bytes.
+                    if self._xq_send is None:
+                        self._xq_send = torch.empty(self.T, self.H, dtype=torch.uint8, device=x.device)
+                        self._xs_send = torch.empty(self.T, self.H // 128, dtype=torch.float32, device=x.device)
+                    xq, xs = self._xq_send, self._xs_send
+                    C.quantise_rows(x, xq, xs, 4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas)
                 C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, True,
                                 self._off(self.xq_recv), self._off(self.xs_recv), self.arrive._symm_off, 0, 0, self.status, self.timeout_ns,
-                                4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas, send_list, self.tile_rows, self.ntiles)
+                                4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas, send_list, self.tile_rows, self.ntiles, xq, xs)
             else:
                 C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, False,
                                 self._off(self.x_recv), 0, self.arrive._symm_off, 0, 0, self.status, self.timeout_ns,
