@@ -18,7 +18,8 @@ namespace {
 
 constexpr int kTokensPerBlock = kRouteTokensPerBlock;
 constexpr int kGateThreads = 256;
-constexpr int kGateBwdMaxChunksPerThread = 4;  // backward: hidden <= 4 * 256 * 8 = 8192
+constexpr int kGateBwdThreads = 512;            // backward: 16 warps hide the shared-memory and reduction latency of the per-token chain
+constexpr int kGateBwdMaxChunksPerThread = 2;  // backward: hidden <= 2 * 512 * 8 = 8192
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -164,9 +165,9 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_route_kernel(const Nor
 // of them, so the gradient partials in shared memory are updated with plain read-modify-writes (no two
 // threads ever touch the same word); the row-wide sum the RMSNorm backward needs is one block reduction per
 // token.
-__global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormGateBwdArgs a) {
+__global__ void __launch_bounds__(kGateBwdThreads) norm_gate_bwd_kernel(const NormGateBwdArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ float s_part[2][kGateThreads / 32];
+  __shared__ float s_part[2][kGateBwdThreads / 32];
   const int E = a.num_experts, H = a.H, K = a.K;
   const int chunks = H / 8;
   uint4* s_gate = reinterpret_cast<uint4*>(smem);
@@ -178,11 +179,13 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormG
   for (int i = threadIdx.x; i < (E + 1) * H; i += blockDim.x) s_dgate[i] = 0.0f;  // d_gate and d_nw are contiguous
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * kTokensPerBlock;
-  const int nt = min(kTokensPerBlock, a.T - t0);
+  // One block per SM, each with an equal share of the tokens (no second, partly filled wave).
+  const int per = (a.T + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int t0 = blockIdx.x * per;
+  const int nt = max(0, min(per, a.T - t0));
   constexpr int kMaxK = 8;
-  constexpr int kMaxC = kGateBwdMaxChunksPerThread;  // my chunks are threadIdx.x + kGateThreads * i, i < nc <= kMaxC
-  const int nc = (chunks - static_cast<int>(threadIdx.x) + kGateThreads - 1) / kGateThreads;
+  constexpr int kMaxC = kGateBwdMaxChunksPerThread;  // my chunks are threadIdx.x + kGateBwdThreads * i, i < nc <= kMaxC
+  const int nc = (chunks - static_cast<int>(threadIdx.x) + kGateBwdThreads - 1) / kGateBwdThreads;
   // The next token's rows are requested before the current token is worked on, and a token's rows stay in
   // registers for both passes: no global-memory latency sits between two block reductions.
   uint4 nx[kMaxC], ng[kMaxC];
@@ -191,7 +194,7 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormG
     const uint4* grow = reinterpret_cast<const uint4*>(a.grad_hn + static_cast<long long>(t0 + lt) * H);
 #pragma unroll
     for (int i = 0; i < kMaxC; ++i)
-      if (i < nc) { nx[i] = __ldg(hrow + threadIdx.x + kGateThreads * i); ng[i] = __ldg(grow + threadIdx.x + kGateThreads * i); }
+      if (i < nc) { nx[i] = __ldg(hrow + threadIdx.x + kGateBwdThreads * i); ng[i] = __ldg(grow + threadIdx.x + kGateBwdThreads * i); }
   };
   if (nt > 0) request(0);
   for (int lt = 0; lt < nt; ++lt) {
@@ -229,7 +232,7 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormG
 #pragma unroll
     for (int ci = 0; ci < kMaxC; ++ci) {
       if (ci >= nc) break;
-      const int c = threadIdx.x + kGateThreads * ci;
+      const int c = threadIdx.x + kGateBwdThreads * ci;
       float x[8], w[8], g[8], hn[8];
       unpack8(cx[ci], x);
       unpack8(s_nw[c], w);
@@ -241,19 +244,21 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormG
         if (j < K) {
           float q[8];
           unpack8(s_gate[static_cast<size_t>(ex[j]) * chunks + c], q);
-          float4* dg = reinterpret_cast<float4*>(s_dgate + static_cast<size_t>(ex[j]) * H + c * 8);
-          float4 d0 = dg[0], d1 = dg[1];
+          // a chunk's first four accumulators sit in the row's first half, the other four in its second
+          // half: a warp's 16-byte accesses are then contiguous (no two-way bank conflict)
+          float4* dg = reinterpret_cast<float4*>(s_dgate + static_cast<size_t>(ex[j]) * H) + c;
+          float4 d0 = dg[0], d1 = dg[chunks];
           d0.x = fmaf(dl[j], hn[0], d0.x); d0.y = fmaf(dl[j], hn[1], d0.y); d0.z = fmaf(dl[j], hn[2], d0.z); d0.w = fmaf(dl[j], hn[3], d0.w);
           d1.x = fmaf(dl[j], hn[4], d1.x); d1.y = fmaf(dl[j], hn[5], d1.y); d1.z = fmaf(dl[j], hn[6], d1.z); d1.w = fmaf(dl[j], hn[7], d1.w);
-          dg[0] = d0; dg[1] = d1;
+          dg[0] = d0; dg[chunks] = d1;
 #pragma unroll
           for (int i = 0; i < 8; ++i) g[i] = fmaf(dl[j], q[i], g[i]);
         }
-      float4* dn = reinterpret_cast<float4*>(s_dnw + c * 8);
-      float4 n0 = dn[0], n1 = dn[1];
+      float4* dn = reinterpret_cast<float4*>(s_dnw) + c;
+      float4 n0 = dn[0], n1 = dn[chunks];
       n0.x = fmaf(g[0], kxh[ci][0], n0.x); n0.y = fmaf(g[1], kxh[ci][1], n0.y); n0.z = fmaf(g[2], kxh[ci][2], n0.z); n0.w = fmaf(g[3], kxh[ci][3], n0.w);
       n1.x = fmaf(g[4], kxh[ci][4], n1.x); n1.y = fmaf(g[5], kxh[ci][5], n1.y); n1.z = fmaf(g[6], kxh[ci][6], n1.z); n1.w = fmaf(g[7], kxh[ci][7], n1.w);
-      dn[0] = n0; dn[1] = n1;
+      dn[0] = n0; dn[chunks] = n1;
 #pragma unroll
       for (int i = 0; i < 8; ++i) { kdx[ci][i] = g[i] * w[i]; s = fmaf(kdx[ci][i], kxh[ci][i], s); }
     }
@@ -262,7 +267,7 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormG
     __syncthreads();
     float tot = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kGateThreads / 32; ++i) tot += s_part[lt & 1][i];
+    for (int i = 0; i < kGateBwdThreads / 32; ++i) tot += s_part[lt & 1][i];
     tot /= static_cast<float>(H);
     // pass 2, from registers: d(h) = rstd * (dxhat - xhat * s)
     uint4* orow = reinterpret_cast<uint4*>(a.grad_h + static_cast<long long>(t) * H);
@@ -272,14 +277,18 @@ __global__ void __launch_bounds__(kGateThreads) norm_gate_bwd_kernel(const NormG
       float o[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] = rstd * (kdx[ci][i] - kxh[ci][i] * tot);
-      orow[threadIdx.x + kGateThreads * ci] = pack8(o);
+      orow[threadIdx.x + kGateBwdThreads * ci] = pack8(o);
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < E * H; i += blockDim.x)
-    if (s_dgate[i] != 0.0f) atomicAdd(a.d_gate + i, s_dgate[i]);
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    if (s_dnw[i] != 0.0f) atomicAdd(a.d_norm_w + i, s_dnw[i]);
+  // rows of d_gate and d_nw are contiguous ((E + 1) rows of H); undo the half-row split on the way out
+  for (int i = threadIdx.x; i < (E + 1) * H; i += blockDim.x) {
+    const int row = i / H, p = i % H;                      // p: position in shared memory
+    const int half = p / (H / 2), q = p % (H / 2);          // accumulator (q % 4) + 4 * half of chunk q / 4
+    const int col = (q / 4) * 8 + half * 4 + (q % 4);
+    const float v = s_dgate[i];
+    if (v != 0.0f) atomicAdd((row < E ? a.d_gate + static_cast<size_t>(row) * H : a.d_norm_w) + col, v);
+  }
 }
 
 }  // namespace
@@ -308,14 +317,19 @@ cudaError_t launch_norm_gate_route(const NormGateArgs& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_norm_gate_bwd(const NormGateBwdArgs& a, cudaStream_t stream) {
-  if (a.num_experts < 1 || a.num_experts > 32 || a.K < 1 || a.K > 8 || a.H % 256 || a.H > kGateBwdMaxChunksPerThread * kGateThreads * 8) return cudaErrorInvalidValue;
+  if (a.num_experts < 1 || a.num_experts > 32 || a.K < 1 || a.K > 8 || a.H % 256 || a.H > kGateBwdMaxChunksPerThread * kGateBwdThreads * 8) return cudaErrorInvalidValue;
   const size_t smem = norm_gate_smem_bytes(a.num_experts, a.H, a.K, true);
   if (smem > 220 * 1024) return cudaErrorInvalidValue;
-  const int blocks = (a.T + kTokensPerBlock - 1) / kTokensPerBlock;
-  if (blocks == 0) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(norm_gate_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (a.T <= 0) return cudaSuccess;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  norm_gate_bwd_kernel<<<blocks, kGateThreads, smem, stream>>>(a);
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  const int blocks = std::max(1, std::min(sms, (a.T + 31) / 32));  // at least 32 tokens per block: each block adds its partial sums to global memory once
+  e = cudaFuncSetAttribute(norm_gate_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  norm_gate_bwd_kernel<<<blocks, kGateBwdThreads, smem, stream>>>(a);
   note_launch();
   return cudaGetLastError();
 }

@@ -55,7 +55,14 @@ class Schedule:
     @property
     def max_bytes(self) -> dict:
         """Largest need of any rank per buffer: symmetric staging is sized by these so that every
-        rank allocates the same amounts in the same order."""
+        rank allocates the same amounts in the same order.
+
+        Staging is never reused inside one collective: every stage of a two-tier plan lands in a rail
+        region of its own, so ``rail`` grows with the bytes a rank relays (about twice its payload for
+        a 1 GiB-per-rank two-tier exchange, zero for single-server plans) and ``balance`` with the
+        bytes it takes over from busier neighbours. That trades memory (180 GB per GPU) for the
+        absence of buffer credits and their waits; a caller short of memory can split the exchange
+        into several ``all_to_all_v`` calls over slices of the matrix, which reuse the same staging."""
         b = self.plan.buffers.max(axis=0) * self.unit_bytes
         return {"input": int(b[0]), "output": int(b[1]), "balance": int(b[2]), "rail": int(b[3])}
 

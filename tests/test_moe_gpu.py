@@ -212,6 +212,32 @@ def test_elementwise_kernels():
     assert torch.equal(pb, master.to(torch.bfloat16))
 
 
+def test_quantise_rows_matches_a_torch_restatement():
+    """Rows to e4m3 in 1 x 128 blocks: the scale is amax / 448 rounded up to a bf16 value, the bytes are
+    round-to-nearest e4m3 of value / scale; value x scale comes back within e4m3's half-ulp."""
+    from fast_b200 import runtime
+
+    C = runtime.ext()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    T, H = 77, 768
+    x = (torch.randn(T, H, generator=g, device="cuda") * torch.logspace(-3, 2, T, device="cuda").unsqueeze(1)).to(torch.bfloat16)
+    x[5, 128:256] = 0  # an all-zero block keeps a tiny positive scale
+    q = torch.empty(T, H, dtype=torch.uint8, device="cuda")
+    sc = torch.empty(T, H // 128, dtype=torch.float32, device="cuda")
+    C.quantise_rows(x, q, sc, 8)
+    blocks = x.float().reshape(T, H // 128, 128)
+    want = blocks.abs().amax(-1).clamp_min(1e-12) / 448.0
+    want = ((want.view(torch.int32) + 0xFFFF) & -65536).view(torch.float32)  # up to the next bf16 value
+    assert torch.equal(sc, want)
+    ref_q = (blocks / want.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    got = q.view(torch.float8_e4m3fn).reshape(T, H // 128, 128)
+    # the kernel multiplies by a reciprocal: a value on a rounding boundary may land one code away
+    assert (got.float() != ref_q.float()).float().mean().item() < 1e-3
+    back = got.float() * sc.unsqueeze(-1)
+    assert ((back - blocks).abs() <= blocks.abs().amax(-1, keepdim=True) * (1.0 / 14) + 1e-12).all()
+    assert torch.count_nonzero(back[5, 1]) == 0
+
+
 def test_embedding_index_is_a_stable_sort_by_id():
     """The counting sort that feeds the embedding gradient equals torch's stable sort, with few and with heavy duplicates."""
     from fast_b200 import runtime
