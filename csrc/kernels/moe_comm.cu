@@ -96,7 +96,11 @@ __global__ void __launch_bounds__(kCommThreads) quantise_rows_kernel(const __nv_
   }
 }
 
-__global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const DispatchArgs a) {
+// FP8: rows leave as e4m3 + scales; SORTED: one warp per (token, slot) entry of send_list (one destination per warp, so the
+// per-slot arrays shrink to one element); SCALED: bf16 rows are multiplied by row_scale on the way. The variants exist for
+// their register counts: the copy loops are bound by the stores a SM keeps in flight, i.e. by resident warps.
+template <bool FP8, bool SORTED, bool SCALED>
+__global__ void __launch_bounds__(kCommThreads, SORTED ? 4 : 3) dispatch_push_kernel(const DispatchArgs a) {
   extern __shared__ int s_cnt[];  // rows this CTA sent: [E] per expert, or [world][num_tiles] per destination tile
   __shared__ int s_ok;
   __shared__ __align__(16) float s_scales[(kCommThreads / 32) * kMaxScaleGroups];  // fp8 mode: the 1x128 scales of the row each warp is sending
@@ -124,19 +128,20 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
   // Sorted mode (send_list != null): one warp per (token, slot) entry, entries ordered by
   // (local expert index, destination rank counted from the sender upwards), so that every rank's expert 0 fills first, then
   // expert 1, ... and the gated GEMM of the receivers can start while later experts still arrive.
-  const long long n_work = a.send_list ? static_cast<long long>(a.T) * a.K : a.T;
+  constexpr int NJ = SORTED ? 1 : kMaxK;  // destinations one warp serves
+  const long long n_work = SORTED ? static_cast<long long>(a.T) * a.K : a.T;
   for (long long wi = blockIdx.x * wpb + warp; wi < n_work; wi += static_cast<long long>(gridDim.x) * wpb) {
-    int t, jbeg, jend;
-    if (a.send_list) { const int tj = a.send_list[wi]; t = tj / a.K; jbeg = tj % a.K; jend = jbeg + 1; }
-    else { t = static_cast<int>(wi); jbeg = 0; jend = a.K; }
-    unsigned char* dst[kMaxK];
-    float scale[kMaxK];
-    int row_of[kMaxK];
+    int t, jbeg, nj;
+    if (SORTED) { const int tj = a.send_list[wi]; t = tj / a.K; jbeg = tj % a.K; nj = 1; }
+    else { t = static_cast<int>(wi); jbeg = 0; nj = a.K; }
+    unsigned char* dst[NJ];
+    float scale[NJ];
+    int row_of[NJ];
 #pragma unroll
-    for (int j = 0; j < kMaxK; ++j) {
+    for (int j = 0; j < NJ; ++j) {
       dst[j] = nullptr; scale[j] = 1.0f; row_of[j] = 0;
-      if (j >= jbeg && j < jend) {
-        const long long tj = static_cast<long long>(t) * a.K + j;
+      if (j < nj) {
+        const long long tj = static_cast<long long>(t) * a.K + jbeg + j;
         const int e = a.topk_idx[tj];
         if (e < 0 || e >= E) {  // not an expert: nothing is indexed with it; the step is flagged and the entry skipped
           if (lane == 0) report_failure(a.status, kStatusBadArg, kSiteExpertId, static_cast<unsigned long long>(tj), static_cast<unsigned long long>(static_cast<unsigned int>(e)), static_cast<unsigned long long>(E));
@@ -151,12 +156,12 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
         }
         row_of[j] = row;
         dst[j] = static_cast<unsigned char*>(a.peer_table[e / El]);
-        if (a.row_scale) scale[j] = a.row_scale[tj];
+        if (SCALED) scale[j] = a.row_scale[tj];
         if (lane == 0) atomicAdd(&s_cnt[a.tile_rows > 0 ? (e / El) * a.num_tiles + min(row / a.tile_rows, a.num_tiles - 1) : e], 1);
       }
     }
     const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.H);
-    if (!a.fp8) {
+    if constexpr (!FP8) {
       // Four 16-byte chunks per lane in flight before the first store: the loop is bound by the
       // latency of the local loads otherwise.
       constexpr int U = 4;
@@ -170,12 +175,12 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
           const int c = c0 + 32 * u;
           if (c >= chunks) break;
           float f[8];
-          if (a.row_scale) unpack8(v[u], f);
+          if (SCALED) unpack8(v[u], f);
 #pragma unroll
-          for (int j = 0; j < kMaxK; ++j) {
-            if (j < jbeg || j >= jend || dst[j] == nullptr) continue;
+          for (int j = 0; j < NJ; ++j) {
+            if (j >= nj || dst[j] == nullptr) continue;
             uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + (static_cast<long long>(row_of[j]) * a.H) * 2) + c;
-            if (a.row_scale) {
+            if (SCALED) {
               float g[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) g[i] = f[i] * scale[j];
@@ -207,8 +212,8 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
             const int c = c0 + 32 * u;
             if (c >= chunks16) break;
 #pragma unroll
-            for (int j = 0; j < kMaxK; ++j) {
-              if (j < jbeg || j >= jend || dst[j] == nullptr) continue;
+            for (int j = 0; j < NJ; ++j) {
+              if (j >= nj || dst[j] == nullptr) continue;
               *(reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c) = v[u];
             }
           }
@@ -237,8 +242,8 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
             const uint4 q = quantise16(raw[u], sc);
             if (active[u] && (lane & 7) == 0) my_scales[c / 8] = sc;
 #pragma unroll
-            for (int j = 0; j < kMaxK; ++j) {
-              if (j < jbeg || j >= jend || !active[u] || dst[j] == nullptr) continue;
+            for (int j = 0; j < NJ; ++j) {
+              if (j >= nj || !active[u] || dst[j] == nullptr) continue;
               uint4* out = reinterpret_cast<uint4*>(dst[j] + a.recv_heap_off + static_cast<long long>(row_of[j]) * a.H) + c;
               *out = q;
             }
@@ -249,8 +254,8 @@ __global__ void __launch_bounds__(kCommThreads) dispatch_push_kernel(const Dispa
       // sgroups is a multiple of 2 (H % 256 == 0): pairs of scales always; quads when the row's scale block is 16-byte aligned.
       const bool quad = (sgroups & 3) == 0;
 #pragma unroll
-      for (int j = 0; j < kMaxK; ++j) {
-        if (j < jbeg || j >= jend || dst[j] == nullptr) continue;
+      for (int j = 0; j < NJ; ++j) {
+        if (j >= nj || dst[j] == nullptr) continue;
         float* srow = reinterpret_cast<float*>(dst[j] + a.scale_heap_off) + static_cast<long long>(row_of[j]) * sgroups;
         if (quad) {
           for (int g = lane * 4; g < sgroups; g += 128) *reinterpret_cast<float4*>(srow + g) = *reinterpret_cast<const float4*>(my_scales + g);
@@ -387,13 +392,19 @@ cudaError_t launch_dispatch_push(const DispatchArgs& a, int ctas, cudaStream_t s
   if (a.tile_rows < 0 || (a.tile_rows > 0 && a.num_tiles < 1)) return cudaErrorInvalidValue;
   const size_t smem = sizeof(int) * (a.tile_rows > 0 ? static_cast<size_t>(a.world) * a.num_tiles : static_cast<size_t>(a.num_experts));
   if (smem > 200 * 1024) return cudaErrorInvalidValue;  // per-CTA histogram of destination tiles must fit in shared memory
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(dispatch_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return e;
-  }
-  dispatch_push_kernel<<<ctas, kCommThreads, smem, stream>>>(a);
-  note_launch();
-  return cudaGetLastError();
+  auto go = [&](auto kern) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return e;
+    }
+    kern<<<ctas, kCommThreads, smem, stream>>>(a);
+    note_launch();
+    return cudaGetLastError();
+  };
+  const bool sorted = a.send_list != nullptr, scaled = a.row_scale != nullptr;
+  if (a.fp8) return sorted ? go(dispatch_push_kernel<true, true, false>) : go(dispatch_push_kernel<true, false, false>);
+  if (sorted) return scaled ? go(dispatch_push_kernel<false, true, true>) : go(dispatch_push_kernel<false, true, false>);
+  return scaled ? go(dispatch_push_kernel<false, false, true>) : go(dispatch_push_kernel<false, false, false>);
 }
 
 cudaError_t launch_quantise_rows(const __nv_bfloat16* x, int T, int H, unsigned char* q, float* scales, int ctas, cudaStream_t stream) {
