@@ -35,7 +35,7 @@ def compat_on_real_peers(rank, world):
         assert torch.equal(y, ref), f"flash_t.all_to_all backward={backward} rank {rank}"
         fa.free_buffers()
         szs = fa.get_buffer_szs()
-        y2 = fa.comm.alloc((max(ref.shape[0], 1), hidden), torch.bfloat16)   # caller-owned, symmetric: written in place by the peers
+        y2 = fa.comm.alloc((max(int(mm.sum(axis=0).max()), 1), hidden), torch.bfloat16)   # caller-owned, symmetric (same size on every rank): written in place by the peers
         lbrecv = fa.comm.alloc((max(int(szs[2]), 1), hidden), torch.bfloat16)
         cros = fa.comm.alloc((max(int(szs[3]), 1), hidden), torch.bfloat16)
         y2.zero_()
