@@ -84,31 +84,47 @@ __global__ void dequant_fp8_kernel(const uint2* __restrict__ q, const float* __r
   }
 }
 
-__global__ void adamw_kernel(uint4* __restrict__ param, float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ v,
-                             const uint4* __restrict__ grad, long long n8, float lr, float b1, float b2, float eps, float wd, float c1, float c2,
+// One thread owns groups of 4 consecutive parameters: its fp32 accesses are 16 bytes, contiguous across the warp
+// (512 bytes per instruction), its bf16 accesses 8 bytes. Two groups are in flight per iteration. Nothing is read
+// twice, so every access is marked streaming (evict first).
+__global__ void adamw_kernel(uint2* __restrict__ param, float4* __restrict__ master, float4* __restrict__ m, float4* __restrict__ v,
+                             const uint2* __restrict__ grad, long long n4, float lr, float b1, float b2, float eps, float wd, float c1, float c2,
                              float gscale) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8; i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float g[8], w[8], mm[8], vv[8];
-    unpack8(grad[i], g);
-    float4 t;
-    t = master[2 * i]; w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
-    t = master[2 * i + 1]; w[4] = t.x; w[5] = t.y; w[6] = t.z; w[7] = t.w;
-    t = m[2 * i]; mm[0] = t.x; mm[1] = t.y; mm[2] = t.z; mm[3] = t.w;
-    t = m[2 * i + 1]; mm[4] = t.x; mm[5] = t.y; mm[6] = t.z; mm[7] = t.w;
-    t = v[2 * i]; vv[0] = t.x; vv[1] = t.y; vv[2] = t.z; vv[3] = t.w;
-    t = v[2 * i + 1]; vv[4] = t.x; vv[5] = t.y; vv[6] = t.z; vv[7] = t.w;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int U = 2;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < n4; i0 += U * stride) {
+    float4 w[U], mm[U], vv[U];
+    uint2 g[U];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float gk = g[k] * gscale;
-      mm[k] = b1 * mm[k] + (1.0f - b1) * gk;
-      vv[k] = b2 * vv[k] + (1.0f - b2) * gk * gk;
-      const float upd = (mm[k] * c1) / (sqrtf(vv[k] * c2) + eps);
-      w[k] = w[k] - lr * (upd + wd * w[k]);
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < n4) { g[u] = __ldcs(grad + i); w[u] = __ldcs(master + i); mm[u] = __ldcs(m + i); vv[u] = __ldcs(v + i); }
     }
-    master[2 * i] = make_float4(w[0], w[1], w[2], w[3]); master[2 * i + 1] = make_float4(w[4], w[5], w[6], w[7]);
-    m[2 * i] = make_float4(mm[0], mm[1], mm[2], mm[3]); m[2 * i + 1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
-    v[2 * i] = make_float4(vv[0], vv[1], vv[2], vv[3]); v[2 * i + 1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
-    param[i] = pack8(w);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= n4) break;
+      const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g[u].x));
+      const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g[u].y));
+      const float gk[4] = {g01.x * gscale, g01.y * gscale, g23.x * gscale, g23.y * gscale};
+      float* wp = reinterpret_cast<float*>(&w[u]);
+      float* mp = reinterpret_cast<float*>(&mm[u]);
+      float* vp = reinterpret_cast<float*>(&vv[u]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        mp[k] = b1 * mp[k] + (1.0f - b1) * gk[k];
+        vp[k] = b2 * vp[k] + (1.0f - b2) * gk[k] * gk[k];
+        const float upd = (mp[k] * c1) / (sqrtf(vp[k] * c2) + eps);
+        wp[k] = wp[k] - lr * (upd + wd * wp[k]);
+      }
+      __stcs(master + i, w[u]);
+      __stcs(m + i, mm[u]);
+      __stcs(v + i, vv[u]);
+      uint2 pb;
+      *reinterpret_cast<__nv_bfloat162*>(&pb.x) = __floats2bfloat162_rn(wp[0], wp[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&pb.y) = __floats2bfloat162_rn(wp[2], wp[3]);
+      __stcs(param + i, pb);
+    }
   }
 }
 
@@ -353,8 +369,8 @@ cudaError_t launch_adamw(__nv_bfloat16* param, float* master, float* m, float* v
                          float beta2, float eps, float weight_decay, float bias_c1, float bias_c2, float grad_scale, cudaStream_t stream) {
   if (n % 8) return cudaErrorInvalidValue;
   if (n == 0) return cudaSuccess;
-  adamw_kernel<<<grid_for(n / 8), 256, 0, stream>>>(reinterpret_cast<uint4*>(param), reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
-                                                    reinterpret_cast<float4*>(v), reinterpret_cast<const uint4*>(grad), n / 8, lr, beta1, beta2, eps,
+  adamw_kernel<<<grid_for(n / 8), 256, 0, stream>>>(reinterpret_cast<uint2*>(param), reinterpret_cast<float4*>(master), reinterpret_cast<float4*>(m),
+                                                    reinterpret_cast<float4*>(v), reinterpret_cast<const uint2*>(grad), n / 4, lr, beta1, beta2, eps,
                                                     weight_decay, bias_c1, bias_c2, grad_scale);
   note_launch();
   return cudaGetLastError();
