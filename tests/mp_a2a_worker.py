@@ -2,6 +2,8 @@
 import os
 import sys
 
+os.environ.setdefault("FASTB_CHECK_SYMM", "1")  # every symmetric allocation is compared across the ranks (read at import)
+
 import numpy as np
 import torch
 import torch.distributed as dist

@@ -3,6 +3,8 @@ single-device fp32 reference built from the gathered expert weights."""
 import os
 import sys
 
+os.environ.setdefault("FASTB_CHECK_SYMM", "1")  # every symmetric allocation is compared across the ranks (read at import)
+
 import torch
 import torch.distributed as dist
 
