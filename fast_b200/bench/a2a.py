@@ -22,21 +22,27 @@ from ..sched import PlanKind, Topology
 from ..utils.results import ResultLog
 
 
-def _time_ms(fn, iters, warmup):
+def _time_ms(fn, iters, warmup, batches=3):
+    """Device time of one call of ``fn``: ``batches`` batches of ``iters`` back-to-back calls between CUDA
+    events, each batch's mean taken as the max over ranks, the median batch reported. Launch-bound
+    collectives on many processes see a late rank now and then; one such batch does not move the figure."""
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev[0].record()
-    for _ in range(iters):
-        fn()
-    ev[1].record()
-    torch.cuda.synchronize()
-    t = torch.tensor([ev[0].elapsed_time(ev[1]) / iters], device="cuda")
+    means = []
+    for _ in range(batches):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(iters):
+            fn()
+        ev[1].record()
+        torch.cuda.synchronize()
+        means.append(ev[0].elapsed_time(ev[1]) / iters)
+    t = torch.tensor(means, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    return float(t.median().item())
 
 
 def _e2e_fresh_ms(comm, out, inp, m, kind, chunk, **opts):
