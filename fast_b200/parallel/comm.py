@@ -63,8 +63,11 @@ class Schedule:
         bytes it takes over from busier neighbours. That trades memory (180 GB per GPU) for the
         absence of buffer credits and their waits; a caller short of memory can split the exchange
         into several ``all_to_all_v`` calls over slices of the matrix, which reuse the same staging."""
-        b = self.plan.buffers.max(axis=0) * self.unit_bytes
-        return {"input": int(b[0]), "output": int(b[1]), "balance": int(b[2]), "rail": int(b[3])}
+        mb = self.__dict__.get("_max_bytes")
+        if mb is None:  # computed once: this sits on the launch path of every collective
+            b = self.plan.buffers.max(axis=0) * self.unit_bytes
+            mb = self.__dict__["_max_bytes"] = {"input": int(b[0]), "output": int(b[1]), "balance": int(b[2]), "rail": int(b[3])}
+        return mb
 
     def buffer_sizes(self) -> dict:
         """Bytes of each buffer this rank needs (the reference's get_buffer_szs, amd/flash.cpp:385-397)."""
