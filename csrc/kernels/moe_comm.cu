@@ -130,7 +130,32 @@ __global__ void __launch_bounds__(kCommThreads, SORTED ? 4 : 3) dispatch_push_ke
   // expert 1, ... and the gated GEMM of the receivers can start while later experts still arrive.
   constexpr int NJ = SORTED ? 1 : kMaxK;  // destinations one warp serves
   const long long n_work = SORTED ? static_cast<long long>(a.T) * a.K : a.T;
-  for (long long wi = blockIdx.x * wpb + warp; wi < n_work; wi += static_cast<long long>(gridDim.x) * wpb) {
+  // Adds this CTA's row counts to the receivers' arrival counters (release: the rows are stored before the counters move)
+  // and clears them. Called by every thread of the CTA.
+  auto publish_counts = [&]() {
+    __syncthreads();  // every row of this CTA so far is stored
+    for (int e = threadIdx.x; e < n_cnt; e += blockDim.x) {
+      const int n = s_cnt[e];
+      if (n == 0) continue;
+      s_cnt[e] = 0;
+      const int peer = a.tile_rows > 0 ? e / a.num_tiles : e / El;
+      const int slot = a.tile_rows > 0 ? e % a.num_tiles : e % El;
+      unsigned long long* cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[peer]) + a.arrive_heap_off);
+      fence_sys();
+      red_add_release_sys(cnt + slot, static_cast<unsigned long long>(n));
+    }
+    __syncthreads();  // cleared before the next rows are counted
+  };
+  // Every warp of a CTA makes the same number of rounds (a round = one entry per warp), so the CTA can meet at a barrier
+  // between rounds. In sorted order the counts are published every kPublishRounds rounds instead of once at the end:
+  // the CTAs walk the send list together, so a receiver's tiles complete in list order while the dispatch is still
+  // running, which is what lets its gated GEMM start early.
+  constexpr int kPublishRounds = 8;
+  const long long round_stride = static_cast<long long>(gridDim.x) * wpb;
+  int round = 0;
+  for (long long base = static_cast<long long>(blockIdx.x) * wpb; base < n_work; base += round_stride) {
+    const long long wi = base + warp;
+    if (wi < n_work) {
     int t, jbeg, nj;
     if (SORTED) { const int tj = a.send_list[wi]; t = tj / a.K; jbeg = tj % a.K; nj = 1; }
     else { t = static_cast<int>(wi); jbeg = 0; nj = a.K; }
@@ -267,17 +292,10 @@ __global__ void __launch_bounds__(kCommThreads, SORTED ? 4 : 3) dispatch_push_ke
       }
       __syncwarp();  // the next row reuses my_scales
     }
+    }  // wi < n_work
+    if (SORTED && (++round % kPublishRounds) == 0 && base + round_stride < n_work) publish_counts();
   }
-  __syncthreads();  // every row of this CTA is stored before the counters move
-  for (int e = threadIdx.x; e < n_cnt; e += blockDim.x) {
-    const int n = s_cnt[e];
-    if (n == 0) continue;
-    const int peer = a.tile_rows > 0 ? e / a.num_tiles : e / El;
-    const int slot = a.tile_rows > 0 ? e % a.num_tiles : e % El;
-    unsigned long long* cnt = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a.peer_table[peer]) + a.arrive_heap_off);
-    fence_sys();
-    red_add_release_sys(cnt + slot, static_cast<unsigned long long>(n));
-  }
+  publish_counts();
 }
 
 __global__ void __launch_bounds__(kCommThreads) combine_pull_kernel(const CombineArgs a) {

@@ -86,11 +86,11 @@ def heap_bytes_needed(world, tokens, hidden, top_k, experts_per_gpu, fp8):
     return int(cap * hidden * (3 if fp8 else 4.2)) + (256 << 20)
 
 
-def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False, overlap=False, fp8_direct=False):
+def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_k=8, fp8=False, iters=20, warmup=5, skip_nccl=False, overlap=False, fp8_direct=False, reserve_sms=16):
     """Runs the forward layer on an existing communicator and returns the result dict (every rank)."""
     rank, world = comm.rank, comm.world
     E, K, H, I, T, El = experts_per_gpu * world, top_k, hidden, inter, tokens, experts_per_gpu
-    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False, overlap_dispatch=overlap, fp8_direct=fp8_direct)
+    eng = ExpertParallel(comm, E, H, I, K, T, fp8_dispatch=fp8, training=False, overlap_dispatch=overlap, fp8_direct=fp8_direct, overlap_reserve_sms=reserve_sms)
     g = torch.Generator(device="cuda").manual_seed(7)      # same on every rank: the bias is replicated
     bias = torch.randn(E, generator=g, device="cuda") * 1.5
     gr = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -139,7 +139,7 @@ def measure(comm, tokens=4096, hidden=7168, inter=2048, experts_per_gpu=32, top_
     combine_alone_us = _max_over_ranks([c0.elapsed_time(c1) * 1e3 / iters], world)[0]
     route_us, dispatch_us, experts_us, combine_us, layer_us = _max_over_ranks(acc, world)
     tm = eng.traffic_matrix().cpu().numpy()
-    res = {"bench": "moe_forward", "world": world, "overlap_dispatch": overlap, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K,
+    res = {"bench": "moe_forward", "world": world, "overlap_dispatch": overlap, "overlap_reserve_sms": eng.overlap_reserve_sms, "tokens_per_rank": T, "hidden": H, "inter": I, "experts": E, "top_k": K,
            "dispatch_dtype": "fp8_e4m3_1x128" if fp8 else "bf16", "expert_feed": "e4m3 rows converted inside the GEMM" if eng.fp8_direct else ("dequantised to bf16 first" if fp8 else "bf16"), "route_us": round(route_us, 1), "dispatch_us": round(dispatch_us, 1),
            "experts_us": round(experts_us, 1), "combine_us": round(combine_us, 1), "combine_alone_us": round(combine_alone_us, 1),
            "dispatch_plus_combine_us": round(dispatch_us + combine_alone_us, 1),
@@ -218,6 +218,7 @@ def main():
     ap.add_argument("--graph", action="store_true", help="time the whole forward layer eagerly and as one CUDA graph replay")
     ap.add_argument("--fp8-direct", action="store_true", help="with --fp8: feed the e4m3 rows to the expert GEMM as they are (converter warps) instead of dequantising first")
     ap.add_argument("--overlap", action="store_true", help="send rows expert by expert on a side stream while the gated GEMM runs (dispatch_us then only times the launch)")
+    ap.add_argument("--reserve-sms", type=int, default=16, help="with --overlap: SMs the first expert GEMM leaves to the dispatch kernel")
     ap.add_argument("--out", default="", help="append the result row to this file (JSON lines)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -229,7 +230,7 @@ def main():
     if a.graph:
         res = measure_graph(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, max(a.iters, 20))
     else:
-        res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap, a.fp8_direct)
+        res = measure(comm, a.tokens, a.hidden, a.inter, a.experts_per_gpu, a.top_k, a.fp8, a.iters, a.warmup, a.skip_nccl, a.overlap, a.fp8_direct, a.reserve_sms)
     if rank == 0:
         print(json.dumps(res), flush=True)
         ResultLog(a.out or None, "moe_fwd").add(res)

@@ -41,6 +41,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--hidden", type=int, default=7168)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--cta-sweep", type=int, nargs="*", default=[], help="also time the all-to-all(v) push with these CTA counts (one CTA per SM)")
     a = ap.parse_args()
     assert torch.cuda.device_count() >= 2, "needs two GPUs in one process"
     C = runtime.ext()
@@ -71,14 +72,17 @@ def main():
     src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda:0")
     epoch = [0]
 
-    def push(bulk=False):
+    def push(bulk=False, ctas=148):
         epoch[0] += 1
         C.a2a_launch(prog, h0, [src.data_ptr(), 0, h0.base_ptr(0), h0.base_ptr(0)], [0, out_off, 0, 0], sig_off, epoch[0], status, timeout_ns,
-                     min(148, prog.n_items), 512, 0, bulk)
+                     min(ctas, prog.n_items), 512, 0, bulk)
 
     for name, bulk in (("a2a_push", False), ("a2a_push_bulk_copy", True)):
         ms = _time(lambda: push(bulk), a.iters)
         out[name] = {"link_bytes": nbytes, "ms": round(ms, 4), "GBps": round(nbytes / ms / 1e6, 1)}
+    # how many SMs each copy loop needs to fill the link (one CTA per SM): GB/s by CTA count
+    out["a2a_push_GBps_by_ctas"] = {str(c): round(nbytes / _time(lambda: push(False, c), a.iters) / 1e6, 1) for c in a.cta_sweep}
+    out["a2a_push_bulk_copy_GBps_by_ctas"] = {str(c): round(nbytes / _time(lambda: push(True, c), a.iters) / 1e6, 1) for c in a.cta_sweep}
     got = h1.tensor(out_off, [nbytes], torch.uint8)
     assert torch.equal(got.to("cuda:0"), src), "pushed bytes differ"
 

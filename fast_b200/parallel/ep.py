@@ -50,7 +50,7 @@ class ExpertParallel:
 
     def __init__(self, comm: Communicator, num_experts: int, hidden: int, inter: int, top_k: int, max_tokens: int, fp8_dispatch: bool = False,
                  capacity_rows: Optional[int] = None, training: bool = True, comm_ctas: Optional[int] = None, overlap_dispatch: bool = False,
-                 graph_mode: bool = False, fp8_direct: bool = False):
+                 graph_mode: bool = False, fp8_direct: bool = False, overlap_reserve_sms: int = 16):
         C = runtime.ext()
         self._C, self.comm = C, comm
         W = comm.world
@@ -73,7 +73,9 @@ class ExpertParallel:
         # Overlapped dispatch: the gated GEMM is persistent (one CTA per SM, nearly all of its shared memory) and
         # waits for rows that this rank's own dispatch kernel must send, so it may never own every SM: it leaves
         # `reserve` SMs to the dispatch kernel, whose grid is sized for them.
-        self.overlap_reserve_sms = 24 if overlap_dispatch else 0
+        # SMs the first expert GEMM leaves to the side-stream dispatch in overlap mode (the GEMM is persistent and would
+        # otherwise hold every SM): about 16 SMs of copy loops fill 0.87 of an NVLink port, 32 all of it.
+        self.overlap_reserve_sms = max(2, int(overlap_reserve_sms)) if overlap_dispatch else 0
         self.gemm1_ctas = (sms - self.overlap_reserve_sms) & ~1
         worst = W * max_tokens * min(top_k, self.El) + 256 * self.El
         self.cap = int(capacity_rows) if capacity_rows else worst
@@ -218,30 +220,31 @@ class ExpertParallel:
 
     def dispatch(self, x: torch.Tensor, rs: RouteState) -> None:
         C = self._C
-        send_list = None
+        send_list = xq = xs = None
         if not self.fp8:
             C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)  # on the main stream: ordered before any consumer
         if self.overlap:
-            # Side stream: ordered after routing, concurrent with whatever the main stream queues next
-            # (the gated expert GEMM). The main stream re-joins in experts_forward.
+            # The sending order and (fp8) the quantised rows are made on the main stream, with the whole GPU, before the
+            # gated GEMM is queued behind them. Only the sends themselves go to the side stream: ordered after routing,
+            # concurrent with whatever the main stream queues next (the gated expert GEMM); the main stream re-joins
+            # in experts_forward.
+            C.build_send_list(rs.topk_idx, rs.slot_in_block, rs.block_base, self.send_pos, self.send_list, self.status)
+            send_list = self.send_list
+            if self.fp8:
+                # Sorted sending gives every (token, slot) entry a warp of its own: quantise each row once, entries copy bytes.
+                if self._xq_send is None:
+                    self._xq_send = torch.empty(self.T, self.H, dtype=torch.uint8, device=x.device)
+                    self._xs_send = torch.empty(self.T, self.H // 128, dtype=torch.float32, device=x.device)
+                xq, xs = self._xq_send, self._xs_send
+                C.quantise_rows(x, xq, xs, self.comm_ctas)
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream())
             self.side.wait_event(ev)
             x.record_stream(self.side)
             ctx = torch.cuda.stream(self.side)
             ctx.__enter__()
-            C.build_send_list(rs.topk_idx, rs.slot_in_block, rs.block_base, self.send_pos, self.send_list, self.status)
-            send_list = self.send_list
         try:
             if self.fp8:
-                xq = xs = None
-                if send_list is not None:
-                    # Sorted sending gives every (token, slot) entry a warp of its own: quantise each row once, entries copy bytes.
-                    if self._xq_send is None:
-                        self._xq_send = torch.empty(self.T, self.H, dtype=torch.uint8, device=x.device)
-                        self._xs_send = torch.empty(self.T, self.H // 128, dtype=torch.float32, device=x.device)
-                    xq, xs = self._xq_send, self._xs_send
-                    C.quantise_rows(x, xq, xs, 4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas)
                 C.dispatch_push(self.comm.heap, x, rs.topk_idx, None, rs.slot_in_block, rs.block_base, rs.send_base, rs.dest_row, True, True,
                                 self._off(self.xq_recv), self._off(self.xs_recv), self.arrive._symm_off, 0, 0, self.status, self.timeout_ns,
                                 4 * self.overlap_reserve_sms if self.overlap else self.comm_ctas, send_list, self.tile_rows, self.ntiles, xq, xs)
