@@ -134,7 +134,17 @@ void run_rank(World& w, int me) {
     auto dispatch = [&](int k, int n) {
       std::vector<int> sent(E, 0);
       std::vector<int> sent_tile(c.tiles ? static_cast<size_t>(W) * ntiles : 0, 0);  // the kernel's per-CTA histogram of destination tiles
-      for (int t = k; t < T; t += n)
+      // Tile counts are published (release) and cleared every few tokens, as the sorted dispatch does every few
+      // rounds, and once more at the end.
+      auto publish_tiles = [&]() {
+        for (int p = 0; p < W; ++p)
+          for (int tl = 0; tl < ntiles; ++tl) {
+            int& cnt = sent_tile[static_cast<size_t>(p) * ntiles + tl];
+            if (cnt) { w.r[p]->tile_arrive[tl].fetch_add(static_cast<uint64_t>(cnt), std::memory_order_release); cnt = 0; }
+          }
+      };
+      int rounds = 0;
+      for (int t = k; t < T; t += n) {
         for (int j = 0; j < K; ++j) {
           const int e = topk[t * K + j];
           Rank& owner = *w.r[e / El];
@@ -143,11 +153,10 @@ void run_rank(World& w, int me) {
           ++sent[e];
           if (c.tiles) ++sent_tile[static_cast<size_t>(e / El) * ntiles + dest_row[t * K + j] / RA];
         }
+        if (c.tiles && ++rounds % 3 == 0) publish_tiles();
+      }
       if (c.tiles) {
-        for (int p = 0; p < W; ++p)
-          for (int tl = 0; tl < ntiles; ++tl)
-            if (sent_tile[static_cast<size_t>(p) * ntiles + tl])
-              w.r[p]->tile_arrive[tl].fetch_add(static_cast<uint64_t>(sent_tile[static_cast<size_t>(p) * ntiles + tl]), std::memory_order_release);
+        publish_tiles();
         return;
       }
       for (int e = 0; e < E; ++e)
