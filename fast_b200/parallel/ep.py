@@ -281,8 +281,9 @@ class ExpertParallel:
                 C.dequant_fp8(self.xq_recv, self.xs_recv, self.x_recv, rs.group_off.data_ptr() + 4 * self.El)
                 C.zero_pad_rows(self.x_recv, rs.group_off, rs.group_rows)
                 gate = None
+            # A gated GEMM leaves SMs to the dispatch it waits for; an ungated one (every row is in) takes them all.
             gemm.grouped_gemm_fwd(self.x_recv, w13, rs.group_off, self.act, swiglu=True, gate_up_out=self.gu if self.training else None, gate=gate,
-                                  gate_tile_rows=gate_tile, ctas=self.gemm1_ctas)
+                                  gate_tile_rows=gate_tile, ctas=self.gemm1_ctas if gate is not None else None)
         gemm.grouped_gemm_fwd(self.act, w2, rs.group_off, self.y)
         self._join_dispatch()
         C.peer_signal(self.comm.heap, self._flag_off(1), rs.epoch, self.epoch_dev.data_ptr() if self.graph_mode else 0)
