@@ -156,142 +156,142 @@ __global__ void __launch_bounds__(kCommThreads, SORTED ? 4 : 3) dispatch_push_ke
   for (long long base = static_cast<long long>(blockIdx.x) * wpb; base < n_work; base += round_stride) {
     const long long wi = base + warp;
     if (wi < n_work) {
-    int t, jbeg, nj;
-    if (SORTED) { const int tj = a.send_list[wi]; t = tj / a.K; jbeg = tj % a.K; nj = 1; }
-    else { t = static_cast<int>(wi); jbeg = 0; nj = a.K; }
-    unsigned char* out_row[NJ];  // where each slot's row starts on its receiver (null: nothing to send for the slot)
-    float scale[NJ];
-    int row_of[NJ];
+      int t, jbeg, nj;
+      if (SORTED) { const int tj = a.send_list[wi]; t = tj / a.K; jbeg = tj % a.K; nj = 1; }
+      else { t = static_cast<int>(wi); jbeg = 0; nj = a.K; }
+      unsigned char* out_row[NJ];  // where each slot's row starts on its receiver (null: nothing to send for the slot)
+      float scale[NJ];
+      int row_of[NJ];
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-      out_row[j] = nullptr; scale[j] = 1.0f; row_of[j] = 0;
-      if (j < nj) {
-        const long long tj = static_cast<long long>(t) * a.K + jbeg + j;
-        const int e = a.topk_idx[tj];
-        if (e < 0 || e >= E) {  // not an expert: nothing is indexed with it; the step is flagged and the entry skipped
-          if (lane == 0) report_failure(a.status, kStatusBadArg, kSiteExpertId, static_cast<unsigned long long>(tj), static_cast<unsigned long long>(static_cast<unsigned int>(e)), static_cast<unsigned long long>(E));
-          continue;
-        }
-        int row;
-        if (a.compute_rows) {
-          row = a.send_base[e] + a.block_base[static_cast<long long>(t / tpb) * E + e] + a.slot_in_block[tj];
-          if (lane == 0) a.dest_row[tj] = row;
-        } else {
-          row = a.dest_row[tj];
-        }
-        row_of[j] = row;
-        out_row[j] = static_cast<unsigned char*>(a.peer_table[e / El]) + a.recv_heap_off + static_cast<long long>(row) * a.H * (FP8 ? 1 : 2);
-        if (SCALED) scale[j] = a.row_scale[tj];
-        if (lane == 0) atomicAdd(&s_cnt[a.tile_rows > 0 ? (e / El) * a.num_tiles + min(row / a.tile_rows, a.num_tiles - 1) : e], 1);
-      }
-    }
-    const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.H);
-    if constexpr (!FP8) {
-      // Four 16-byte chunks per lane in flight before the first store: the loop is bound by the
-      // latency of the local loads otherwise.
-      constexpr int U = 4;
-      for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
-        uint4 v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (c0 + 32 * u < chunks) v[u] = __ldg(src + c0 + 32 * u);
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int c = c0 + 32 * u;
-          if (c >= chunks) break;
-          float f[8];
-          if (SCALED) unpack8(v[u], f);
-#pragma unroll
-          for (int j = 0; j < NJ; ++j) {
-            if (j >= nj || out_row[j] == nullptr) continue;
-            uint4* out = reinterpret_cast<uint4*>(out_row[j]) + c;
-            if (SCALED) {
-              float g[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) g[i] = f[i] * scale[j];
-              *out = pack8(g);
-            } else {
-              *out = v[u];
-            }
+      for (int j = 0; j < NJ; ++j) {
+        out_row[j] = nullptr; scale[j] = 1.0f; row_of[j] = 0;
+        if (j < nj) {
+          const long long tj = static_cast<long long>(t) * a.K + jbeg + j;
+          const int e = a.topk_idx[tj];
+          if (e < 0 || e >= E) {  // not an expert: nothing is indexed with it; the step is flagged and the entry skipped
+            if (lane == 0) report_failure(a.status, kStatusBadArg, kSiteExpertId, static_cast<unsigned long long>(tj), static_cast<unsigned long long>(static_cast<unsigned int>(e)), static_cast<unsigned long long>(E));
+            continue;
           }
+          int row;
+          if (a.compute_rows) {
+            row = a.send_base[e] + a.block_base[static_cast<long long>(t / tpb) * E + e] + a.slot_in_block[tj];
+            if (lane == 0) a.dest_row[tj] = row;
+          } else {
+            row = a.dest_row[tj];
+          }
+          row_of[j] = row;
+          out_row[j] = static_cast<unsigned char*>(a.peer_table[e / El]) + a.recv_heap_off + static_cast<long long>(row) * a.H * (FP8 ? 1 : 2);
+          if (SCALED) scale[j] = a.row_scale[tj];
+          if (lane == 0) atomicAdd(&s_cnt[a.tile_rows > 0 ? (e / El) * a.num_tiles + min(row / a.tile_rows, a.num_tiles - 1) : e], 1);
         }
       }
-    } else {
-      // 16 elements per lane (one 16-byte store of e4m3); 8 consecutive lanes = 128 elements share
-      // one scale (amax / 448). The row's scales leave as 16-byte stores after the payload: 4-byte
-      // remote stores would each cost a packet of their own.
-      const int sgroups = a.H / 128;
-      const int chunks16 = a.H / 16;
-      float* my_scales = s_scales + warp * kMaxScaleGroups;
-      if (a.xq != nullptr) {
-        // Rows were quantised once by quantise_rows_kernel: this entry copies bytes.
-        const uint4* qsrc = reinterpret_cast<const uint4*>(a.xq + static_cast<long long>(t) * a.H);
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.H);
+      if constexpr (!FP8) {
+        // Four 16-byte chunks per lane in flight before the first store: the loop is bound by the
+        // latency of the local loads otherwise.
         constexpr int U = 4;
-        for (int c0 = lane; c0 < chunks16; c0 += 32 * U) {
+        for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
           uint4 v[U];
 #pragma unroll
           for (int u = 0; u < U; ++u)
-            if (c0 + 32 * u < chunks16) v[u] = __ldg(qsrc + c0 + 32 * u);
+            if (c0 + 32 * u < chunks) v[u] = __ldg(src + c0 + 32 * u);
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const int c = c0 + 32 * u;
-            if (c >= chunks16) break;
+            if (c >= chunks) break;
+            float f[8];
+            if (SCALED) unpack8(v[u], f);
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
               if (j >= nj || out_row[j] == nullptr) continue;
-              *(reinterpret_cast<uint4*>(out_row[j]) + c) = v[u];
+              uint4* out = reinterpret_cast<uint4*>(out_row[j]) + c;
+              if (SCALED) {
+                float g[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) g[i] = f[i] * scale[j];
+                *out = pack8(g);
+              } else {
+                *out = v[u];
+              }
             }
           }
         }
-        for (int g = lane; g < sgroups; g += 32) my_scales[g] = __ldg(a.xq_scales + static_cast<long long>(t) * sgroups + g);
       } else {
-        // The whole warp walks the row together (the shuffles in quantise16 need every lane); lanes past
-        // the end of a short row carry zeros and store nothing. Two blocks of 512 elements are in flight
-        // per pass (their loads are issued before either is reduced). Measured: neither more resident warps
-        // (8, 16 or 24 per SM), nor requesting the next pass before reducing this one, nor packed arithmetic
-        // moves this path off about 600 GB/s to one peer; a plain copy of already quantised rows reaches 624.
-        constexpr int U = 2;
-        for (int c0 = 0; c0 < chunks16; c0 += 32 * U) {
-          uint4 raw[U][2];
-          bool active[U];
+        // 16 elements per lane (one 16-byte store of e4m3); 8 consecutive lanes = 128 elements share
+        // one scale (amax / 448). The row's scales leave as 16-byte stores after the payload: 4-byte
+        // remote stores would each cost a packet of their own.
+        const int sgroups = a.H / 128;
+        const int chunks16 = a.H / 16;
+        float* my_scales = s_scales + warp * kMaxScaleGroups;
+        if (a.xq != nullptr) {
+          // Rows were quantised once by quantise_rows_kernel: this entry copies bytes.
+          const uint4* qsrc = reinterpret_cast<const uint4*>(a.xq + static_cast<long long>(t) * a.H);
+          constexpr int U = 4;
+          for (int c0 = lane; c0 < chunks16; c0 += 32 * U) {
+            uint4 v[U];
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int c = c0 + 32 * u + lane;
-            active[u] = c < chunks16;
-            raw[u][0] = active[u] ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0);
-            raw[u][1] = active[u] ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < U; ++u)
+              if (c0 + 32 * u < chunks16) v[u] = __ldg(qsrc + c0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int c = c0 + 32 * u;
+              if (c >= chunks16) break;
+#pragma unroll
+              for (int j = 0; j < NJ; ++j) {
+                if (j >= nj || out_row[j] == nullptr) continue;
+                *(reinterpret_cast<uint4*>(out_row[j]) + c) = v[u];
+              }
+            }
           }
+          for (int g = lane; g < sgroups; g += 32) my_scales[g] = __ldg(a.xq_scales + static_cast<long long>(t) * sgroups + g);
+        } else {
+          // The whole warp walks the row together (the shuffles in quantise16 need every lane); lanes past
+          // the end of a short row carry zeros and store nothing. Two blocks of 512 elements are in flight
+          // per pass (their loads are issued before either is reduced). Measured: neither more resident warps
+          // (8, 16 or 24 per SM), nor requesting the next pass before reducing this one, nor packed arithmetic
+          // moves this path off about 600 GB/s to one peer; a plain copy of already quantised rows reaches 624.
+          constexpr int U = 2;
+          for (int c0 = 0; c0 < chunks16; c0 += 32 * U) {
+            uint4 raw[U][2];
+            bool active[U];
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            if (c0 + 32 * u >= chunks16) break;  // warp-uniform: the second block of the last pass may not exist
-            const int c = c0 + 32 * u + lane;
-            float sc;
-            const uint4 q = quantise16(raw[u], sc);
-            if (active[u] && (lane & 7) == 0) my_scales[c / 8] = sc;
+            for (int u = 0; u < U; ++u) {
+              const int c = c0 + 32 * u + lane;
+              active[u] = c < chunks16;
+              raw[u][0] = active[u] ? __ldg(src + 2 * c) : make_uint4(0, 0, 0, 0);
+              raw[u][1] = active[u] ? __ldg(src + 2 * c + 1) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-              if (j >= nj || !active[u] || out_row[j] == nullptr) continue;
-              *(reinterpret_cast<uint4*>(out_row[j]) + c) = q;
+            for (int u = 0; u < U; ++u) {
+              if (c0 + 32 * u >= chunks16) break;  // warp-uniform: the second block of the last pass may not exist
+              const int c = c0 + 32 * u + lane;
+              float sc;
+              const uint4 q = quantise16(raw[u], sc);
+              if (active[u] && (lane & 7) == 0) my_scales[c / 8] = sc;
+#pragma unroll
+              for (int j = 0; j < NJ; ++j) {
+                if (j >= nj || !active[u] || out_row[j] == nullptr) continue;
+                *(reinterpret_cast<uint4*>(out_row[j]) + c) = q;
+              }
             }
           }
         }
-      }
-      __syncwarp();
-      // sgroups is a multiple of 2 (H % 256 == 0): pairs of scales always; quads when the row's scale block is 16-byte aligned.
-      const bool quad = (sgroups & 3) == 0;
+        __syncwarp();
+        // sgroups is a multiple of 2 (H % 256 == 0): pairs of scales always; quads when the row's scale block is 16-byte aligned.
+        const bool quad = (sgroups & 3) == 0;
 #pragma unroll
-      for (int j = 0; j < NJ; ++j) {
-        if (j >= nj || out_row[j] == nullptr) continue;
-        // the receiver's slab base is the row pointer minus the row's offset in the receive buffer
-        float* srow = reinterpret_cast<float*>(out_row[j] - a.recv_heap_off - static_cast<long long>(row_of[j]) * a.H + a.scale_heap_off) + static_cast<long long>(row_of[j]) * sgroups;
-        if (quad) {
-          for (int g = lane * 4; g < sgroups; g += 128) *reinterpret_cast<float4*>(srow + g) = *reinterpret_cast<const float4*>(my_scales + g);
-        } else {
-          for (int g = lane * 2; g < sgroups; g += 64) *reinterpret_cast<float2*>(srow + g) = *reinterpret_cast<const float2*>(my_scales + g);
+        for (int j = 0; j < NJ; ++j) {
+          if (j >= nj || out_row[j] == nullptr) continue;
+          // the receiver's slab base is the row pointer minus the row's offset in the receive buffer
+          float* srow = reinterpret_cast<float*>(out_row[j] - a.recv_heap_off - static_cast<long long>(row_of[j]) * a.H + a.scale_heap_off) + static_cast<long long>(row_of[j]) * sgroups;
+          if (quad) {
+            for (int g = lane * 4; g < sgroups; g += 128) *reinterpret_cast<float4*>(srow + g) = *reinterpret_cast<const float4*>(my_scales + g);
+          } else {
+            for (int g = lane * 2; g < sgroups; g += 64) *reinterpret_cast<float2*>(srow + g) = *reinterpret_cast<const float2*>(my_scales + g);
+          }
         }
+        __syncwarp();  // the next row reuses my_scales
       }
-      __syncwarp();  // the next row reuses my_scales
-    }
     }  // wi < n_work
     if (SORTED && (++round % kPublishRounds) == 0 && base + round_stride < n_work) publish_counts();
   }
