@@ -17,7 +17,7 @@ namespace fastb {
 namespace {
 
 constexpr int kTokensPerBlock = kRouteTokensPerBlock;
-constexpr int kGateThreads = 256;
+constexpr int kGateThreads = 512;  // forward: 16 warps per block, two tokens per warp and pass
 constexpr int kGateBwdThreads = 512;            // backward: 16 warps hide the shared-memory and reduction latency of the per-token chain
 constexpr int kGateBwdMaxChunksPerThread = 2;  // backward: hidden <= 2 * 512 * 8 = 8192
 
